@@ -1,0 +1,305 @@
+/*
+ * C ABI of the sm_100a (B200) NVFP4 packed-weight kernels.
+ *
+ * This is the boundary a host runtime binds.  It is a drop-in for the
+ * reference's SM75 adapter ABI (crates/nml-kernel-nvfp4/include/nml_nvfp4.h):
+ * the four request structs below begin with exactly the reference's fields in
+ * the reference's order, so the `#[repr(C)]` mirrors in
+ * crates/nml-kernel-nvfp4/src/cuda.rs:39-117 can be passed unchanged.  Fields
+ * added here sit after the reference's last field and are read only when
+ * `struct_size` says they are present.
+ *
+ * Conventions (same as the reference, nml_nvfp4.h:16-17,
+ * turing_adapter.cu:13-22): every pointer is a borrowed device address; the
+ * library only enqueues work on `stream`, never synchronises, and never
+ * allocates or retains memory.  Every entry point returns 0 on success,
+ * 1 for an invalid argument, 2 for a launch failure, and writes a
+ * NUL-terminated message into `error_message` (when capacity > 0) on failure.
+ * All extents must be positive and fit in int32.
+ *
+ * Weight representation (NVFP4 recipe v2, crates/nml-parameter/src/lib.rs:393-597):
+ *   payload      u8 [rows, ceil(K/2)]  two E2M1 codes per byte, even column in the low nibble
+ *   block_scales u8 [rows, ceil(K/16)] unsigned E4M3FN, one per 16 consecutive K
+ *   global_scale f32 scalar in device memory
+ *   value(r, k) = e2m1(code) * (e4m3(scale) * global)
+ */
+#ifndef NML_NVFP4_SM100_H_
+#define NML_NVFP4_SM100_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Same codes as NmlNvFp4DType (nml_nvfp4.h:11-14). */
+typedef enum NmlSm100DType {
+  NML_SM100_F16 = 1,
+  NML_SM100_BF16 = 2,
+} NmlSm100DType;
+
+#define NML_SM100_OK 0
+#define NML_SM100_INVALID_ARGUMENT 1
+#define NML_SM100_LAUNCH_FAILURE 2
+
+/* Y[rows, outputs] = X[rows, inputs] * W[outputs, inputs]^T (+ bias), f32 accumulate.
+ * Field-for-field NmlNvFp4Linear (nml_nvfp4.h:18-31). */
+typedef struct NmlSm100Linear {
+  size_t struct_size;
+  const void *activation;      /* [rows, inputs] dtype */
+  const uint8_t *payload;      /* [outputs, ceil(inputs/2)] */
+  const uint8_t *block_scales; /* [outputs, ceil(inputs/16)] */
+  const float *global_scale;   /* device scalar */
+  const void *bias;            /* [outputs] dtype, may be NULL */
+  void *output;                /* [rows, outputs] dtype */
+  void *stream;                /* cudaStream_t, must not be NULL */
+  int64_t rows;
+  int64_t outputs;
+  int64_t inputs;
+  int32_t dtype; /* NmlSm100DType */
+} NmlSm100Linear;
+
+/* out[r, :] = decode(W[indices[r], :]); an index outside [0, vocabulary) yields a row of
+ * zeros and raises the device status bit NML_SM100_STATUS_INDEX_RANGE.
+ * Field-for-field NmlNvFp4Embedding (nml_nvfp4.h:33-46). */
+typedef struct NmlSm100Embedding {
+  size_t struct_size;
+  const void *indices; /* [rows] i32 or i64 */
+  const uint8_t *payload;
+  const uint8_t *block_scales;
+  const float *global_scale;
+  void *output; /* [rows, width] dtype */
+  void *stream;
+  int64_t rows;
+  int64_t vocabulary;
+  int64_t width;
+  int32_t dtype;
+  uint8_t indices_are_i64;
+} NmlSm100Embedding;
+
+/* activated[a, i] = swiglu(hidden[a / k, :] . W[e, 2i, :] + b[e, 2i],
+ *                          hidden[a / k, :] . W[e, 2i+1, :] + b[e, 2i+1])
+ * for every assignment a listed in the schedule; e = block_experts[slot / 16].
+ * The first 20 fields are NmlNvFp4ExpertGateUp (nml_nvfp4.h:48-69).  The two
+ * trailing pointers are the operands the reference's Triton grouped ABI also
+ * carries (crates/nml-ir/src/nvfp4_backend.rs:633-651); both may be NULL or
+ * absent (struct_size of the reference struct):
+ *   active_blocks  device i32 scalar: blocks at or past it are skipped
+ *   expert_offset  device i32 scalar: payload/scales/bias hold experts
+ *                  [offset, offset + experts); other blocks are skipped. */
+typedef struct NmlSm100ExpertGateUp {
+  size_t struct_size;
+  const void *hidden;                /* [tokens, hidden_size] dtype */
+  const int32_t *sorted_assignments; /* [schedule_positions], sentinel >= assignments */
+  const int32_t *block_experts;      /* [schedule_blocks], -1 = padding block */
+  const uint8_t *payload;            /* [experts, 2*intermediate, ceil(hidden/2)] */
+  const uint8_t *block_scales;       /* [experts, 2*intermediate, ceil(hidden/16)] */
+  const float *global_scale;
+  const void *bias;  /* [experts, 2*intermediate] dtype */
+  void *activated;   /* [assignments, intermediate] dtype */
+  void *stream;
+  int64_t tokens;
+  int64_t assignments;
+  int64_t schedule_positions;
+  int64_t schedule_blocks;
+  int64_t hidden_size;
+  int64_t intermediate_size;
+  int64_t experts;
+  int64_t experts_per_token;
+  int32_t block_size; /* must be 16 */
+  int32_t dtype;
+  const int32_t *active_blocks;
+  const int32_t *expert_offset;
+} NmlSm100ExpertGateUp;
+
+/* weighted[a, h] = (activated[a, :] . W[e, h, :] + b[e, h]) * routing_weights[a].
+ * The first 20 fields are NmlNvFp4ExpertDown (nml_nvfp4.h:71-92). */
+typedef struct NmlSm100ExpertDown {
+  size_t struct_size;
+  const void *activated; /* [assignments, intermediate] dtype */
+  const int32_t *sorted_assignments;
+  const int32_t *block_experts;
+  const uint8_t *payload;      /* [experts, hidden, ceil(intermediate/2)] */
+  const uint8_t *block_scales; /* [experts, hidden, ceil(intermediate/16)] */
+  const float *global_scale;
+  const void *bias;            /* [experts, hidden] dtype */
+  const void *routing_weights; /* [assignments] dtype */
+  void *weighted_output;       /* [assignments, hidden] dtype */
+  void *stream;
+  int64_t assignments;
+  int64_t schedule_positions;
+  int64_t schedule_blocks;
+  int64_t intermediate_size;
+  int64_t hidden_size;
+  int64_t experts;
+  int64_t experts_per_token;
+  int32_t block_size;
+  int32_t dtype;
+  const int32_t *active_blocks;
+  const int32_t *expert_offset;
+} NmlSm100ExpertDown;
+
+/* Top-k routing from f32 router logits: softmax over all experts, top-k by
+ * descending probability with ties to the lower expert index, renormalise by
+ * max(sum, FLT_EPSILON), masked tokens get expert -1 / weight 0, weights
+ * narrowed to dtype.  Replaces the StableHLO subgraph authored by
+ * routed_clamped_swiglu_impl (crates/nml-ir/src/lib.rs:1411-1437, softmax
+ * :4109-4137, top_k :3581-3605). */
+typedef struct NmlSm100Route {
+  size_t struct_size;
+  const float *logits;          /* [tokens, experts] */
+  const uint8_t *active_tokens; /* [tokens] bool, may be NULL (all active) */
+  int32_t *expert_ids;          /* [tokens, experts_per_token] */
+  void *routing_weights;        /* [tokens, experts_per_token] dtype */
+  void *stream;
+  int64_t tokens;
+  int64_t experts;           /* at most 256 */
+  int64_t experts_per_token; /* at most 16 */
+  int32_t dtype;
+} NmlSm100Route;
+
+/* The assignment schedule of moe_assignment_plan (crates/nml-ir/src/lib.rs:5644-5779),
+ * block size 16, same capacity rule:
+ *   schedule_blocks = ceil((A + min(A, E) * 15) / 16), positions = 16 * blocks.
+ * Expert-parallel use: ids are global, this device holds experts
+ * [expert_offset, expert_offset + experts); other ids are left out of the schedule like
+ * masked routes, and block_experts holds local indices (id - expert_offset). */
+typedef struct NmlSm100AssignmentPlan {
+  size_t struct_size;
+  const int32_t *expert_ids;   /* [assignments], -1 = masked */
+  int32_t *sorted_assignments; /* [schedule_positions] */
+  int32_t *block_experts;      /* [schedule_blocks] */
+  int32_t *active_blocks;      /* device scalar */
+  void *stream;
+  int64_t assignments;
+  int64_t experts;             /* at most 1024 */
+  int64_t schedule_positions;
+  int64_t schedule_blocks;
+  int32_t block_size;          /* must be 16 */
+  int32_t expert_offset;
+} NmlSm100AssignmentPlan;
+
+/* out[t, h] = sum over routes r (in route order) of weighted[t * k + r, h], f32
+ * accumulation, one narrowing.  When expert_ids is given, routes whose id is negative or
+ * outside [expert_offset, expert_offset + experts) are skipped (their rows were never
+ * written).
+ * Replaces the reshape + stablehlo.reduce of lower_routed_swiglu
+ * (crates/nml-ir/src/nvfp4_backend.rs:486-508). */
+typedef struct NmlSm100Combine {
+  size_t struct_size;
+  const void *weighted;      /* [tokens * k, hidden] dtype */
+  const int32_t *expert_ids; /* [tokens * k] or NULL (every route contributes) */
+  void *output;              /* [tokens, hidden] dtype */
+  void *stream;
+  int64_t tokens;
+  int64_t experts_per_token;
+  int64_t hidden_size;
+  int64_t experts;           /* used with expert_ids */
+  int32_t expert_offset;     /* used with expert_ids */
+  int32_t dtype;
+} NmlSm100Combine;
+
+/* The whole routed clamped-SwiGLU layer, the unit the reference's CPU target
+ * "nml.nvfp4.routed_swiglu" computes in one call
+ * (crates/nml-kernel-nvfp4/src/ffi.rs:228-428, lib.rs:333-448): plan, gate/up
+ * with the SwiGLU epilogue, down with bias and routing weight, k-way sum.
+ * `workspace` is caller-provided scratch of at least
+ * nml_nvfp4_sm100_routed_swiglu_workspace_bytes(...) bytes, 256-byte aligned. */
+typedef struct NmlSm100RoutedSwiglu {
+  size_t struct_size;
+  const void *hidden;           /* [tokens, hidden_size] dtype */
+  const int32_t *expert_ids;    /* [tokens, k], -1 = masked */
+  const void *routing_weights;  /* [tokens, k] dtype */
+  const uint8_t *gate_payload;  /* [experts, 2I, ceil(H/2)] */
+  const uint8_t *gate_scales;
+  const float *gate_global;
+  const void *gate_bias;        /* [experts, 2I] dtype */
+  const uint8_t *down_payload;  /* [experts, H, ceil(I/2)] */
+  const uint8_t *down_scales;
+  const float *down_global;
+  const void *down_bias;        /* [experts, H] dtype */
+  void *output;                 /* [tokens, hidden_size] dtype */
+  void *workspace;
+  size_t workspace_bytes;
+  void *stream;
+  int64_t tokens;
+  int64_t hidden_size;
+  int64_t intermediate_size;
+  int64_t experts;              /* experts held by payload/scales/bias */
+  int64_t experts_per_token;
+  int32_t expert_offset;        /* first expert id held locally (expert parallel), else 0 */
+  int32_t dtype;
+} NmlSm100RoutedSwiglu;
+
+/* Replaces nml_nvfp4_turing_linear (nml_nvfp4.h:94-96, turing_adapter.cu:669-733). */
+int32_t nml_nvfp4_sm100_linear(const NmlSm100Linear *request, char *error_message,
+                               size_t error_message_capacity);
+
+/* Replaces nml_nvfp4_turing_embedding (nml_nvfp4.h:98-100, turing_adapter.cu:735-783). */
+int32_t nml_nvfp4_sm100_embedding(const NmlSm100Embedding *request, char *error_message,
+                                  size_t error_message_capacity);
+
+/* Replaces nml_nvfp4_turing_expert_gate_up (nml_nvfp4.h:102-104, turing_adapter.cu:785-864)
+ * and the Triton grouped gate/up kernels (crates/nml-kernel-triton/src/nvfp4.rs:1007-1227). */
+int32_t nml_nvfp4_sm100_expert_gate_up(const NmlSm100ExpertGateUp *request, char *error_message,
+                                       size_t error_message_capacity);
+
+/* Replaces nml_nvfp4_turing_expert_down (nml_nvfp4.h:106-108, turing_adapter.cu:866-942)
+ * and the Triton grouped down kernels (crates/nml-kernel-triton/src/nvfp4.rs:1229-1420). */
+int32_t nml_nvfp4_sm100_expert_down(const NmlSm100ExpertDown *request, char *error_message,
+                                    size_t error_message_capacity);
+
+/* Replaces the routing subgraph (crates/nml-ir/src/lib.rs:1411-1437). */
+int32_t nml_nvfp4_sm100_route(const NmlSm100Route *request, char *error_message,
+                              size_t error_message_capacity);
+
+/* Replaces moe_assignment_plan (crates/nml-ir/src/lib.rs:5644-5779). */
+int32_t nml_nvfp4_sm100_assignment_plan(const NmlSm100AssignmentPlan *request,
+                                        char *error_message, size_t error_message_capacity);
+
+/* Replaces the k-way reduce of lower_routed_swiglu (crates/nml-ir/src/nvfp4_backend.rs:486-508). */
+int32_t nml_nvfp4_sm100_combine(const NmlSm100Combine *request, char *error_message,
+                                size_t error_message_capacity);
+
+/* Replaces the CPU target "nml.nvfp4.routed_swiglu" (crates/nml-kernel-nvfp4/src/ffi.rs:228-428). */
+int32_t nml_nvfp4_sm100_routed_swiglu(const NmlSm100RoutedSwiglu *request, char *error_message,
+                                      size_t error_message_capacity);
+
+/* Scratch bytes nml_nvfp4_sm100_routed_swiglu needs for the given extents (0 on overflow). */
+size_t nml_nvfp4_sm100_routed_swiglu_workspace_bytes(int64_t tokens, int64_t hidden_size,
+                                                     int64_t intermediate_size, int64_t experts,
+                                                     int64_t experts_per_token);
+
+/* Schedule capacity of the assignment plan: writes blocks and positions, returns 0,
+ * or 1 when the schedule would not be addressable by int32
+ * (crates/nml-ir/src/lib.rs:5662-5688). */
+int32_t nml_nvfp4_sm100_plan_capacity(int64_t assignments, int64_t experts, int64_t *blocks,
+                                      int64_t *positions);
+
+/* Device status word of the current device: 0 when healthy, else an OR of the bits below.
+ * Kernels never trap; a bounded wait that runs out or an out-of-range index records a
+ * bit here and the kernel returns.  Reading synchronises `stream`; `clear` resets it. */
+#define NML_SM100_STATUS_BARRIER_TIMEOUT 1
+#define NML_SM100_STATUS_TMEM_ALLOC 2
+#define NML_SM100_STATUS_INDEX_RANGE 4
+int32_t nml_nvfp4_sm100_device_status(void *stream, int32_t clear, int32_t *status);
+
+/* Kernel selection override for experiments and tests: 0 = automatic, 1 = force the
+ * portable SIMT kernels, 2 = force the tcgen05 kernels where the shape allows.
+ * Process-wide; returns the previous value. */
+int32_t nml_nvfp4_sm100_set_kernel_policy(int32_t policy);
+
+/* Name of the kernel family the last nml_nvfp4_sm100_linear call on this thread selected
+ * ("umma_swapab", "simt"), for tests and benchmark records. */
+const char *nml_nvfp4_sm100_last_linear_kernel(void);
+
+/* ABI version of this header. */
+#define NML_NVFP4_SM100_ABI_VERSION 1
+int32_t nml_nvfp4_sm100_abi_version(void);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+
+#endif /* NML_NVFP4_SM100_H_ */

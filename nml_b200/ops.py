@@ -1,0 +1,397 @@
+"""Operator API of the NVFP4 path, mirroring the reference's graph operators.
+
+The names and argument meaning follow the reference's ``nml::Graph`` operators
+(crates/nml-ir/src/lib.rs): ``linear`` (:4841), ``linear_qkv`` (:4884),
+``token_embedding`` (:2816), ``routed_clamped_swiglu`` / ``routed_clamped_swiglu_masked``
+(:1257, :1286) over a logical ``Parameter::nvfp4`` (crates/nml-parameter/src/lib.rs:168).
+The shape and dtype checks are those of the reference's operator builders and of its
+custom-call handlers (crates/nml-kernel-nvfp4/src/cuda.rs:216-308 and following); a
+violation raises ``ValueError`` before anything is launched.
+
+Every operator ends in a call through the C ABI declared in
+``include/nml_nvfp4_sm100.h``.  torch supplies device memory and the current stream; no
+operator has a PyTorch or CPU implementation behind it.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from . import _abi
+
+_DTYPE_CODE = {torch.float16: _abi.F16, torch.bfloat16: _abi.BF16}
+
+
+def _code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise ValueError("NVFP4 operations support F16 and BF16 only") from None
+
+
+def _stream(tensor: torch.Tensor) -> int:
+    # The C ABI rejects a null stream like the reference adapter does.  torch's default
+    # stream has handle 0; its explicit, non-null spelling is cudaStreamLegacy (0x1).
+    handle = torch.cuda.current_stream(tensor.device).cuda_stream
+    return handle if handle != 0 else 0x1
+
+
+def _ptr(tensor: torch.Tensor | None) -> int | None:
+    return None if tensor is None else tensor.data_ptr()
+
+
+def _require_cuda(*tensors: torch.Tensor | None) -> None:
+    for tensor in tensors:
+        if tensor is not None and not tensor.is_cuda:
+            raise RuntimeError("NVFP4 operators run on a CUDA device only (no CPU fallback)")
+        if tensor is not None and not tensor.is_contiguous():
+            raise ValueError("NVFP4 operators require row-major contiguous tensors")
+
+
+@dataclass
+class NvFp4Parameter:
+    """One logical NVFP4 weight: the three physical components of recipe v2.
+
+    ``shape`` is the logical shape ``[..., K]``; ``payload`` is u8 ``[..., ceil(K/2)]``,
+    ``block_scales`` u8 ``[..., ceil(K/16)]`` and ``global_scale`` an f32 scalar tensor
+    (crates/nml-parameter/src/lib.rs:163-206).
+    """
+
+    name: str
+    shape: tuple
+    dtype: torch.dtype
+    payload: torch.Tensor
+    block_scales: torch.Tensor
+    global_scale: torch.Tensor
+
+    @staticmethod
+    def nvfp4(name: str, shape, dtype: torch.dtype, payload: torch.Tensor,
+              block_scales: torch.Tensor, global_scale: torch.Tensor) -> "NvFp4Parameter":
+        shape = tuple(int(d) for d in shape)
+        if not shape or shape[-1] <= 0 or any(d <= 0 for d in shape):
+            raise ValueError("invalid NVFP4 logical weight shape")
+        _code(dtype)
+        width = shape[-1]
+        if payload.dtype != torch.uint8 or block_scales.dtype != torch.uint8:
+            raise ValueError("NVFP4 payloads and block scales must use U8 buffers")
+        if tuple(payload.shape) != shape[:-1] + ((width + 1) // 2,):
+            raise ValueError(
+                f"NVFP4 payload extent mismatch: expected {shape[:-1] + ((width + 1) // 2,)}, "
+                f"received {tuple(payload.shape)}")
+        if tuple(block_scales.shape) != shape[:-1] + ((width + 15) // 16,):
+            raise ValueError(
+                f"NVFP4 block-scale extent mismatch: expected "
+                f"{shape[:-1] + ((width + 15) // 16,)}, received {tuple(block_scales.shape)}")
+        if global_scale.dtype != torch.float32 or global_scale.numel() != 1:
+            raise ValueError("NVFP4 global scales must be F32 scalars")
+        return NvFp4Parameter(name, shape, dtype, payload.contiguous(),
+                              block_scales.contiguous(), global_scale.reshape(()).contiguous())
+
+    def slice_rows(self, start: int, stop: int, name: str | None = None) -> "NvFp4Parameter":
+        """Rows [start, stop) of axis 0 (expert or output-column shards); the global scale is
+        shared, block boundaries are untouched (crates/nml-parameter/src/lib.rs:285-312)."""
+        return NvFp4Parameter(name or f"{self.name}[{start}:{stop}]",
+                              (stop - start,) + self.shape[1:], self.dtype,
+                              self.payload[start:stop].contiguous(),
+                              self.block_scales[start:stop].contiguous(), self.global_scale)
+
+
+def linear(input: torch.Tensor, weight: NvFp4Parameter, bias: torch.Tensor | None = None,
+           out: torch.Tensor | None = None) -> torch.Tensor:
+    """``[..., K] x [N, K]^T (+ bias[N])`` with f32 accumulation; result in the input dtype."""
+    if input.dim() == 0:
+        raise ValueError("linear input requires at least one dimension")
+    if len(weight.shape) != 2:
+        raise ValueError("linear requires a rank-2 NVFP4 weight")
+    outputs, inputs = weight.shape
+    dtype = _code(input.dtype)
+    if input.dtype != weight.dtype:
+        raise ValueError("NVFP4 linear dtypes are inconsistent")
+    if input.shape[-1] != inputs:
+        raise ValueError(
+            f"linear input extent {input.shape[-1]} does not match rows of {inputs} values")
+    if bias is not None and (tuple(bias.shape) != (outputs,) or bias.dtype != input.dtype):
+        raise ValueError("NVFP4 linear bias must be a length-N activation vector")
+    rows = input.numel() // inputs
+    if rows <= 0:
+        raise ValueError("NVFP4 linear row extent must be positive")
+    _require_cuda(input, weight.payload, weight.block_scales, weight.global_scale, bias)
+    result_shape = tuple(input.shape[:-1]) + (outputs,)
+    if out is None:
+        out = torch.empty(result_shape, dtype=input.dtype, device=input.device)
+    elif tuple(out.shape) != result_shape or out.dtype != input.dtype:
+        raise ValueError("NVFP4 linear component and output shapes are inconsistent")
+    request = _abi.Linear(activation=_ptr(input), payload=_ptr(weight.payload),
+                          block_scales=_ptr(weight.block_scales),
+                          global_scale=_ptr(weight.global_scale), bias=_ptr(bias),
+                          output=_ptr(out), stream=_stream(input), rows=rows, outputs=outputs,
+                          inputs=inputs, dtype=dtype)
+    _abi.call("nml_nvfp4_sm100_linear", request)
+    return out
+
+
+def linear_qkv(input: torch.Tensor, query_weight: NvFp4Parameter, query_bias,
+               key_weight: NvFp4Parameter, key_bias, value_weight: NvFp4Parameter, value_bias):
+    """Three projections over one activation (crates/nml-ir/src/lib.rs:4884-4928)."""
+    return (linear(input, query_weight, query_bias), linear(input, key_weight, key_bias),
+            linear(input, value_weight, value_bias))
+
+
+def token_embedding(weight: NvFp4Parameter, indices: torch.Tensor,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+    """Decodes rows ``indices`` of a ``[vocabulary, width]`` table; result ``indices.shape +
+    [width]`` in the table's logical dtype."""
+    if len(weight.shape) != 2:
+        raise ValueError("embedding requires a rank-2 NVFP4 weight")
+    if indices.dtype not in (torch.int32, torch.int64):
+        raise ValueError("NVFP4 embedding supports I32 and I64 indices")
+    vocabulary, width = weight.shape
+    rows = indices.numel()
+    if rows <= 0:
+        raise ValueError("NVFP4 embedding row extent must be positive")
+    _require_cuda(indices, weight.payload, weight.block_scales, weight.global_scale)
+    result_shape = tuple(indices.shape) + (width,)
+    if out is None:
+        out = torch.empty(result_shape, dtype=weight.dtype, device=indices.device)
+    elif tuple(out.shape) != result_shape or out.dtype != weight.dtype:
+        raise ValueError("NVFP4 embedding output shape is inconsistent")
+    request = _abi.Embedding(indices=_ptr(indices), payload=_ptr(weight.payload),
+                             block_scales=_ptr(weight.block_scales),
+                             global_scale=_ptr(weight.global_scale), output=_ptr(out),
+                             stream=_stream(indices), rows=rows, vocabulary=vocabulary,
+                             width=width, dtype=_code(weight.dtype),
+                             indices_are_i64=1 if indices.dtype == torch.int64 else 0)
+    _abi.call("nml_nvfp4_sm100_embedding", request)
+    return out
+
+
+# ------------------------------------------------------------------ routed experts
+
+def route(router_logits: torch.Tensor, experts_per_token: int, dtype: torch.dtype,
+          active_tokens: torch.Tensor | None = None):
+    """Top-k routing: returns ``(expert_ids i32 [T, k], routing_weights dtype [T, k])``.
+
+    Softmax over all experts in f32, top-k by descending probability with ties to the lower
+    expert index, renormalised; masked tokens get expert -1 and weight 0
+    (crates/nml-ir/src/lib.rs:1411-1437)."""
+    if router_logits.dim() != 2 or router_logits.dtype != torch.float32:
+        raise ValueError("router logits must be F32 [tokens, experts]")
+    tokens, experts = router_logits.shape
+    if experts_per_token <= 0 or experts_per_token > experts:
+        raise ValueError("experts per token must be positive and not exceed the expert count")
+    if active_tokens is not None and (active_tokens.dtype != torch.bool or
+                                      tuple(active_tokens.shape) != (tokens,)):
+        raise ValueError("active MoE token mask must be Bool [tokens]")
+    _require_cuda(router_logits, active_tokens)
+    ids = torch.empty((tokens, experts_per_token), dtype=torch.int32, device=router_logits.device)
+    weights = torch.empty((tokens, experts_per_token), dtype=dtype, device=router_logits.device)
+    request = _abi.Route(logits=_ptr(router_logits), active_tokens=_ptr(active_tokens),
+                         expert_ids=_ptr(ids), routing_weights=_ptr(weights),
+                         stream=_stream(router_logits), tokens=tokens, experts=experts,
+                         experts_per_token=experts_per_token, dtype=_code(dtype))
+    _abi.call("nml_nvfp4_sm100_route", request)
+    return ids, weights
+
+
+@dataclass
+class AssignmentPlan:
+    """The schedule of crates/nml-ir/src/lib.rs:5644-5779 (device tensors)."""
+
+    sorted_assignments: torch.Tensor  # i32 [positions]
+    block_experts: torch.Tensor       # i32 [blocks]
+    active_blocks: torch.Tensor       # i32 scalar
+    block_size: int = 16
+
+
+def moe_assignment_plan(expert_ids: torch.Tensor, experts: int,
+                        expert_offset: int = 0) -> AssignmentPlan:
+    if expert_ids.dtype != torch.int32:
+        raise ValueError("expert ids must be I32")
+    assignments = expert_ids.numel()
+    try:
+        blocks, positions = _abi.plan_capacity(assignments, experts)
+    except _abi.NvFp4Error as error:
+        raise ValueError(error.message) from None
+    _require_cuda(expert_ids)
+    device = expert_ids.device
+    plan = AssignmentPlan(torch.empty(positions, dtype=torch.int32, device=device),
+                          torch.empty(blocks, dtype=torch.int32, device=device),
+                          torch.empty((), dtype=torch.int32, device=device))
+    request = _abi.AssignmentPlan(expert_ids=_ptr(expert_ids),
+                                  sorted_assignments=_ptr(plan.sorted_assignments),
+                                  block_experts=_ptr(plan.block_experts),
+                                  active_blocks=_ptr(plan.active_blocks),
+                                  stream=_stream(expert_ids), assignments=assignments,
+                                  experts=experts, schedule_positions=positions,
+                                  schedule_blocks=blocks, block_size=16,
+                                  expert_offset=expert_offset)
+    _abi.call("nml_nvfp4_sm100_assignment_plan", request)
+    return plan
+
+
+def _check_experts(hidden_size, gate_up: NvFp4Parameter, gate_up_bias, down: NvFp4Parameter,
+                   down_bias, dtype):
+    if len(gate_up.shape) != 3 or len(down.shape) != 3 or gate_up_bias.dim() != 2 or \
+            down_bias.dim() != 2:
+        raise ValueError(
+            "clamped SwiGLU expects hidden [tokens, hidden], router [tokens, experts], gate/up "
+            "[experts, 2*intermediate, hidden], gate/up bias [experts, 2*intermediate], down "
+            "[experts, hidden, intermediate], and down bias [experts, hidden]")
+    experts, doubled, gate_inputs = gate_up.shape
+    if doubled <= 0 or doubled % 2 != 0 or gate_inputs != hidden_size or \
+            down.shape != (experts, hidden_size, doubled // 2) or \
+            tuple(gate_up_bias.shape) != (experts, doubled) or \
+            tuple(down_bias.shape) != (experts, hidden_size):
+        raise ValueError("clamped SwiGLU expert parameter dimensions are inconsistent")
+    for tensor_dtype in (gate_up.dtype, down.dtype, gate_up_bias.dtype, down_bias.dtype):
+        if tensor_dtype != dtype:
+            raise ValueError(
+                "clamped SwiGLU weights, biases, and hidden states must use one dtype")
+    return experts, doubled // 2
+
+
+def expert_gate_up(hidden: torch.Tensor, plan: AssignmentPlan, gate_up: NvFp4Parameter,
+                   gate_up_bias: torch.Tensor, experts_per_token: int,
+                   expert_offset: torch.Tensor | None = None,
+                   use_active_blocks: bool = True) -> torch.Tensor:
+    """activated ``[tokens * k, intermediate]``; rows of unscheduled routes are not written."""
+    tokens, hidden_size = hidden.shape
+    experts, doubled, _ = gate_up.shape
+    intermediate = doubled // 2
+    assignments = tokens * experts_per_token
+    _require_cuda(hidden, gate_up.payload, gate_up_bias)
+    activated = torch.zeros((assignments, intermediate), dtype=hidden.dtype, device=hidden.device)
+    request = _abi.ExpertGateUp(
+        hidden=_ptr(hidden), sorted_assignments=_ptr(plan.sorted_assignments),
+        block_experts=_ptr(plan.block_experts), payload=_ptr(gate_up.payload),
+        block_scales=_ptr(gate_up.block_scales), global_scale=_ptr(gate_up.global_scale),
+        bias=_ptr(gate_up_bias), activated=_ptr(activated), stream=_stream(hidden),
+        tokens=tokens, assignments=assignments,
+        schedule_positions=plan.sorted_assignments.numel(),
+        schedule_blocks=plan.block_experts.numel(), hidden_size=hidden_size,
+        intermediate_size=intermediate, experts=experts, experts_per_token=experts_per_token,
+        block_size=16, dtype=_code(hidden.dtype),
+        active_blocks=_ptr(plan.active_blocks) if use_active_blocks else None,
+        expert_offset=_ptr(expert_offset))
+    _abi.call("nml_nvfp4_sm100_expert_gate_up", request)
+    return activated
+
+
+def expert_down(activated: torch.Tensor, plan: AssignmentPlan, down: NvFp4Parameter,
+                down_bias: torch.Tensor, routing_weights: torch.Tensor, experts_per_token: int,
+                expert_offset: torch.Tensor | None = None,
+                use_active_blocks: bool = True) -> torch.Tensor:
+    """weighted ``[tokens * k, hidden]`` = (activated . W_down^T + bias) * routing weight."""
+    assignments, intermediate = activated.shape
+    experts, hidden_size, _ = down.shape
+    _require_cuda(activated, down.payload, down_bias, routing_weights)
+    weighted = torch.zeros((assignments, hidden_size), dtype=activated.dtype,
+                           device=activated.device)
+    request = _abi.ExpertDown(
+        activated=_ptr(activated), sorted_assignments=_ptr(plan.sorted_assignments),
+        block_experts=_ptr(plan.block_experts), payload=_ptr(down.payload),
+        block_scales=_ptr(down.block_scales), global_scale=_ptr(down.global_scale),
+        bias=_ptr(down_bias), routing_weights=_ptr(routing_weights),
+        weighted_output=_ptr(weighted), stream=_stream(activated), assignments=assignments,
+        schedule_positions=plan.sorted_assignments.numel(),
+        schedule_blocks=plan.block_experts.numel(), intermediate_size=intermediate,
+        hidden_size=hidden_size, experts=experts, experts_per_token=experts_per_token,
+        block_size=16, dtype=_code(activated.dtype),
+        active_blocks=_ptr(plan.active_blocks) if use_active_blocks else None,
+        expert_offset=_ptr(expert_offset))
+    _abi.call("nml_nvfp4_sm100_expert_down", request)
+    return weighted
+
+
+def combine(weighted: torch.Tensor, tokens: int, experts_per_token: int,
+            expert_ids: torch.Tensor | None = None, experts: int = 0,
+            expert_offset: int = 0) -> torch.Tensor:
+    """Sums the k weighted rows of every token in f32 and narrows once."""
+    hidden_size = weighted.shape[-1]
+    _require_cuda(weighted, expert_ids)
+    out = torch.empty((tokens, hidden_size), dtype=weighted.dtype, device=weighted.device)
+    request = _abi.Combine(weighted=_ptr(weighted), expert_ids=_ptr(expert_ids),
+                           output=_ptr(out), stream=_stream(weighted), tokens=tokens,
+                           experts_per_token=experts_per_token, hidden_size=hidden_size,
+                           experts=experts, expert_offset=expert_offset,
+                           dtype=_code(weighted.dtype))
+    _abi.call("nml_nvfp4_sm100_combine", request)
+    return out
+
+
+_WORKSPACES: dict = {}
+
+
+def routed_experts(hidden: torch.Tensor, expert_ids: torch.Tensor,
+                   routing_weights: torch.Tensor, gate_up: NvFp4Parameter,
+                   gate_up_bias: torch.Tensor, down: NvFp4Parameter, down_bias: torch.Tensor,
+                   expert_offset: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """The routed layer from given routes, one C-ABI call (plan, gate/up + SwiGLU, down,
+    k-way sum); the unit of the reference's CPU target ``nml.nvfp4.routed_swiglu``
+    (crates/nml-kernel-nvfp4/src/ffi.rs:228-428)."""
+    if hidden.dim() != 2 or expert_ids.dim() != 2 or \
+            tuple(routing_weights.shape) != tuple(expert_ids.shape) or \
+            expert_ids.shape[0] != hidden.shape[0]:
+        raise ValueError("routing tensors do not match the token and hidden extents")
+    tokens, hidden_size = hidden.shape
+    top_k = expert_ids.shape[1]
+    experts, intermediate = _check_experts(hidden_size, gate_up, gate_up_bias, down, down_bias,
+                                           hidden.dtype)
+    if expert_ids.dtype != torch.int32 or routing_weights.dtype != hidden.dtype:
+        raise ValueError("NVFP4 routed SwiGLU activations and biases must share F16 or BF16")
+    _require_cuda(hidden, expert_ids, routing_weights, gate_up.payload, gate_up_bias,
+                  down.payload, down_bias)
+    size = _abi.load().nml_nvfp4_sm100_routed_swiglu_workspace_bytes(
+        tokens, hidden_size, intermediate, experts, top_k)
+    if size == 0:
+        raise ValueError("MoE routing schedule must be addressable by i32 indices")
+    key = (hidden.device, torch.cuda.current_stream(hidden.device).cuda_stream)
+    workspace = _WORKSPACES.get(key)
+    if workspace is None or workspace.numel() < size:
+        workspace = torch.empty(size, dtype=torch.uint8, device=hidden.device)
+        _WORKSPACES[key] = workspace
+    if out is None:
+        out = torch.empty_like(hidden)
+    request = _abi.RoutedSwiglu(
+        hidden=_ptr(hidden), expert_ids=_ptr(expert_ids), routing_weights=_ptr(routing_weights),
+        gate_payload=_ptr(gate_up.payload), gate_scales=_ptr(gate_up.block_scales),
+        gate_global=_ptr(gate_up.global_scale), gate_bias=_ptr(gate_up_bias),
+        down_payload=_ptr(down.payload), down_scales=_ptr(down.block_scales),
+        down_global=_ptr(down.global_scale), down_bias=_ptr(down_bias), output=_ptr(out),
+        workspace=_ptr(workspace), workspace_bytes=workspace.numel(), stream=_stream(hidden),
+        tokens=tokens, hidden_size=hidden_size, intermediate_size=intermediate, experts=experts,
+        experts_per_token=top_k, expert_offset=expert_offset, dtype=_code(hidden.dtype))
+    _abi.call("nml_nvfp4_sm100_routed_swiglu", request)
+    return out
+
+
+def routed_clamped_swiglu(hidden: torch.Tensor, router_logits: torch.Tensor,
+                          gate_up_weights: NvFp4Parameter, gate_up_bias: torch.Tensor,
+                          down_weights: NvFp4Parameter, down_bias: torch.Tensor,
+                          experts_per_token: int) -> torch.Tensor:
+    """Routed clamped residual SwiGLU (crates/nml-ir/src/lib.rs:1257-1277)."""
+    return routed_clamped_swiglu_masked(hidden, router_logits, gate_up_weights, gate_up_bias,
+                                        down_weights, down_bias, experts_per_token, None)
+
+
+def routed_clamped_swiglu_masked(hidden: torch.Tensor, router_logits: torch.Tensor,
+                                 gate_up_weights: NvFp4Parameter, gate_up_bias: torch.Tensor,
+                                 down_weights: NvFp4Parameter, down_bias: torch.Tensor,
+                                 experts_per_token: int,
+                                 active_tokens: torch.Tensor | None) -> torch.Tensor:
+    """As ``routed_clamped_swiglu`` with a runtime active-token mask: masked tokens create no
+    expert work and return an exact zero row (crates/nml-ir/src/lib.rs:1279-1308,1490-1498)."""
+    if hidden.dim() != 2 or router_logits.dim() != 2:
+        raise ValueError(
+            "clamped SwiGLU expects hidden [tokens, hidden], router [tokens, experts], gate/up "
+            "[experts, 2*intermediate, hidden], gate/up bias [experts, 2*intermediate], down "
+            "[experts, hidden, intermediate], and down bias [experts, hidden]")
+    experts, _ = _check_experts(hidden.shape[1], gate_up_weights, gate_up_bias, down_weights,
+                                down_bias, hidden.dtype)
+    if router_logits.shape[0] != hidden.shape[0] or router_logits.shape[1] != experts:
+        raise ValueError("clamped SwiGLU expert parameter dimensions are inconsistent")
+    ids, weights = route(router_logits, experts_per_token, hidden.dtype, active_tokens)
+    return routed_experts(hidden, ids, weights, gate_up_weights, gate_up_bias, down_weights,
+                          down_bias)

@@ -1,0 +1,130 @@
+"""NVFP4 linear through the C ABI against the oracle's f32-accumulated output.
+
+Bar for every case: max relative error <= 2e-2 and mean relative error <= 2e-3 (see
+gpu_util.assert_gemm_close for the exact definition)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from helpers import make_activation, make_weight, rng
+
+pytestmark = pytest.mark.gpu
+
+
+def run_linear(M, K, N, dtype, policy, with_bias=False, seed=0, sample_rows=None,
+               expect_kernel=None):
+    from nml_b200 import ops, _abi
+    import gpu_util as gu
+    triple = make_weight(100 + seed, (N, K))
+    weight = gu.parameter("w", triple, K, dtype)
+    x_bits, x32 = make_activation(200 + seed, (M, K), dtype=dtype)
+    bias_bits = bias32 = None
+    if with_bias:
+        bias_bits, bias32 = make_activation(300 + seed, (N,), std=0.5, dtype=dtype)
+    x = gu.to_device_bits(x_bits, dtype)
+    bias = None if bias_bits is None else gu.to_device_bits(bias_bits, dtype)
+    previous = _abi.set_kernel_policy(policy)
+    try:
+        y = ops.linear(x, weight, bias)
+        torch.cuda.synchronize()
+        kernel = _abi.last_linear_kernel()
+    finally:
+        _abi.set_kernel_policy(previous)
+    assert _abi.device_status(0x1) == 0
+    if expect_kernel is not None:
+        assert kernel.startswith(expect_kernel), kernel
+    rows = np.arange(M) if sample_rows is None or sample_rows >= M else np.sort(
+        rng(seed).choice(M, sample_rows, replace=False))
+    expected = oracle.linear(x32[rows], *triple, bias32)
+    actual = gu.device_f32(y)[rows]
+    return gu.assert_gemm_close(actual, expected, f"M={M} K={K} N={N} policy={policy}")
+
+
+@pytest.mark.parametrize("dtype", [oracle.BF16, oracle.F16])
+@pytest.mark.parametrize("M,K,N,bias", [(1, 16, 5, True), (3, 16, 5, False), (3, 16, 5, True),
+                                        (2, 17, 4, True), (17, 80, 33, False), (1, 17, 5, False),
+                                        (3, 33, 4, True), (1, 2880, 64, False)])
+def test_portable_kernel_odd_shapes(dtype, M, K, N, bias):
+    # shapes of crates/nml-kernel-nvfp4/tests/cpu_contract.rs:106-129 and
+    # crates/nml/tests/nvfp4_contract.rs:48-117, plus odd extents
+    from nml_b200 import _abi
+    run_linear(M, K, N, dtype, _abi.POLICY_SIMT, bias, seed=M + K + N, expect_kernel="simt")
+
+
+def test_contract_linear_closed_form_inputs():
+    # crates/nml/tests/nvfp4_contract.rs:48-117, tolerance of :528-531
+    from nml_b200 import ops
+    import gpu_util as gu
+    K, N = 16, 5
+    source = ((np.float32(27.0) - np.arange(N * K, dtype=np.float32)) / np.float32(17.0)).reshape(
+        N, K)
+    triple = oracle.quantize_tensor(source)
+    decoded = oracle.dequantize_tensor(*triple, K)
+    bias = np.array([-0.5, -0.125, 0.0, 0.25, 0.75], np.float32)
+    for dtype, t in ((oracle.F16, 1e-2), (oracle.BF16, 6e-2)):
+        for rows, with_bias in ((3, False), (3, True), (1, True)):
+            x = ((np.arange(rows * K, dtype=np.float32) - np.float32(19.0)) /
+                 np.float32(13.0)).reshape(rows, K)
+            weight = gu.parameter("w", triple, K, dtype)
+            y = ops.linear(gu.to_device_bits(oracle.from_f32(x, dtype), dtype), weight,
+                           gu.to_device_bits(oracle.from_f32(bias, dtype), dtype)
+                           if with_bias else None)
+            expected = x @ decoded.T + (bias if with_bias else 0.0)
+            assert (np.abs(gu.device_f32(y) - expected) <= t + t * np.abs(expected)).all()
+
+
+UMMA_CASES = [(1, 64, 128), (16, 128, 128), (17, 256, 200), (64, 2880, 2880), (100, 2880, 640),
+              (130, 512, 384), (300, 1024, 256), (1, 2880, 5760)]
+
+
+@pytest.mark.parametrize("M,K,N", UMMA_CASES)
+def test_tensor_core_kernel_f16_activations(M, K, N):
+    from nml_b200 import _abi
+    run_linear(M, K, N, oracle.F16, _abi.POLICY_UMMA, with_bias=(M % 2 == 0), seed=M + N,
+               expect_kernel="umma_swapab_af16")
+
+
+@pytest.mark.parametrize("M,K,N", UMMA_CASES)
+def test_tensor_core_kernel_bf16_operand_decode(M, K, N):
+    from nml_b200 import _abi
+    run_linear(M, K, N, oracle.BF16, _abi.POLICY_UMMA_BF16_OPERAND, with_bias=(M % 2 == 1),
+               seed=M + N, expect_kernel="umma_swapab_abf16")
+
+
+@pytest.mark.parametrize("M,K,N", UMMA_CASES)
+def test_tensor_core_kernel_bf16_activations_default_decode(M, K, N):
+    from nml_b200 import _abi
+    run_linear(M, K, N, oracle.BF16, _abi.POLICY_UMMA, with_bias=(M % 2 == 0), seed=M + N,
+               expect_kernel="umma_swapab")
+
+
+CONFIG_SHAPES = [(2880, 5120), (4096, 2880), (2880, 5760), (2880, 2880)]
+
+
+@pytest.mark.parametrize("K,N", CONFIG_SHAPES)
+@pytest.mark.parametrize("M", [1, 16, 64])
+def test_config_shapes_small_m_full_oracle(K, N, M):
+    from nml_b200 import _abi
+    run_linear(M, K, N, oracle.BF16, _abi.POLICY_AUTO, seed=K + N + M, expect_kernel="umma")
+
+
+@pytest.mark.parametrize("K,N", CONFIG_SHAPES)
+@pytest.mark.parametrize("M", [512, 4096, 16384])
+def test_config_shapes_large_m_sampled_rows(K, N, M):
+    from nml_b200 import _abi
+    run_linear(M, K, N, oracle.BF16, _abi.POLICY_AUTO, seed=K + N + M, sample_rows=24,
+               expect_kernel="umma")
+
+
+@pytest.mark.parametrize("M", [1, 16, 1024])
+def test_unembedding_shape(M):
+    from nml_b200 import _abi
+    run_linear(M, 2880, 201088, oracle.BF16, _abi.POLICY_AUTO, seed=M, sample_rows=4,
+               expect_kernel="umma")
+
+
+def test_config0_single_linear():
+    # BASELINE config 0: X bf16 [16, 2880], W [5760, 2880]
+    from nml_b200 import _abi
+    run_linear(16, 2880, 5760, oracle.BF16, _abi.POLICY_AUTO, seed=7)

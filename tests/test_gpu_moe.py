@@ -1,0 +1,165 @@
+"""Routing, assignment plan and routed experts through the C ABI against the oracle.
+
+Routing ids, routing weights and the plan are integer/selection work: bit-exact.  The two
+expert projections are GEMM outputs: the 2e-2 / 2e-3 relative-error bar against the oracle's
+f32-accumulated result computed from the same inputs."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from helpers import Lcg, make_activation, make_weight, rng
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("tokens,experts,k,dtype", [(4096, 32, 4, oracle.BF16),
+                                                   (64, 32, 4, oracle.BF16),
+                                                   (7, 3, 2, oracle.F16), (33, 128, 8, oracle.BF16),
+                                                   (5, 200, 16, oracle.F16), (1, 32, 4, oracle.BF16)])
+def test_route_ids_and_weights_bit_exact(tokens, experts, k, dtype):
+    from nml_b200 import ops
+    import gpu_util as gu
+    logits = (rng(tokens + experts).standard_normal((tokens, experts)) * 0.6).astype(np.float32)
+    ids, w = ops.route(torch.from_numpy(logits).cuda(), k, gu.TORCH_DTYPE[dtype])
+    e_ids, _, e_w16 = oracle.route(logits, k, dtype)
+    assert np.array_equal(ids.cpu().numpy(), e_ids)
+    assert np.array_equal(gu.from_device_bits(w), e_w16)
+
+
+def test_route_ties_masks_and_degenerate_rows():
+    from nml_b200 import ops
+    import gpu_util as gu
+    logits = np.zeros((6, 32), np.float32)
+    logits[1, [5, 2]] = 1.0
+    logits[2, :] = -np.inf
+    logits[3] = np.round(rng(1).standard_normal(32) * 2) / 2  # many exact ties
+    logits[4, :] = 80.0
+    logits[4, 7] = -80.0
+    logits[5] = rng(2).standard_normal(32).astype(np.float32) * 1e-7  # ties after exp rounding
+    active = np.array([1, 1, 1, 1, 0, 1], np.uint8)
+    for mask in (None, active):
+        ids, w = ops.route(torch.from_numpy(logits).cuda(), 4, torch.bfloat16,
+                           None if mask is None else torch.from_numpy(mask).bool().cuda())
+        e_ids, _, e_w16 = oracle.route(logits, 4, oracle.BF16, active=mask)
+        assert np.array_equal(ids.cpu().numpy(), e_ids)
+        assert np.array_equal(gu.from_device_bits(w), e_w16)
+    assert ids.cpu().numpy()[0].tolist() == [0, 1, 2, 3]
+    assert (ids.cpu().numpy()[4] == -1).all()
+
+
+@pytest.mark.parametrize("A,E,seed", [(8, 32, 1), (32, 32, 2), (33, 32, 3), (256, 32, 4),
+                                      (1000, 7, 5), (16384, 32, 6), (40, 4, 7), (5000, 256, 8),
+                                      (70000, 32, 9)])
+def test_assignment_plan_bit_exact(A, E, seed):
+    from nml_b200 import ops
+    r = rng(seed)
+    ids = r.integers(0, E, A).astype(np.int32)
+    if seed % 2 == 0:
+        ids[r.integers(0, A, max(1, A // 7))] = -1
+    if E > 3:
+        ids[ids == 1] = 0
+    plan = ops.moe_assignment_plan(torch.from_numpy(ids).cuda(), E)
+    s, b, active = oracle.assignment_plan(ids, E, 16)
+    assert int(plan.active_blocks.item()) == active
+    assert np.array_equal(plan.sorted_assignments.cpu().numpy(), s)
+    assert np.array_equal(plan.block_experts.cpu().numpy(), b)
+
+
+def test_assignment_plan_expert_parallel_slice():
+    # ids outside [offset, offset + local) are left out like masked routes
+    from nml_b200 import ops
+    ids = rng(3).integers(0, 32, 2000).astype(np.int32)
+    offset, local = 8, 8
+    plan = ops.moe_assignment_plan(torch.from_numpy(ids).cuda(), local, expert_offset=offset)
+    shifted = np.where((ids >= offset) & (ids < offset + local), ids - offset, -1).astype(np.int32)
+    s, b, active = oracle.assignment_plan(shifted, local, 16)
+    assert int(plan.active_blocks.item()) == active
+    assert np.array_equal(plan.sorted_assignments.cpu().numpy(), s)
+    assert np.array_equal(plan.block_experts.cpu().numpy(), b)
+
+
+def make_experts(seed, E, H, I, dtype, std=0.02, bias_std=0.02):
+    gate = make_weight(seed, (E, 2 * I, H), std)
+    down = make_weight(seed + 1, (E, H, I), std)
+    gb_bits, gb = make_activation(seed + 2, (E, 2 * I), bias_std, dtype)
+    db_bits, db = make_activation(seed + 3, (E, H), bias_std, dtype)
+    return gate, down, (gb_bits, gb), (db_bits, db)
+
+
+def run_routed(tokens, H, E, I, k, dtype, policy, seed=0, std=0.02, mask=None):
+    from nml_b200 import ops, _abi
+    import gpu_util as gu
+    gate, down, (gb_bits, gb), (db_bits, db) = make_experts(seed, E, H, I, dtype, std)
+    x_bits, x = make_activation(seed + 9, (tokens, H), 1.0, dtype)
+    logits = (rng(seed + 10).standard_normal((tokens, E)) * 0.6).astype(np.float32)
+    ids, w32, w16 = oracle.route(logits, k, dtype, active=mask)
+    w = oracle.to_f32(w16, dtype)
+    gate_p = gu.parameter("gate_up", gate, H, dtype)
+    down_p = gu.parameter("down", down, I, dtype)
+    d_x = gu.to_device_bits(x_bits, dtype)
+    d_gb = gu.to_device_bits(gb_bits, dtype)
+    d_db = gu.to_device_bits(db_bits, dtype)
+    d_ids = torch.from_numpy(ids).cuda()
+    d_w = gu.to_device_bits(w16, dtype)
+    previous = _abi.set_kernel_policy(policy)
+    try:
+        plan = ops.moe_assignment_plan(d_ids.reshape(-1), E)
+        activated = ops.expert_gate_up(d_x, plan, gate_p, d_gb, k)
+        weighted = ops.expert_down(activated, plan, down_p, d_db, d_w.reshape(-1), k)
+        combined = ops.combine(weighted, tokens, k, d_ids.reshape(-1), E, 0)
+        fused = ops.routed_experts(d_x, d_ids, d_w, gate_p, d_gb, down_p, d_db)
+        end_to_end = ops.routed_clamped_swiglu_masked(
+            d_x, torch.from_numpy(logits).cuda(), gate_p, d_gb, down_p, d_db, k,
+            None if mask is None else torch.from_numpy(np.asarray(mask, np.uint8)).bool().cuda())
+        torch.cuda.synchronize()
+    finally:
+        _abi.set_kernel_policy(previous)
+    assert _abi.device_status(0x1) == 0
+    valid = ids.ravel() >= 0
+    # stage 1: gate/up + SwiGLU from the same hidden rows
+    e_act = oracle.expert_gate_up(x, ids.ravel(), k, gate, gb)
+    gu.assert_gemm_close(gu.device_f32(activated)[valid], e_act[valid], "gate_up")
+    # stage 2: down from the device's own (narrowed) activations
+    act_in = gu.device_f32(activated)
+    e_weighted = oracle.expert_down(act_in, ids.ravel(), w.ravel(), down, db)
+    gu.assert_gemm_close(gu.device_f32(weighted)[valid], e_weighted[valid], "down")
+    # stage 3: the k-way sum is f32 with one narrowing: bit-exact against the oracle
+    w_bits = gu.from_device_bits(weighted).copy()
+    w_bits[~valid] = 0
+    assert np.array_equal(gu.from_device_bits(combined),
+                          oracle.combine(w_bits, tokens, k, dtype, mode=0))
+    assert np.array_equal(gu.from_device_bits(fused), gu.from_device_bits(combined))
+    assert np.array_equal(gu.from_device_bits(end_to_end), gu.from_device_bits(combined))
+    # whole layer against the reference CPU semantics (f32 activations between the
+    # projections): the reference's own mixed tolerance, crates/nml/tests/nvfp4_contract.rs:510-534
+    safe_ids = np.where(ids < 0, 0, ids)
+    e_layer = oracle.routed_clamped_swiglu(x, safe_ids, np.where(ids < 0, 0, w), gate, gb, down,
+                                           db)
+    t = 1e-2 if dtype == oracle.F16 else 6e-2
+    assert (np.abs(gu.device_f32(fused) - e_layer) <= t + t * np.abs(e_layer)).all()
+    return oracle.error_metrics(gu.device_f32(fused), e_layer)
+
+
+@pytest.mark.parametrize("tokens,H,E,I,k", [(1, 3, 4, 5, 2), (3, 5, 6, 7, 2), (4, 3, 7, 3, 3),
+                                            (2, 4, 3, 5, 2), (1, 4, 3, 5, 2), (40, 48, 4, 24, 2)])
+@pytest.mark.parametrize("dtype", [oracle.BF16, oracle.F16])
+def test_routed_experts_small_shapes_portable_kernel(tokens, H, E, I, k, dtype):
+    # shapes of crates/nml-kernel-nvfp4/tests/cpu_contract.rs:236-238 and
+    # crates/nml/tests/nvfp4_contract.rs:180-184
+    from nml_b200 import _abi
+    run_routed(tokens, H, E, I, k, dtype, _abi.POLICY_SIMT, seed=tokens + H + E, std=1.0)
+
+
+def test_routed_experts_masked_tokens_and_empty_experts():
+    from nml_b200 import _abi
+    mask = np.ones(40, np.uint8)
+    mask[[0, 7, 39]] = 0
+    run_routed(40, 64, 6, 32, 2, oracle.BF16, _abi.POLICY_SIMT, seed=5, mask=mask)
+
+
+@pytest.mark.parametrize("tokens", [1, 2, 16, 64, 300])
+def test_routed_experts_gpt_oss_width(tokens):
+    # hidden 2880, intermediate 2880, top-4; 8 experts keep the CPU oracle fast
+    from nml_b200 import _abi
+    run_routed(tokens, 2880, 8, 2880, 4, oracle.BF16, _abi.POLICY_AUTO, seed=tokens)
