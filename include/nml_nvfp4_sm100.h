@@ -291,7 +291,7 @@ int32_t nml_nvfp4_sm100_device_status(void *stream, int32_t clear, int32_t *stat
 int32_t nml_nvfp4_sm100_set_kernel_policy(int32_t policy);
 
 /* Name of the kernel family the last nml_nvfp4_sm100_linear call on this thread selected
- * ("umma_swapab", "simt"), for tests and benchmark records. */
+ * ("umma_swapab_af16", "umma_swapab_abf16", "simt"), for tests and benchmark records. */
 const char *nml_nvfp4_sm100_last_linear_kernel(void);
 
 /* ABI version of this header. */

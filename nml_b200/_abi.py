@@ -25,7 +25,6 @@ STATUS_INDEX_RANGE = 4
 POLICY_AUTO = 0
 POLICY_SIMT = 1
 POLICY_UMMA = 2
-POLICY_UMMA_BF16_OPERAND = 3
 
 _vp = ctypes.c_void_p
 _i64 = ctypes.c_int64

@@ -23,13 +23,17 @@
 // exact in f16 and in bf16: the only rounding left is the f32 accumulation order.  The f32
 // global scale is applied in the epilogue.
 //
-// Operand-format variants of the decode (kAf16 / kAbf16), both exact:
-//   kAf16   W' in f16 by the hardware converts cvt.rn.f16x2.e2m1x2 / .e4m3x2 and one
-//           half2 multiply.  With bf16 activations this issues the MMA with A = f16 and
-//           B = bf16, which the kind::f16 instruction descriptor expresses independently.
-//   kAbf16  W' in bf16 by bit placement: the code's magnitude bits at bf16 bits 8:6 read as
-//           value * 2^-126 (0.5 is the bf16 subnormal); one bf16x2 multiply by
-//           scale * 2^119 gives value * scale * 2^-7, and the epilogue multiplies by g * 128.
+// Operand-format variants of the decode, both exact; the variant follows the activation
+// dtype because tcgen05.mma kind::f16 with A = f16 and B = bf16 raises an illegal
+// instruction on sm_100a (observed), so both operands always share one format:
+//   kAf16   (f16 activations) W' in f16 by the hardware converts cvt.rn.f16x2.e2m1x2 /
+//           .e4m3x2 and one half2 multiply.
+//   kAbf16  (bf16 activations) W' in bf16 by bit placement: the code's magnitude bits at
+//           bf16 bits 8:6 read as value * 2^-126 (0.5 is the bf16 subnormal); one bf16x2
+//           multiply by scale * 2^119 gives value * scale * 2^-7, and the epilogue
+//           multiplies by g * 128.
+#include <type_traits>
+
 #include "common.cuh"
 #include "sm100_primitives.cuh"
 
@@ -41,7 +45,6 @@ constexpr int kTileK = 64;   // K per stage: one 128-byte swizzled row of 16-bit
 constexpr int kUmmaK = 16;
 constexpr int kProducerWarp = 0;
 constexpr int kMmaWarp = 1;
-constexpr int kEpilogueWarp0 = 2;
 constexpr int kEpilogueWarps = 4;
 constexpr int kDecodeWarp0 = 6;
 constexpr int kDecodeWarps = 8;
@@ -534,14 +537,10 @@ bool linear_umma_supported(const LinearArgs& args) {
 
 int32_t launch_linear_umma(const LinearArgs& args, const DeviceInfo& device, char* message,
                            size_t capacity) {
-  // Policy 3 selects the bf16-operand decode for bf16 activations; f16 activations always
-  // use the f16 operand decode (both operands f16).
-  const bool a_bf16 = get_kernel_policy() == 3 && args.dtype == NML_SM100_BF16;
   if (args.dtype == NML_SM100_F16) {
     return launch_for_rows<kAf16, __half>(args, device, message, capacity);
   }
-  return a_bf16 ? launch_for_rows<kAbf16, __nv_bfloat16>(args, device, message, capacity)
-                : launch_for_rows<kAf16, __nv_bfloat16>(args, device, message, capacity);
+  return launch_for_rows<kAbf16, __nv_bfloat16>(args, device, message, capacity);
 }
 
 }  // namespace nml_sm100

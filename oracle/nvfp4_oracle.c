@@ -31,6 +31,13 @@
 
 #define NML_BLOCK 16
 
+#if defined(__x86_64__)
+#include <immintrin.h>
+#define NML_HAVE_AVX2_PATH 1
+#else
+#define NML_HAVE_AVX2_PATH 0
+#endif
+
 /* ------------------------------------------------------------------ codec */
 
 /* crates/nml-parameter/src/lib.rs:391 (E2M1_MAGNITUDES) and :416-426. */
@@ -319,9 +326,9 @@ long long nml_oracle_embedding(const int64_t *indices, size_t count, const uint8
  * block contributes lanes += x[0..8]*w[0..8] then lanes += x[8..16]*w[8..16]
  * as separate multiply and add; lanes are then summed in lane order and the
  * columns past the last whole block are added one by one. */
-static float dot_row_avx2_order(const uint8_t *payload, const uint8_t *scales, float global_scale,
-                                size_t packed, size_t scale_width, size_t width, size_t row,
-                                const float *input) {
+static float dot_row_scalar_order(const uint8_t *payload, const uint8_t *scales,
+                                  float global_scale, size_t packed, size_t scale_width,
+                                  size_t width, size_t row, const float *input) {
   float lanes[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   const size_t vector_width = width / NML_BLOCK * NML_BLOCK;
   for (size_t block_start = 0; block_start < vector_width; block_start += NML_BLOCK) {
@@ -352,6 +359,105 @@ static float dot_row_avx2_order(const uint8_t *payload, const uint8_t *scales, f
   return sum;
 }
 
+#if NML_HAVE_AVX2_PATH
+/* The same arithmetic with AVX2 registers, so that the CPU baseline runs at the speed class
+ * of the reference's own AVX2 kernel: identical operations in identical order (one multiply
+ * by the effective scale per value, then multiply and add per lane), hence identical bits to
+ * dot_row_scalar_order.  Magnitudes come from an in-register 8-entry table and the sign bit
+ * is OR-ed in, instead of the reference's 16-entry memory gather. */
+__attribute__((target("avx2"))) static float dot_row_avx2(
+    const uint8_t *payload, const uint8_t *scales, float global_scale, size_t packed,
+    size_t scale_width, size_t width, size_t row, const float *input,
+    const float *scale_table) {
+  const __m256 magnitudes = _mm256_setr_ps(0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f);
+  const __m256i seven = _mm256_set1_epi32(7);
+  const __m256i eight = _mm256_set1_epi32(8);
+  const __m128i nibble_mask = _mm_set1_epi8(0x0f);
+  __m256 lanes = _mm256_setzero_ps();
+  const size_t vector_width = width / NML_BLOCK * NML_BLOCK;
+  const uint8_t *row_payload = payload + row * packed;
+  const uint8_t *row_scales = scales + row * scale_width;
+  for (size_t block_start = 0; block_start < vector_width; block_start += NML_BLOCK) {
+    const __m256 effective =
+        _mm256_set1_ps(scale_table[row_scales[block_start / NML_BLOCK]] * global_scale);
+    const __m128i bytes = _mm_loadl_epi64((const __m128i *)(row_payload + block_start / 2));
+    const __m128i low = _mm_and_si128(bytes, nibble_mask);
+    const __m128i high = _mm_and_si128(_mm_srli_epi16(bytes, 4), nibble_mask);
+    const __m128i codes = _mm_unpacklo_epi8(low, high); /* 16 codes in column order */
+    const __m256i first = _mm256_cvtepu8_epi32(codes);
+    const __m256i second = _mm256_cvtepu8_epi32(_mm_srli_si128(codes, 8));
+    const __m256 sign_first =
+        _mm256_castsi256_ps(_mm256_slli_epi32(_mm256_and_si256(first, eight), 28));
+    const __m256 sign_second =
+        _mm256_castsi256_ps(_mm256_slli_epi32(_mm256_and_si256(second, eight), 28));
+    const __m256 value_first = _mm256_or_ps(
+        _mm256_permutevar8x32_ps(magnitudes, _mm256_and_si256(first, seven)), sign_first);
+    const __m256 value_second = _mm256_or_ps(
+        _mm256_permutevar8x32_ps(magnitudes, _mm256_and_si256(second, seven)), sign_second);
+    const __m256 weight_first = _mm256_mul_ps(value_first, effective);
+    const __m256 weight_second = _mm256_mul_ps(value_second, effective);
+    lanes = _mm256_add_ps(lanes, _mm256_mul_ps(_mm256_loadu_ps(input + block_start),
+                                               weight_first));
+    lanes = _mm256_add_ps(lanes, _mm256_mul_ps(_mm256_loadu_ps(input + block_start + 8),
+                                               weight_second));
+  }
+  float lane_values[8];
+  _mm256_storeu_ps(lane_values, lanes);
+  float sum = 0.0f;
+  for (int lane = 0; lane < 8; ++lane) sum += lane_values[lane];
+  for (size_t column = vector_width; column < width; ++column) {
+    sum += input[column] *
+           weight_value(payload, scales, global_scale, packed, scale_width, row, column);
+  }
+  return sum;
+}
+#endif
+
+static float g_scale_table[256];
+static int g_scale_table_ready = 0;
+static int g_use_avx2 = -1;
+
+static void prepare_tables(void) {
+  if (!g_scale_table_ready) {
+    for (int bits = 0; bits < 256; ++bits) {
+      float value = 0.0f;
+      if (!nml_oracle_decode_e4m3fn_scale((uint8_t)bits, &value)) value = NAN;
+      g_scale_table[bits] = value;
+    }
+    g_scale_table_ready = 1;
+  }
+  if (g_use_avx2 < 0) {
+#if NML_HAVE_AVX2_PATH
+    g_use_avx2 = __builtin_cpu_supports("avx2") ? 1 : 0;
+#else
+    g_use_avx2 = 0;
+#endif
+  }
+}
+
+/* 1: use the AVX2 evaluation when the host has it (default); 0: scalar evaluation. */
+void nml_oracle_set_avx2(int enabled) {
+  prepare_tables();
+#if NML_HAVE_AVX2_PATH
+  g_use_avx2 = (enabled && __builtin_cpu_supports("avx2")) ? 1 : 0;
+#else
+  (void)enabled;
+#endif
+}
+
+static float dot_row_avx2_order(const uint8_t *payload, const uint8_t *scales, float global_scale,
+                                size_t packed, size_t scale_width, size_t width, size_t row,
+                                const float *input) {
+#if NML_HAVE_AVX2_PATH
+  if (g_use_avx2 == 1) {
+    return dot_row_avx2(payload, scales, global_scale, packed, scale_width, width, row, input,
+                        g_scale_table);
+  }
+#endif
+  return dot_row_scalar_order(payload, scales, global_scale, packed, scale_width, width, row,
+                              input);
+}
+
 /* f64 accumulation of the same terms, the independent oracle the reference's
  * own tests use (crates/nml-kernel-nvfp4/tests/cpu_contract.rs:44-85). */
 static double dot_row_f64(const uint8_t *payload, const uint8_t *scales, float global_scale,
@@ -374,6 +480,7 @@ static double dot_row_f64(const uint8_t *payload, const uint8_t *scales, float g
 void nml_oracle_linear(const float *input, size_t rows, const uint8_t *payload,
                        const uint8_t *scales, float global_scale, size_t outputs, size_t inputs,
                        const float *bias, float *out, int mode) {
+  prepare_tables();
   const size_t packed = (inputs + 1) / 2, scale_width = (inputs + NML_BLOCK - 1) / NML_BLOCK;
 #pragma omp parallel for schedule(static) collapse(2)
   for (long long row = 0; row < (long long)rows; ++row) {
@@ -443,6 +550,7 @@ long long nml_oracle_grouped_projection(const float *input, const int64_t *exper
                                         const uint8_t *scales, float global_scale, size_t experts,
                                         size_t outputs, size_t inputs, const float *bias,
                                         float *out, int mode) {
+  prepare_tables();
   for (size_t a = 0; a < assignments; ++a) {
     if (expert_indices[a] < 0 || (uint64_t)expert_indices[a] >= experts) return 1 + (long long)a;
   }
@@ -467,6 +575,7 @@ long long nml_oracle_routed_clamped_swiglu(
     const uint8_t *down_payload, const uint8_t *down_scales, float down_global,
     const float *down_bias, size_t experts, size_t hidden_size, size_t intermediate, float *out,
     int mode) {
+  prepare_tables();
   const size_t doubled = 2 * intermediate;
   for (size_t a = 0; a < tokens * top_k; ++a) {
     if (router_indices[a] < 0 || (uint64_t)router_indices[a] >= experts) return 1 + (long long)a;
@@ -520,6 +629,7 @@ void nml_oracle_expert_gate_up(const float *hidden, const int32_t *expert_ids, s
                                size_t top_k, const uint8_t *payload, const uint8_t *scales,
                                float global_scale, const float *bias, size_t hidden_size,
                                size_t intermediate, float *activated, int mode) {
+  prepare_tables();
   const size_t doubled = 2 * intermediate;
 #pragma omp parallel
   {
@@ -550,6 +660,7 @@ void nml_oracle_expert_down(const float *activated, const int32_t *expert_ids,
                             const uint8_t *payload, const uint8_t *scales, float global_scale,
                             const float *bias, size_t hidden_size, size_t intermediate,
                             float *weighted, int mode) {
+  prepare_tables();
 #pragma omp parallel
   {
     float *projected = (float *)malloc(sizeof(float) * hidden_size);

@@ -30,7 +30,7 @@ __all__ = [
     "validate_weight", "to_f32", "from_f32", "embedding", "linear", "linear_16",
     "grouped_projection", "routed_clamped_swiglu", "expert_gate_up", "expert_down", "route",
     "assignment_plan", "plan_capacity", "combine", "exp_det", "threads", "set_threads",
-    "error_metrics",
+    "error_metrics", "set_avx2",
 ]
 
 
@@ -113,6 +113,7 @@ def _declare(l: ctypes.CDLL) -> None:
     l.nml_oracle_combine.restype = None
     l.nml_oracle_combine.argtypes = [_u16p, _sz, _sz, _sz, ctypes.c_int, ctypes.c_int, _u16p]
     l.nml_oracle_threads.restype = ctypes.c_int
+    l.nml_oracle_set_avx2.argtypes = [ctypes.c_int]
     l.nml_oracle_set_threads.argtypes = [ctypes.c_int]
 
 
@@ -387,6 +388,12 @@ def combine(weighted_bits, tokens, top_k, dtype, mode: int = 0) -> np.ndarray:
     lib().nml_oracle_combine(_p(w, _u16p), tokens, top_k, hidden_size, dtype, mode,
                              _p(out, _u16p))
     return out
+
+
+def set_avx2(enabled: bool) -> None:
+    """Chooses between the AVX2 and the scalar evaluation of the dot product; both perform
+    the same operations in the same order and return the same bits."""
+    lib().nml_oracle_set_avx2(1 if enabled else 0)
 
 
 def threads() -> int:

@@ -86,17 +86,10 @@ def test_tensor_core_kernel_f16_activations(M, K, N):
 
 
 @pytest.mark.parametrize("M,K,N", UMMA_CASES)
-def test_tensor_core_kernel_bf16_operand_decode(M, K, N):
+def test_tensor_core_kernel_bf16_activations(M, K, N):
     from nml_b200 import _abi
-    run_linear(M, K, N, oracle.BF16, _abi.POLICY_UMMA_BF16_OPERAND, with_bias=(M % 2 == 1),
-               seed=M + N, expect_kernel="umma_swapab_abf16")
-
-
-@pytest.mark.parametrize("M,K,N", UMMA_CASES)
-def test_tensor_core_kernel_bf16_activations_default_decode(M, K, N):
-    from nml_b200 import _abi
-    run_linear(M, K, N, oracle.BF16, _abi.POLICY_UMMA, with_bias=(M % 2 == 0), seed=M + N,
-               expect_kernel="umma_swapab")
+    run_linear(M, K, N, oracle.BF16, _abi.POLICY_UMMA, with_bias=(M % 2 == 1), seed=M + N,
+               expect_kernel="umma_swapab_abf16")
 
 
 CONFIG_SHAPES = [(2880, 5120), (4096, 2880), (2880, 5760), (2880, 2880)]

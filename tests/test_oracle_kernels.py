@@ -299,3 +299,25 @@ def test_plan_capacity_figures():
     # T=4096,k=4 -> 1054 blocks / 16864 slots; T=64 -> 46 blocks
     assert oracle.plan_capacity(16384, 32) == (1054, 16864)
     assert oracle.plan_capacity(256, 32)[0] == 46
+
+
+def test_avx2_and_scalar_evaluations_return_identical_bits():
+    from helpers import make_activation, make_weight
+    w = make_weight(1, (96, 2880))
+    _, x = make_activation(2, (5, 2880))
+    bias = np.linspace(-1, 1, 96, dtype=np.float32)
+    try:
+        oracle.set_avx2(False)
+        scalar = oracle.linear(x, *w, bias)
+    finally:
+        oracle.set_avx2(True)
+    vector = oracle.linear(x, *w, bias)
+    assert np.array_equal(scalar.view(np.uint32), vector.view(np.uint32))
+    odd = make_weight(3, (7, 49))
+    _, xo = make_activation(4, (3, 49))
+    try:
+        oracle.set_avx2(False)
+        scalar = oracle.linear(xo, *odd)
+    finally:
+        oracle.set_avx2(True)
+    assert np.array_equal(scalar.view(np.uint32), oracle.linear(xo, *odd).view(np.uint32))
