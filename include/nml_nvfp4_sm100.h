@@ -266,6 +266,35 @@ int32_t nml_nvfp4_sm100_combine(const NmlSm100Combine *request, char *error_mess
 int32_t nml_nvfp4_sm100_routed_swiglu(const NmlSm100RoutedSwiglu *request, char *error_message,
                                       size_t error_message_capacity);
 
+/* Routed clamped-SwiGLU layer for callers that cannot hand over scratch memory.
+ *
+ * This entry point has no counterpart in the reference.  Some hosts of this library have
+ * no way to obtain device memory for the layer's intermediates at call time: a custom-call
+ * handler that only receives the operand and result buffers the compiler planned, or a
+ * runtime that forbids cudaMalloc once serving has started.  For them the intermediates
+ * (schedule, activated rows, weighted rows) live in a fixed array inside the library's
+ * device image instead of in `workspace`.
+ *
+ * Same request struct and same result as nml_nvfp4_sm100_routed_swiglu; `workspace` and
+ * `workspace_bytes` are ignored.  Limits and rules:
+ *   - the array is NML_SM100_STATIC_SCRATCH_BYTES (8 MiB) and every GPU that loads the
+ *     library holds it until the process exits; a request whose
+ *     nml_nvfp4_sm100_routed_swiglu_workspace_bytes(...) exceeds it is rejected with
+ *     status 1 and a message naming both sizes (at GPT-OSS widths, hidden = intermediate =
+ *     2880 and 4 routes per token, that is about 180 tokens);
+ *   - the first call on a device looks up the array's device address (one runtime query,
+ *     no allocation); make that first call before starting any stream capture;
+ *   - nothing is allocated or freed, here or in anything it calls;
+ *   - all calls on a device share the one array and it keeps whatever the previous call
+ *     left.  That is harmless for a single call, because every word the layer reads it
+ *     has written earlier in the same call, but two calls that overlap on the GPU (different
+ *     streams, or one stream captured twice and replayed concurrently) race on it: keep
+ *     calls on one device ordered. */
+#define NML_SM100_STATIC_SCRATCH_BYTES (8u << 20)
+int32_t nml_nvfp4_sm100_routed_swiglu_static(const NmlSm100RoutedSwiglu *request,
+                                             char *error_message,
+                                             size_t error_message_capacity);
+
 /* Scratch bytes nml_nvfp4_sm100_routed_swiglu needs for the given extents (0 on overflow). */
 size_t nml_nvfp4_sm100_routed_swiglu_workspace_bytes(int64_t tokens, int64_t hidden_size,
                                                      int64_t intermediate_size, int64_t experts,

@@ -22,6 +22,8 @@ STATUS_BARRIER_TIMEOUT = 1
 STATUS_TMEM_ALLOC = 2
 STATUS_INDEX_RANGE = 4
 
+STATIC_SCRATCH_BYTES = 8 << 20
+
 POLICY_AUTO = 0
 POLICY_SIMT = 1
 POLICY_UMMA = 2
@@ -108,6 +110,7 @@ REQUEST_ENTRY_POINTS = {
     "nml_nvfp4_sm100_assignment_plan": AssignmentPlan,
     "nml_nvfp4_sm100_combine": Combine,
     "nml_nvfp4_sm100_routed_swiglu": RoutedSwiglu,
+    "nml_nvfp4_sm100_routed_swiglu_static": RoutedSwiglu,
 }
 
 OTHER_ENTRY_POINTS = [

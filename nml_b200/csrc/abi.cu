@@ -12,6 +12,11 @@ namespace nml_sm100 {
 
 __device__ int g_status_word = 0;
 
+// Scratch for nml_nvfp4_sm100_routed_swiglu_static: lives in the device image, so no call
+// ever allocates it.  In host code this name is only a handle for cudaGetSymbolAddress, not
+// a device pointer; kernels receive the address looked up by static_scratch_address().
+static __device__ __align__(256) unsigned char g_static_scratch[NML_SM100_STATIC_SCRATCH_BYTES];
+
 namespace {
 std::atomic<int> g_kernel_policy{0};
 thread_local const char* t_last_linear_kernel = "none";
@@ -531,6 +536,144 @@ extern "C" int32_t nml_nvfp4_sm100_routed_swiglu(const NmlSm100RoutedSwiglu* req
   args.block_experts = block_experts;
   args.active_blocks = active;
   args.expert_offset = nullptr;  // the plan already stores local expert indices
+  args.stream = stream;
+  args.assignments = assignments;
+  args.schedule_blocks = static_cast<int>(w.blocks);
+  args.experts = static_cast<int>(request->experts);
+  args.experts_per_token = static_cast<int>(request->experts_per_token);
+  args.dtype = request->dtype;
+
+  args.input = request->hidden;
+  args.payload = request->gate_payload;
+  args.block_scales = request->gate_scales;
+  args.global_scale = request->gate_global;
+  args.bias = request->gate_bias;
+  args.routing_weights = nullptr;
+  args.output = activated;
+  args.inputs = static_cast<int>(request->hidden_size);
+  args.outputs = static_cast<int>(request->intermediate_size);
+  args.gate_up = true;
+  status = dispatch_experts(args, *device, error_message, error_message_capacity);
+  if (status != NML_SM100_OK) return status;
+
+  args.input = activated;
+  args.payload = request->down_payload;
+  args.block_scales = request->down_scales;
+  args.global_scale = request->down_global;
+  args.bias = request->down_bias;
+  args.routing_weights = request->routing_weights;
+  args.output = weighted;
+  args.inputs = static_cast<int>(request->intermediate_size);
+  args.outputs = static_cast<int>(request->hidden_size);
+  args.gate_up = false;
+  status = dispatch_experts(args, *device, error_message, error_message_capacity);
+  if (status != NML_SM100_OK) return status;
+
+  return launch_combine(weighted, request->expert_ids, request->output,
+                        static_cast<int>(request->tokens),
+                        static_cast<int>(request->experts_per_token),
+                        static_cast<int>(request->hidden_size),
+                        static_cast<int>(request->experts), request->expert_offset,
+                        request->dtype, stream, error_message, error_message_capacity);
+}
+
+
+namespace nml_sm100 {
+namespace {
+
+uint8_t* g_static_scratch_address[kMaxDevices];
+std::atomic<int> g_static_scratch_ready[kMaxDevices];
+
+// Device address of g_static_scratch on the current device, looked up once per device with
+// that device current.  Returns nullptr and fills the message when the lookup fails.
+uint8_t* static_scratch_address(int device, char* message, size_t capacity) {
+  if (g_static_scratch_ready[device].load(std::memory_order_acquire) == 2) {
+    return g_static_scratch_address[device];
+  }
+  void* address = nullptr;
+  const cudaError_t status = cudaGetSymbolAddress(&address, g_static_scratch);
+  if (status != cudaSuccess || address == nullptr) {
+    fail(NML_SM100_LAUNCH_FAILURE,
+         status != cudaSuccess ? cudaGetErrorString(status)
+                               : "the static scratch array has no device address",
+         message, capacity);
+    return nullptr;
+  }
+  int expected = 0;
+  if (g_static_scratch_ready[device].compare_exchange_strong(expected, 1)) {
+    g_static_scratch_address[device] = static_cast<uint8_t*>(address);
+    g_static_scratch_ready[device].store(2, std::memory_order_release);
+  } else {
+    while (g_static_scratch_ready[device].load(std::memory_order_acquire) != 2) {
+    }
+  }
+  return g_static_scratch_address[device];
+}
+
+}  // namespace
+}  // namespace nml_sm100
+
+extern "C" int32_t nml_nvfp4_sm100_routed_swiglu_static(const NmlSm100RoutedSwiglu* request,
+                                                        char* error_message,
+                                                        size_t error_message_capacity) {
+  if (request == nullptr || request->struct_size < sizeof(NmlSm100RoutedSwiglu)) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "truncated NVFP4 routed SwiGLU request",
+                error_message, error_message_capacity);
+  }
+  RoutedWorkspace w;
+  if (request->hidden == nullptr || request->expert_ids == nullptr ||
+      request->routing_weights == nullptr || request->gate_payload == nullptr ||
+      request->gate_scales == nullptr || request->gate_global == nullptr ||
+      request->gate_bias == nullptr || request->down_payload == nullptr ||
+      request->down_scales == nullptr || request->down_global == nullptr ||
+      request->down_bias == nullptr || request->output == nullptr ||
+      request->stream == nullptr || request->expert_offset < 0 || !fits_i32(request->tokens) ||
+      !fits_i32(request->hidden_size) || !fits_i32(request->intermediate_size) ||
+      request->intermediate_size > std::numeric_limits<int32_t>::max() / 2 ||
+      !fits_i32(request->experts) || request->experts > 1024 ||
+      !routed_workspace(request->tokens, request->hidden_size, request->intermediate_size,
+                        request->experts, request->experts_per_token, &w)) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "invalid NVFP4 routed SwiGLU request", error_message,
+                error_message_capacity);
+  }
+  if (w.total > NML_SM100_STATIC_SCRATCH_BYTES) {
+    char text[160];
+    std::snprintf(text, sizeof(text),
+                  "NVFP4 routed SwiGLU needs %zu scratch bytes, the static scratch holds %u",
+                  w.total, static_cast<unsigned>(NML_SM100_STATIC_SCRATCH_BYTES));
+    return fail(NML_SM100_INVALID_ARGUMENT, text, error_message, error_message_capacity);
+  }
+  if (!valid_dtype(request->dtype)) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "NVFP4 experts support F16 and BF16 only",
+                error_message, error_message_capacity);
+  }
+  const DeviceInfo* device = current_device(error_message, error_message_capacity);
+  if (device == nullptr) return NML_SM100_LAUNCH_FAILURE;
+  uint8_t* base =
+      static_scratch_address(device->device, error_message, error_message_capacity);
+  if (base == nullptr) return NML_SM100_LAUNCH_FAILURE;
+
+  int32_t* sorted = reinterpret_cast<int32_t*>(base + w.sorted_offset);
+  int32_t* block_experts = reinterpret_cast<int32_t*>(base + w.block_experts_offset);
+  int32_t* active = reinterpret_cast<int32_t*>(base + w.active_offset);
+  void* activated = base + w.activated_offset;
+  void* weighted = base + w.weighted_offset;
+  cudaStream_t stream = static_cast<cudaStream_t>(request->stream);
+  const int assignments = static_cast<int>(request->tokens * request->experts_per_token);
+
+  // The schedule is rewritten in full (sentinels included) and the combine reads only rows
+  // of routes the schedule covered, so nothing has to be cleared between calls.
+  int32_t status = launch_assignment_plan(
+      request->expert_ids, sorted, block_experts, active, assignments,
+      static_cast<int>(request->experts), request->expert_offset, static_cast<int>(w.positions),
+      static_cast<int>(w.blocks), stream, error_message, error_message_capacity);
+  if (status != NML_SM100_OK) return status;
+
+  ExpertArgs args;
+  args.sorted_assignments = sorted;
+  args.block_experts = block_experts;
+  args.active_blocks = active;
+  args.expert_offset = nullptr;
   args.stream = stream;
   args.assignments = assignments;
   args.schedule_blocks = static_cast<int>(w.blocks);
