@@ -1,15 +1,118 @@
-// Grouped expert projections on tcgen05.  Placeholder translation unit: until the grouped
-// tensor-core kernel is in place every shape goes to the portable kernels in moe.cu.
-#include "common.cuh"
+// Grouped (routed-expert) NVFP4 projections on tcgen05: host-side launch of
+// umma::gemm_kernel in gate/up and down mode.
+//
+// The schedule (16-slot blocks sorted by expert) is read on the device: each CTA derives the
+// runs of blocks that share an expert and cuts them into units of BM slots x 128 weight
+// rows, so the launch shape never depends on routing.  Activation rows are gathered by
+// assignment (hidden[a / k] for gate/up, activated[a] for down) straight into the swizzled
+// UMMA operand tile with 16-byte cp.async; there is no permuted copy of the tokens in HBM.
+// Gate/up keeps the checkpoint's interleaved rows (2i = gate, 2i+1 = up): lane pairs of the
+// epilogue exchange accumulators and write swiglu(gate, up) for intermediate column i.
+#include "umma_gemm.cuh"
 
 namespace nml_sm100 {
+namespace {
 
-bool experts_umma_supported(const ExpertArgs&) { return false; }
+using namespace umma;
 
-int32_t launch_experts_umma(const ExpertArgs&, const DeviceInfo&, char* message,
+template <int BM, int KS, int RAW, int WB, int AFMT, typename T, int MODE>
+int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* message,
+                      size_t capacity) {
+  using L = Layout<BM, KS, RAW, WB, true>;
+  const int rows_per_expert = args.gate_up ? 2 * args.outputs : args.outputs;
+  const int64_t weight_rows = static_cast<int64_t>(args.experts) * rows_per_expert;
+  CUtensorMap tmap_payload;
+  if (!encode_payload_map<KS>(&tmap_payload, args.payload, weight_rows, args.inputs)) {
+    return fail(NML_SM100_LAUNCH_FAILURE, "tensor map encoding failed", message, capacity);
+  }
+  Params p = {};
+  p.block_scales = args.block_scales;
+  p.global_scale = args.global_scale;
+  p.bias = args.bias;
+  p.scale_width = args.inputs / 16;
+  p.weight_rows_total = static_cast<int>(weight_rows);
+  p.rows_per_expert = rows_per_expert;
+  p.M = 0;
+  p.N = args.outputs;
+  p.K = args.inputs;
+  p.n_tiles = (rows_per_expert + kTileN - 1) / kTileN;
+  p.m_tiles = 0;
+  p.k_steps = args.inputs / kTileK;
+  p.n_fastest = 1;
+  p.output = args.output;
+  p.input = args.input;
+  p.sorted_assignments = args.sorted_assignments;
+  p.block_experts = args.block_experts;
+  p.active_blocks = args.active_blocks;
+  p.expert_offset = args.expert_offset;
+  p.routing_weights = args.routing_weights;
+  p.assignments = args.assignments;
+  p.schedule_blocks = args.schedule_blocks;
+  p.experts = args.experts;
+  p.top_k = args.experts_per_token;
+  p.status = device.status_word;
+
+  auto kernel = gemm_kernel<BM, KS, RAW, WB, AFMT, T, MODE>;
+  static bool configured[64] = {};
+  if (!reserve_smem(kernel, L::kSmemBytes, device.device, configured)) {
+    return fail(NML_SM100_LAUNCH_FAILURE, "cannot reserve shared memory for the tcgen05 experts",
+                message, capacity);
+  }
+  // Upper bound of units: every block could open its own slot tile.
+  const int64_t slot_tiles = args.schedule_blocks;
+  const int64_t max_units = slot_tiles * p.n_tiles;
+  const unsigned grid =
+      static_cast<unsigned>(max_units < device.sm_count ? max_units : device.sm_count);
+  kernel<<<grid, kThreadsGrouped, L::kSmemBytes, args.stream>>>(tmap_payload, tmap_payload, p);
+  return launch_result(message, capacity);
+}
+
+template <int AFMT, typename T, int MODE>
+int32_t launch_for_load(const ExpertArgs& args, const DeviceInfo& device, char* message,
+                        size_t capacity) {
+  // Expected slots per expert under balanced routing decide the slot-tile height.
+  const int64_t average = args.assignments <= args.experts
+                              ? 1
+                              : (args.assignments + args.experts - 1) / args.experts;
+  if (average <= 16) {
+    return launch_config<16, 4, 6, 3, AFMT, T, MODE>(args, device, message, capacity);
+  }
+  if (average <= 32) {
+    return launch_config<32, 4, 5, 3, AFMT, T, MODE>(args, device, message, capacity);
+  }
+  if (average <= 64) {
+    return launch_config<64, 4, 3, 3, AFMT, T, MODE>(args, device, message, capacity);
+  }
+  if (average <= 160) {
+    return launch_config<128, 1, 7, 4, AFMT, T, MODE>(args, device, message, capacity);
+  }
+  return launch_config<256, 1, 4, 4, AFMT, T, MODE>(args, device, message, capacity);
+}
+
+template <int MODE>
+int32_t launch_mode(const ExpertArgs& args, const DeviceInfo& device, char* message,
+                    size_t capacity) {
+  if (args.dtype == NML_SM100_F16) {
+    return launch_for_load<kAf16, __half, MODE>(args, device, message, capacity);
+  }
+  return launch_for_load<kAbf16, __nv_bfloat16, MODE>(args, device, message, capacity);
+}
+
+}  // namespace
+
+bool experts_umma_supported(const ExpertArgs& args) {
+  const int64_t rows_per_expert = args.gate_up ? 2ll * args.outputs : args.outputs;
+  return args.inputs % kTileK == 0 && args.experts <= kMaxGroups &&
+         args.experts * rows_per_expert <= std::numeric_limits<int32_t>::max() &&
+         reinterpret_cast<uintptr_t>(args.payload) % 16 == 0 &&
+         reinterpret_cast<uintptr_t>(args.input) % 16 == 0 &&
+         reinterpret_cast<uintptr_t>(args.block_scales) % 4 == 0;
+}
+
+int32_t launch_experts_umma(const ExpertArgs& args, const DeviceInfo& device, char* message,
                             size_t capacity) {
-  return fail(NML_SM100_LAUNCH_FAILURE, "the tcgen05 expert kernel is not built", message,
-              capacity);
+  return args.gate_up ? launch_mode<kGateUp>(args, device, message, capacity)
+                      : launch_mode<kDown>(args, device, message, capacity);
 }
 
 }  // namespace nml_sm100

@@ -1,0 +1,769 @@
+// The weights-stationary tcgen05 NVFP4 GEMM, shared by the dense linear and the grouped
+// (routed-expert) projections.
+//
+//   D[n, m] = sum_k W'[n, k] * X[m, k]        W' = e2m1 code * e4m3 block scale (exact 16-bit)
+//
+// A tile of 128 weight rows is the UMMA M dimension; BM in {16..256} activation rows (dense)
+// or schedule slots (grouped) are the UMMA N dimension, so packed weights are decoded once
+// per K step whatever the number of rows.
+//
+// Two rings decouple bytes in flight from the 16 KB decoded-operand buffers:
+//   raw ring  (RAW stages, each KS K-steps of 64): payload tile [128 x 32*KS B] by TMA,
+//             block-scale bytes by 4-byte cp.async, X tiles [BM x 64] by TMA (dense) or by
+//             16-byte cp.async gathers of scheduled rows (grouped), 128B-swizzled
+//   W' ring   (WB buffers): decoded operand tile [128 x 64], UMMA K-major 128B swizzle
+// Warp roles: 0 producer, 1 MMA issuer + TMEM owner, 2-5 epilogue, 6-13 decode, 14-15 row
+// gather (grouped only).  Accumulators are double-buffered in TMEM; the kernel is persistent.
+//
+// Every mbarrier wait is bounded; a wait that runs out sets the barrier-timeout bit of the
+// device status word and all roles leave through the common teardown.
+#pragma once
+
+#include <type_traits>
+
+#include "common.cuh"
+#include "sm100_primitives.cuh"
+
+namespace nml_sm100 {
+namespace umma {
+
+enum Mode : int { kDense = 0, kGateUp = 1, kDown = 2 };
+enum AFormat : int { kAf16 = 0, kAbf16 = 1 };
+
+constexpr int kTileN = 128;
+constexpr int kTileK = 64;
+constexpr int kUmmaK = 16;
+constexpr int kProducerWarp = 0;
+constexpr int kMmaWarp = 1;
+constexpr int kEpilogueWarps = 4;
+constexpr int kDecodeWarp0 = 6;
+constexpr int kDecodeWarps = 8;
+constexpr int kDecodeThreads = kDecodeWarps * 32;
+constexpr int kGatherWarp0 = kDecodeWarp0 + kDecodeWarps;  // 14
+constexpr int kGatherWarps = 2;
+constexpr int kGatherThreads = kGatherWarps * 32;
+constexpr int kThreadsDense = kGatherWarp0 * 32;                     // 448
+constexpr int kThreadsGrouped = (kGatherWarp0 + kGatherWarps) * 32;  // 512
+constexpr int kWBytes = kTileN * 128;
+constexpr int kSmemBudget = 227 * 1024;
+constexpr int kMaxGroups = 256;
+
+template <int BM, int KS, int RAW, int WB, bool GROUPED>
+struct Layout {
+  static constexpr int kPayloadBytes = kTileN * 32 * KS;
+  static constexpr int kScaleBytes = kTileN * 4 * KS < 1024 ? 1024 : kTileN * 4 * KS;
+  static constexpr int kXBytes = BM * 128;                 // one K step
+  static constexpr int kRawBytes = kPayloadBytes + kScaleBytes + kXBytes * KS;
+  static constexpr int kRawOffset = WB * kWBytes;
+  static constexpr int kBarrierOffset = kRawOffset + RAW * kRawBytes;
+  static constexpr int kBarrierBytes = 2048;
+  static constexpr int kGroupBytes = GROUPED ? (kMaxGroups * 16 + 64) : 0;
+  static constexpr int kSmemBytes = kBarrierOffset + kBarrierBytes + kGroupBytes + 1024;
+  static constexpr int kTmemColumns = 2 * BM < 32 ? 32 : 2 * BM;
+  static_assert(kSmemBytes <= kSmemBudget, "shared memory budget exceeded");
+  static_assert(kRawBytes % 1024 == 0, "raw stage must keep 1024-byte alignment");
+  static_assert((kTmemColumns & (kTmemColumns - 1)) == 0 && kTmemColumns <= 512, "TMEM");
+  static_assert(KS == 1 || KS == 2 || KS == 4, "K steps per raw stage");
+};
+
+struct Params {
+  // weights
+  const uint8_t* block_scales;
+  const float* global_scale;
+  const void* bias;
+  int scale_width;        // K / 16
+  int weight_rows_total;  // rows of the payload tensor (N, or experts * rows_per_expert)
+  int rows_per_expert;    // grouped: 2I (gate/up) or H (down)
+  // problem
+  int M, N, K;            // dense: rows, outputs, inputs; grouped: N = output columns per expert
+  int n_tiles, m_tiles, k_steps, n_fastest;
+  void* output;
+  // grouped
+  const void* input;  // hidden [tokens, K] (gate/up) or activated [assignments, K] (down)
+  const int32_t* sorted_assignments;
+  const int32_t* block_experts;
+  const int32_t* active_blocks;
+  const int32_t* expert_offset;
+  const void* routing_weights;
+  int assignments, schedule_blocks, experts, top_k;
+  int* status;
+};
+
+// One unit of work: a 128-row weight tile against BM activation rows / schedule slots.
+struct Unit {
+  int weight_row0;  // first row of the tile in the payload tensor
+  int n0;           // first output column (dense) / first weight row inside the expert (grouped)
+  int m0;           // dense: first activation row; grouped: first schedule slot
+  int rows;         // grouped: valid slots in this unit (<= BM)
+  int expert;       // grouped: local expert index
+};
+
+// Group table in shared memory (grouped mode): runs of schedule blocks with one expert.
+struct Groups {
+  int count;
+  int total_units;
+  int expert[kMaxGroups];
+  int first_block[kMaxGroups];
+  int blocks[kMaxGroups];
+  int unit_prefix[kMaxGroups];
+};
+
+// ---- operand decode -------------------------------------------------------------------
+
+// 8 codes (one payload word) -> 8 exact f16 products with the block scale, K order.
+__device__ __forceinline__ void decode8_f16(uint32_t word, uint32_t scale2, uint32_t (&out)[4]) {
+  uint32_t h0, h1, h2, h3;
+  asm("{\n"
+      ".reg .b8 b0, b1, b2, b3;\n"
+      "mov.b32 {b0, b1, b2, b3}, %4;\n"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n"
+      "cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n"
+      "cvt.rn.f16x2.e2m1x2 %3, b3;\n"
+      "}\n"
+      : "=r"(h0), "=r"(h1), "=r"(h2), "=r"(h3)
+      : "r"(word));
+  asm("mul.rn.f16x2 %0, %0, %1;" : "+r"(h0) : "r"(scale2));
+  asm("mul.rn.f16x2 %0, %0, %1;" : "+r"(h1) : "r"(scale2));
+  asm("mul.rn.f16x2 %0, %0, %1;" : "+r"(h2) : "r"(scale2));
+  asm("mul.rn.f16x2 %0, %0, %1;" : "+r"(h3) : "r"(scale2));
+  out[0] = h0;
+  out[1] = h1;
+  out[2] = h2;
+  out[3] = h3;
+}
+
+// Two E4M3 scale bytes -> two duplicated f16x2 scale words.
+__device__ __forceinline__ void scales2_f16(uint32_t two_bytes, uint32_t& first,
+                                            uint32_t& second) {
+  uint32_t pair;
+  asm("{\n"
+      ".reg .b16 s;\n"
+      "cvt.u16.u32 s, %1;\n"
+      "cvt.rn.f16x2.e4m3x2 %0, s;\n"
+      "}\n"
+      : "=r"(pair)
+      : "r"(two_bytes));
+  first = __byte_perm(pair, pair, 0x1010);
+  second = __byte_perm(pair, pair, 0x3232);
+}
+
+// 8 codes -> 8 exact bf16 values code * scale * 2^-7, K order.  scale2 holds
+// bf16(scale * 2^119) in both halves.  The code's magnitude bits placed at bf16 bits 8:6
+// read as value * 2^-126 (0.5 is the bf16 subnormal); the sign stays at bit 15.
+__device__ __forceinline__ void decode8_bf16(uint32_t word, uint32_t scale2, uint32_t (&out)[4]) {
+  uint32_t t[4];
+  uint32_t q = word;
+#pragma unroll
+  for (int i = 3; i >= 0; --i) {
+    t[i] = (q & 0x80008000u) | ((q & 0x70007000u) >> 6);  // codes i and i + 4
+    q <<= 4;
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(t[i]) : "r"(scale2));
+  }
+  out[0] = __byte_perm(t[0], t[1], 0x5410);
+  out[1] = __byte_perm(t[2], t[3], 0x5410);
+  out[2] = __byte_perm(t[0], t[1], 0x7632);
+  out[3] = __byte_perm(t[2], t[3], 0x7632);
+}
+
+// One E4M3 scale byte -> bf16(scale * 2^119) in both halves: the byte's value bits at bf16
+// bits 10:4 read as scale * 2^-120; two exact bf16 multiplies rescale.
+__device__ __forceinline__ uint32_t scale_bf16_dup(uint32_t byte) {
+  uint32_t s = (byte & 0x7fu) << 4;
+  s |= s << 16;
+  const uint32_t two_p120 = 0x7b807b80u;
+  const uint32_t two_p119 = 0x7b007b00u;
+  asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(s) : "r"(two_p120));
+  asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(s) : "r"(two_p119));
+  return s;
+}
+
+// ---- unit enumeration -------------------------------------------------------------------
+
+// Built by one warp: consecutive schedule blocks with the same (valid, local) expert form a
+// group; a group is cut into slot tiles of BM and weight tiles of 128 rows.
+__device__ __forceinline__ void build_groups(Groups* groups, const Params& p, int BM, int lane) {
+  int blocks = p.schedule_blocks;
+  if (p.active_blocks != nullptr) blocks = max(0, min(blocks, p.active_blocks[0]));
+  const int offset = p.expert_offset != nullptr ? p.expert_offset[0] : 0;
+  auto local_expert = [&](int b) -> int {
+    if (b < 0 || b >= blocks) return -1;
+    const int id = p.block_experts[b];
+    const int local = id - offset;
+    return (id >= 0 && local >= 0 && local < p.experts) ? local : -1;
+  };
+  int starts = 0, ends = 0;
+  for (int base = 0; base < blocks; base += 32) {
+    const int b = base + lane;
+    const int e = local_expert(b);
+    const bool is_start = e >= 0 && local_expert(b - 1) != e;
+    const bool is_end = e >= 0 && local_expert(b + 1) != e;
+    const unsigned start_mask = __ballot_sync(0xffffffffu, is_start);
+    const unsigned end_mask = __ballot_sync(0xffffffffu, is_end);
+    const unsigned below = (1u << lane) - 1u;
+    const int start_index = starts + __popc(start_mask & below);
+    const int end_index = ends + __popc(end_mask & below);
+    if (is_start && start_index < kMaxGroups) {
+      groups->expert[start_index] = e;
+      groups->first_block[start_index] = b;
+    }
+    if (is_end && end_index < kMaxGroups) groups->blocks[end_index] = b + 1;  // end for now
+    starts += __popc(start_mask);
+    ends += __popc(end_mask);
+  }
+  __syncwarp();
+  const int count = min(starts, kMaxGroups);
+  if (lane == 0) {
+    int prefix = 0;
+    for (int g = 0; g < count; ++g) {
+      const int n_blocks = groups->blocks[g] - groups->first_block[g];
+      groups->blocks[g] = n_blocks;
+      groups->unit_prefix[g] = prefix;
+      prefix += ((n_blocks * 16 + BM - 1) / BM) * p.n_tiles;
+    }
+    groups->count = count;
+    groups->total_units = prefix;
+  }
+  __syncwarp();
+}
+
+template <int BM, bool GROUPED>
+__device__ __forceinline__ int total_units(const Params& p, const Groups* groups) {
+  if constexpr (GROUPED) {
+    return groups->total_units;
+  } else {
+    return p.n_tiles * p.m_tiles;
+  }
+}
+
+template <int BM, bool GROUPED>
+__device__ __forceinline__ Unit get_unit(const Params& p, const Groups* groups, int index) {
+  Unit u;
+  if constexpr (GROUPED) {
+    int lo = 0, hi = groups->count - 1;
+    while (lo < hi) {  // last group whose prefix <= index
+      const int mid = (lo + hi + 1) >> 1;
+      if (groups->unit_prefix[mid] <= index) {
+        lo = mid;
+      } else {
+        hi = mid - 1;
+      }
+    }
+    const int local = index - groups->unit_prefix[lo];
+    const int slot_tile = local / p.n_tiles;
+    const int n_tile = local - slot_tile * p.n_tiles;
+    u.expert = groups->expert[lo];
+    u.n0 = n_tile * kTileN;
+    u.weight_row0 = u.expert * p.rows_per_expert + u.n0;
+    u.m0 = groups->first_block[lo] * 16 + slot_tile * BM;
+    u.rows = min(BM, groups->blocks[lo] * 16 - slot_tile * BM);
+  } else {
+    int n_tile, m_tile;
+    if (p.n_fastest) {
+      m_tile = index / p.n_tiles;
+      n_tile = index - m_tile * p.n_tiles;
+    } else {
+      n_tile = index / p.m_tiles;
+      m_tile = index - n_tile * p.m_tiles;
+    }
+    u.expert = 0;
+    u.n0 = n_tile * kTileN;
+    u.weight_row0 = u.n0;
+    u.m0 = m_tile * BM;
+    u.rows = min(BM, p.M - u.m0);
+  }
+  return u;
+}
+
+struct RingState {
+  int index = 0;
+  uint32_t phase = 0;
+  template <int N>
+  __device__ __forceinline__ void advance() {
+    if (++index == N) {
+      index = 0;
+      phase ^= 1u;
+    }
+  }
+};
+
+// ---- the kernel ---------------------------------------------------------------------------
+
+template <int BM, int KS, int RAW, int WB, int AFMT, typename T, int MODE>
+__global__ void __launch_bounds__(MODE == kDense ? kThreadsDense : kThreadsGrouped, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
+            const __grid_constant__ CUtensorMap tmap_x, const Params p) {
+  constexpr bool GROUPED = MODE != kDense;
+  using L = Layout<BM, KS, RAW, WB, GROUPED>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+
+  auto w_tile = [&](int w) { return smem + w * kWBytes; };
+  auto raw_base = [&](int r) { return smem + L::kRawOffset + r * L::kRawBytes; };
+  auto x_tile = [&](int r, int j) { return raw_base(r) + j * L::kXBytes; };
+  auto payload_tile = [&](int r) { return raw_base(r) + KS * L::kXBytes; };
+  auto scale_tile = [&](int r) { return raw_base(r) + KS * L::kXBytes + L::kPayloadBytes; };
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarrierOffset);
+  uint64_t* full_raw = bars;               // [RAW]
+  uint64_t* empty_raw = bars + RAW;        // [RAW]
+  uint64_t* full_w = bars + 2 * RAW;       // [WB]
+  uint64_t* empty_w = full_w + WB;         // [WB]
+  uint64_t* tmem_full = empty_w + WB;      // [2]
+  uint64_t* tmem_empty = tmem_full + 2;    // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* row_table = reinterpret_cast<int*>(tmem_slot + 2);  // [BM] gather source rows
+  static_assert((2 * RAW + 2 * WB + 4) * 8 + 8 + 256 * 4 <= L::kBarrierBytes, "barrier area");
+  Groups* groups = reinterpret_cast<Groups*>(smem + L::kBarrierOffset + L::kBarrierBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int r = 0; r < RAW; ++r) {
+      mbar_init(&full_raw[r], 1 + 32 + (GROUPED ? kGatherThreads : 0));
+      mbar_init(&empty_raw[r], 1);
+    }
+    for (int w = 0; w < WB; ++w) {
+      mbar_init(&full_w[w], kDecodeThreads);
+      mbar_init(&empty_w[w], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], kEpilogueWarps * 32);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == kProducerWarp) {
+    if (lane == 0) {
+      tma_prefetch_descriptor(&tmap_payload);
+      if constexpr (!GROUPED) tma_prefetch_descriptor(&tmap_x);
+    }
+    if constexpr (GROUPED) build_groups(groups, p, BM, lane);
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(tmem_slot, L::kTmemColumns);
+    tmem_relinquish_alloc_permit();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const int units = total_units<BM, GROUPED>(p, groups);
+  const int raw_stages = (p.k_steps + KS - 1) / KS;
+
+  auto give_up = [&]() {
+    *abort_flag = 1;
+    atomicOr(p.status, NML_SM100_STATUS_BARRIER_TIMEOUT);
+  };
+  // Bounded wait that also honours an abort raised by another role.
+  auto wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+    if (*abort_flag) return false;
+    if (mbar_wait(bar, parity)) return true;
+    give_up();
+    return false;
+  };
+
+  if (warp == kProducerWarp) {
+    // ------------------------------------------------------------------ producer
+    RingState raw;
+    int issued = 0;
+    bool ok = true;
+    for (int index = blockIdx.x; index < units && ok; index += gridDim.x) {
+      const Unit u = get_unit<BM, GROUPED>(p, groups, index);
+      for (int rs = 0; rs < raw_stages; ++rs) {
+        if (!wait(&empty_raw[raw.index], raw.phase ^ 1u)) {
+          ok = false;
+          break;
+        }
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&full_raw[raw.index],
+                                L::kPayloadBytes + (GROUPED ? 0 : KS * L::kXBytes));
+          tma_load_2d(payload_tile(raw.index), &tmap_payload, &full_raw[raw.index],
+                      rs * KS * 32, u.weight_row0);
+          if constexpr (!GROUPED) {
+#pragma unroll
+            for (int j = 0; j < KS; ++j) {
+              tma_load_2d(x_tile(raw.index, j), &tmap_x, &full_raw[raw.index],
+                          (rs * KS + j) * kTileK, u.m0);
+            }
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < KS; ++j) {
+          const int k_step = rs * KS + j;
+          if (k_step < p.k_steps) {
+#pragma unroll
+            for (int i = 0; i < kTileN / 32; ++i) {
+              const int row = lane + 32 * i;
+              const int n = min(u.weight_row0 + row, p.weight_rows_total - 1);
+              cp_async_4(scale_tile(raw.index) + row * (4 * KS) + j * 4,
+                         p.block_scales + static_cast<int64_t>(n) * p.scale_width + k_step * 4);
+            }
+          }
+        }
+        cp_async_mbar_arrive_noinc(&full_raw[raw.index]);
+        ++issued;
+        raw.advance<RAW>();
+      }
+    }
+    // Do not leave while copies this warp started may still be landing in shared memory.
+    const int pending = issued < RAW ? issued : RAW;
+    for (int i = 0; i < pending; ++i) {
+      raw.index = raw.index == 0 ? RAW - 1 : raw.index - 1;
+      if (raw.index == RAW - 1) raw.phase ^= 1u;
+      if (!mbar_wait(&full_raw[raw.index], raw.phase)) give_up();
+    }
+  } else if (warp == kMmaWarp) {
+    // ----------------------------------------------------------------------- MMA
+    if (lane == 0) {
+      constexpr uint32_t a_format = AFMT == kAf16 ? kUmmaF16 : kUmmaBF16;
+      constexpr uint32_t b_format = std::is_same<T, __half>::value ? kUmmaF16 : kUmmaBF16;
+      constexpr uint32_t idesc = umma_idesc_f16(a_format, b_format, kTileN, BM);
+      RingState raw, wb;
+      int local = 0;
+      bool ok = true;
+      for (int index = blockIdx.x; index < units && ok; index += gridDim.x, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!wait(&tmem_empty[acc], acc_phase ^ 1u)) break;
+        tcgen05_fence_after_sync();
+        const uint32_t d_address = tmem_base + acc * BM;
+        for (int rs = 0; rs < raw_stages && ok; ++rs) {
+          if (!wait(&full_raw[raw.index], raw.phase)) {
+            ok = false;
+            break;
+          }
+          const int sub_steps = min(KS, p.k_steps - rs * KS);
+          for (int j = 0; j < sub_steps; ++j) {
+            if (!wait(&full_w[wb.index], wb.phase)) {
+              ok = false;
+              break;
+            }
+            tcgen05_fence_after_sync();
+            const uint64_t a_desc = umma_smem_desc_sw128(smem_u32(w_tile(wb.index)));
+            const uint64_t b_desc = umma_smem_desc_sw128(smem_u32(x_tile(raw.index, j)));
+#pragma unroll
+            for (int q = 0; q < kTileK / kUmmaK; ++q) {
+              // each K=16 slice is 32 bytes further along the swizzled 128-byte rows
+              umma_f16(d_address, a_desc + 2 * q, b_desc + 2 * q, idesc, (rs | j | q) != 0);
+            }
+            umma_commit(&empty_w[wb.index]);
+            wb.advance<WB>();
+          }
+          if (ok) umma_commit(&empty_raw[raw.index]);
+          raw.advance<RAW>();
+        }
+        if (ok) umma_commit(&tmem_full[acc]);
+      }
+    }
+    __syncwarp();
+  } else if (warp < kDecodeWarp0) {
+    // ------------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;  // TMEM lanes a warp may read: 32 * (warp % 4)
+    const float g = __ldg(p.global_scale) * (AFMT == kAbf16 ? 128.0f : 1.0f);
+    T* out = static_cast<T*>(p.output);
+    const T* bias = static_cast<const T*>(p.bias);
+    const int row = quarter * 32 + lane;  // row of the weight tile this thread reads
+    int local = 0;
+    for (int index = blockIdx.x; index < units; index += gridDim.x, ++local) {
+      const Unit u = get_unit<BM, GROUPED>(p, groups, index);
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      if (!wait(&tmem_full[acc], acc_phase)) break;
+      tcgen05_fence_after_sync();
+      const int n = u.n0 + row;  // output column (dense, down) or weight row in the expert
+      const bool n_ok = n < (MODE == kGateUp ? p.rows_per_expert : p.N);
+      float bias_value = 0.0f;
+      if (bias != nullptr && n_ok) {
+        bias_value = Elem<T>::load(
+            bias[(GROUPED ? static_cast<int64_t>(u.expert) * p.rows_per_expert : 0) + n]);
+      }
+      constexpr int kChunk = BM >= 32 ? 32 : 16;
+#pragma unroll 1
+      for (int c = 0; c < BM; c += kChunk) {
+        const uint32_t address =
+            tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BM + c;
+        uint32_t v[kChunk];
+        if constexpr (kChunk == 32) {
+          tmem_load_32x32(address, v);
+        } else {
+          tmem_load_32x16(address, v);
+        }
+        tmem_load_wait();
+        if (c >= u.rows) continue;  // uniform: nothing valid left in this chunk
+        if constexpr (MODE == kDense) {
+          if (n_ok) {
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j) {
+              const int m = u.m0 + c + j;
+              if (c + j < u.rows) {
+                out[static_cast<int64_t>(m) * p.N + n] =
+                    Elem<T>::store(fmaf(__uint_as_float(v[j]), g, bias_value));
+              }
+            }
+          }
+        } else if constexpr (MODE == kDown) {
+#pragma unroll
+          for (int j = 0; j < kChunk; ++j) {
+            if (c + j < u.rows) {
+              const int a = p.sorted_assignments[u.m0 + c + j];
+              if (n_ok && a >= 0 && a < p.assignments) {
+                const float weight =
+                    Elem<T>::load(static_cast<const T*>(p.routing_weights)[a]);
+                out[static_cast<int64_t>(a) * p.N + n] =
+                    Elem<T>::store(fmaf(__uint_as_float(v[j]), g, bias_value) * weight);
+              }
+            }
+          }
+        } else {
+          // gate/up: even tile rows carry gate, odd rows carry up of the same intermediate
+          // column.  Lane pairs swap one value per column pair, so the even lane finishes
+          // column c+2q and the odd lane column c+2q+1.
+          const bool odd = (lane & 1) != 0;
+          const int column = n >> 1;  // intermediate column inside the expert
+#pragma unroll
+          for (int q = 0; q < kChunk / 2; ++q) {
+            const float mine_even = fmaf(__uint_as_float(v[2 * q]), g, bias_value);
+            const float mine_odd = fmaf(__uint_as_float(v[2 * q + 1]), g, bias_value);
+            const float received =
+                __shfl_xor_sync(0xffffffffu, odd ? mine_even : mine_odd, 1);
+            const int j = 2 * q + (odd ? 1 : 0);
+            const float gate = odd ? received : mine_even;
+            const float up = odd ? mine_odd : received;
+            if (c + j < u.rows) {
+              const int a = p.sorted_assignments[u.m0 + c + j];
+              if (n_ok && a >= 0 && a < p.assignments) {
+                out[static_cast<int64_t>(a) * p.N + column] =
+                    Elem<T>::store(clamped_swiglu(gate, up));
+              }
+            }
+          }
+        }
+      }
+      tcgen05_fence_before_sync();
+      mbar_arrive(&tmem_empty[acc]);
+    }
+  } else if (warp < kGatherWarp0) {
+    // -------------------------------------------------------------------- decode
+    const int t = threadIdx.x - kDecodeWarp0 * 32;  // 0..255
+    const int row = KS == 1 ? (t >> 1) : (t & 127);
+    const int half = KS == 1 ? (t & 1) : (t >> 7);
+    RingState raw, wb;
+    bool ok = true;
+    for (int index = blockIdx.x; index < units && ok; index += gridDim.x) {
+      for (int rs = 0; rs < raw_stages && ok; ++rs) {
+        if (!wait(&full_raw[raw.index], raw.phase)) {
+          ok = false;
+          break;
+        }
+        const int sub_steps = min(KS, p.k_steps - rs * KS);
+        for (int j = 0; j < sub_steps; ++j) {
+          if (!wait(&empty_w[wb.index], wb.phase ^ 1u)) {
+            ok = false;
+            break;
+          }
+          uint4 codes;
+          if constexpr (KS == 1) {
+            codes = *reinterpret_cast<const uint4*>(payload_tile(raw.index) + t * 16);
+          } else {
+            // rows of 32*KS bytes, 128-byte swizzled by the TMA load
+            codes = *reinterpret_cast<const uint4*>(
+                payload_tile(raw.index) + row * (32 * KS) + (((2 * j + half) ^ (row & 7)) * 16));
+          }
+          const uint32_t two_scales = *reinterpret_cast<const uint16_t*>(
+              scale_tile(raw.index) + row * (4 * KS) + j * 4 + half * 2);
+          uint32_t scale_a, scale_b;
+          if constexpr (AFMT == kAf16) {
+            scales2_f16(two_scales, scale_a, scale_b);
+          } else {
+            scale_a = scale_bf16_dup(two_scales & 0xffu);
+            scale_b = scale_bf16_dup(two_scales >> 8);
+          }
+          uint8_t* w_row = w_tile(wb.index) + row * 128;
+          const uint32_t words[4] = {codes.x, codes.y, codes.z, codes.w};
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            uint32_t o[4];
+            if constexpr (AFMT == kAf16) {
+              decode8_f16(words[jj], jj < 2 ? scale_a : scale_b, o);
+            } else {
+              decode8_bf16(words[jj], jj < 2 ? scale_a : scale_b, o);
+            }
+            const int chunk = (half * 4 + jj) ^ (row & 7);
+            *reinterpret_cast<uint4*>(w_row + chunk * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+          fence_proxy_async_smem();
+          mbar_arrive(&full_w[wb.index]);
+          wb.advance<WB>();
+        }
+        raw.advance<RAW>();
+      }
+    }
+  } else {
+    // -------------------------------------------------------------------- gather
+    if constexpr (GROUPED) {
+      const int t = threadIdx.x - kGatherWarp0 * 32;  // 0..63
+      const int chunk = t & 7;
+      const int row0 = t >> 3;  // rows row0 + 8 i; (row & 7) == row0 for all of them
+      const int position = (chunk ^ row0) * 16;
+      const uint8_t* input = static_cast<const uint8_t*>(p.input);
+      constexpr int kLag = RAW > 2 ? 2 : RAW - 1;  // stages whose copies may still be landing
+      RingState raw, arrive;
+      int in_flight = 0;
+      bool ok = true;
+      auto retire = [&](int keep) {
+        while (in_flight > keep) {
+          if (in_flight - 1 >= 2) {
+            asm volatile("cp.async.wait_group 2;" ::: "memory");
+          } else if (in_flight - 1 == 1) {
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+          } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+          }
+          fence_proxy_async_smem();
+          mbar_arrive(&full_raw[arrive.index]);
+          arrive.advance<RAW>();
+          --in_flight;
+        }
+      };
+      for (int index = blockIdx.x; index < units && ok; index += gridDim.x) {
+        const Unit u = get_unit<BM, GROUPED>(p, groups, index);
+        // Each gather warp owns the table entries of the rows it copies (row & 7 in its
+        // group of four), so a warp-level sync is all the table needs.
+        __syncwarp();
+        for (int r = row0 & ~3; r < BM; r += 8) {
+          const int mine = r + (lane >> 3);
+          if ((lane & 7) == 0 && mine < BM) {
+            int source = -1;
+            if (mine < u.rows) {
+              const int a = p.sorted_assignments[u.m0 + mine];
+              if (a >= 0 && a < p.assignments) source = MODE == kGateUp ? a / p.top_k : a;
+            }
+            row_table[mine] = source;
+          }
+        }
+        __syncwarp();
+        for (int rs = 0; rs < raw_stages; ++rs) {
+          if (!wait(&empty_raw[raw.index], raw.phase ^ 1u)) {
+            ok = false;
+            break;
+          }
+#pragma unroll
+          for (int j = 0; j < KS; ++j) {
+            const int k_step = rs * KS + j;
+            if (k_step < p.k_steps) {
+              const int64_t column_bytes = (static_cast<int64_t>(k_step) * kTileK + chunk * 8) * 2;
+              uint8_t* tile = x_tile(raw.index, j) + position;
+#pragma unroll 4
+              for (int r = row0; r < BM; r += 8) {
+                const int source = row_table[r];
+                const bool valid = source >= 0;
+                cp_async_16_zfill(tile + r * 128,
+                                  input + (valid ? static_cast<int64_t>(source) : 0) * p.K * 2 +
+                                      column_bytes,
+                                  valid);
+              }
+            }
+          }
+          asm volatile("cp.async.commit_group;" ::: "memory");
+          ++in_flight;
+          raw.advance<RAW>();
+          retire(kLag);
+        }
+      }
+      retire(0);
+    }
+  }
+
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tcgen05_fence_after_sync();
+    tmem_dealloc(tmem_base, L::kTmemColumns);
+  }
+}
+
+}  // namespace umma
+}  // namespace nml_sm100
+
+// ---- host helpers -------------------------------------------------------------------------
+
+namespace nml_sm100 {
+namespace umma {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled, resolved through the runtime so the library has no link-time
+// dependency on the driver.
+inline EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = [] {
+    void* symbol = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &symbol, cudaEnableDefault, &result) !=
+            cudaSuccess ||
+        result != cudaDriverEntryPointSuccess) {
+      symbol = nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(symbol);
+  }();
+  return fn;
+}
+
+// Payload tensor [rows, K/2] bytes; one box is 128 rows x 32*KS bytes (128B-swizzled when a
+// row of the box is 128 bytes).
+template <int KS>
+inline bool encode_payload_map(CUtensorMap* map, const uint8_t* payload, int64_t rows, int K) {
+  EncodeTiledFn encode = encode_tiled();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K / 2), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K / 2)};
+  const cuuint32_t box[2] = {32 * KS, kTileN};
+  const cuuint32_t elem[2] = {1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(payload), dims,
+                strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                KS == 4 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Activation tensor [M, K] of 16-bit elements; one box is BM rows x 64 columns, 128B swizzle.
+template <typename T>
+inline bool encode_activation_map(CUtensorMap* map, const void* x, int64_t rows, int K, int BM) {
+  EncodeTiledFn encode = encode_tiled();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
+  const cuuint32_t box[2] = {kTileK, static_cast<cuuint32_t>(BM)};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUtensorMapDataType type = std::is_same<T, __half>::value
+                                       ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                       : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  return encode(map, type, 2, const_cast<void*>(x), dims, strides, box, elem,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Opts a kernel into its dynamic shared memory once per device.  `configured` is the
+// caller's per-kernel table (one static array per kernel instantiation).
+template <typename Kernel>
+inline bool reserve_smem(Kernel kernel, int bytes, int device, bool (&configured)[64]) {
+  if (device >= 0 && device < 64 && configured[device]) return true;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) !=
+      cudaSuccess) {
+    return false;
+  }
+  if (device >= 0 && device < 64) configured[device] = true;
+  return true;
+}
+
+}  // namespace umma
+}  // namespace nml_sm100

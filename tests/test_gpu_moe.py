@@ -200,3 +200,63 @@ def test_contract_experts_closed_form_inputs(dtype, t, tokens):
     expected = oracle.routed_clamped_swiglu(r(hidden), ids, oracle.to_f32(w16, dtype), gate,
                                             r(gb), down, r(db))
     assert (np.abs(gu.device_f32(out) - expected) <= t + t * np.abs(expected)).all()
+
+
+@pytest.mark.parametrize("tokens,E,k,H,I,dtype", [
+    (1, 8, 4, 512, 384, oracle.BF16),      # sparse schedule form (A <= E), 16-slot tiles
+    (3, 8, 4, 512, 384, oracle.F16),
+    (40, 8, 4, 512, 384, oracle.BF16),     # ~20 slots per expert: 32-slot tiles
+    (100, 8, 4, 512, 384, oracle.BF16),    # ~50: 64-slot tiles
+    (250, 8, 4, 512, 384, oracle.F16),     # ~125: 128-slot tiles
+    (700, 8, 4, 512, 384, oracle.BF16),    # ~350: 256-slot tiles, several slot tiles per expert
+    (96, 32, 4, 2880, 2880, oracle.BF16),  # GPT-OSS widths, 128-row tail tile on the down side
+])
+def test_routed_experts_tensor_core_kernel(tokens, E, k, H, I, dtype):
+    from nml_b200 import _abi
+    mask = None
+    if tokens >= 40:
+        mask = np.ones(tokens, np.uint8)
+        mask[rng(tokens).integers(0, tokens, tokens // 9)] = 0
+    run_routed(tokens, H, E, I, k, dtype, _abi.POLICY_UMMA, seed=tokens + E, mask=mask)
+
+
+def test_tensor_core_experts_match_portable_kernel_with_expert_offset():
+    # Expert-parallel form of the kernel ABI: global expert ids in block_experts, a device
+    # scalar expert_offset, weights of the local experts only; other blocks are skipped.
+    from nml_b200 import ops, _abi
+    import gpu_util as gu
+    dtype = oracle.BF16
+    E, local, offset, H, I, k, tokens = 8, 4, 4, 256, 128, 2, 64
+    gate, down, (gb_bits, gb), (db_bits, db) = make_experts(77, E, H, I, dtype)
+    x_bits, x = make_activation(78, (tokens, H), 1.0, dtype)
+    logits = (rng(79).standard_normal((tokens, E)) * 0.6).astype(np.float32)
+    ids, _, w16 = oracle.route(logits, k, dtype)
+    sl = slice(offset, offset + local)
+    gate_l = gu.parameter("gate", (gate[0][sl], gate[1][sl], gate[2]), H, dtype)
+    down_l = gu.parameter("down", (down[0][sl], down[1][sl], down[2]), I, dtype)
+    d_x = gu.to_device_bits(x_bits, dtype)
+    d_gb = gu.to_device_bits(gb_bits[sl], dtype)
+    d_db = gu.to_device_bits(db_bits[sl], dtype)
+    d_ids = torch.from_numpy(ids).cuda()
+    d_w = gu.to_device_bits(w16, dtype)
+    d_offset = torch.tensor(offset, dtype=torch.int32).cuda()
+    plan = ops.moe_assignment_plan(d_ids.reshape(-1), E)  # global plan, as the reference builds
+    results = {}
+    for policy in (_abi.POLICY_SIMT, _abi.POLICY_UMMA):
+        previous = _abi.set_kernel_policy(policy)
+        try:
+            act = ops.expert_gate_up(d_x, plan, gate_l, d_gb, k, expert_offset=d_offset)
+            out = ops.expert_down(act, plan, down_l, d_db, d_w.reshape(-1), k,
+                                  expert_offset=d_offset, use_active_blocks=False)
+            torch.cuda.synchronize()
+        finally:
+            _abi.set_kernel_policy(previous)
+        results[policy] = (gu.device_f32(act), gu.device_f32(out))
+    assert _abi.device_status(0x1) == 0
+    is_local = (ids.ravel() >= offset) & (ids.ravel() < offset + local)
+    e_act = oracle.expert_gate_up(x, ids.ravel(), k, gate, gb)
+    for policy, (act, out) in results.items():
+        gu.assert_gemm_close(act[is_local], e_act[is_local], f"gate_up policy {policy}")
+        assert (act[~is_local] == 0).all() and (out[~is_local] == 0).all()
+        e_out = oracle.expert_down(act, ids.ravel(), oracle.to_f32(w16, dtype).ravel(), down, db)
+        gu.assert_gemm_close(out[is_local], e_out[is_local], f"down policy {policy}")
