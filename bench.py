@@ -51,6 +51,8 @@ def parse_args():
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass")
     parser.add_argument("--no-detail", action="store_true", help="skip the per-shape table")
+    parser.add_argument("--no-extras", action="store_true",
+                        help="skip the sharded MoE / unembedding / embedding figures")
     parser.add_argument("--rows", type=str, default="",
                         help="comma-separated subset of M values (profiling captures)")
     parser.add_argument("--shapes", type=str, default="",
@@ -366,6 +368,15 @@ def run_ours(args) -> None:
     if not args.no_e2e:
         line["e2e"] = end_to_end(args, cases, weights, activations, outputs, world, barrier,
                                  flops_per_pass)
+    if full_sweep and not args.no_extras:
+        # free the sweep's buffers before the sharded workloads allocate theirs
+        del outputs, activations
+        head = weights.pop("unembed")
+        weights.clear()
+        torch.cuda.empty_cache()
+        extras = sharded_extras(args, rank, world, device, barrier, head, peaks)
+        if rank == 0:
+            line.update(extras)
     if rank == 0:
         if world == 1 and full_sweep:
             line["cpu_baseline"] = time_cpu_baseline()
@@ -466,6 +477,99 @@ def end_to_end(args, cases, weights, activations, outputs, world, barrier, flops
     return {"value": world * flops_per_pass * steps / (elapsed_ms * 1e-3) / 1e12, "unit": UNIT,
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": steps,
             "ms_per_step": elapsed_ms / steps}
+
+
+def timed(fn, warmup, steps, barrier, world):
+    """Device time of `steps` calls of fn in ms per call, max over ranks."""
+    import torch
+    import torch.distributed as dist
+    for _ in range(warmup):
+        fn()
+    barrier()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(steps):
+        fn()
+    end.record()
+    barrier()
+    elapsed = begin.elapsed_time(end) / steps
+    if world > 1:
+        t = torch.tensor([elapsed], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed = float(t.item())
+    return elapsed
+
+
+def sharded_extras(args, rank, world, device, barrier, head, peaks) -> dict:
+    """Figures for the configurations that shard over GPUs (not part of `value`):
+    config 2, the GPT-OSS-20B-shaped routed layer (T=4096, 32 experts, top-4), expert-parallel
+    over the job's ranks with the NCCL token all-to-all (fixed total work: strong scaling);
+    config 3, the packed embedding gather (8192 rows) and the 201088-wide unembedding at
+    M in {1, 64, 1024} column-sharded over the ranks."""
+    import torch
+    from nml_b200 import expert_parallel as ep, ops, quantize
+    out = {}
+    generator = torch.Generator(device=device).manual_seed(99)  # same on every rank
+    hidden_size, inter, experts, top_k, tokens = 2880, 2880, 32, 4, 4096
+
+    def normal(shape, std):
+        return (torch.randn(shape, device=device, generator=generator) * std).to(torch.bfloat16)
+
+    gate_up = quantize.quantize_parameter("gate_up", normal((experts, 2 * inter, hidden_size), 0.02))
+    down = quantize.quantize_parameter("down", normal((experts, hidden_size, inter), 0.02))
+    gate_bias, down_bias = normal((experts, 2 * inter), 0.02), normal((experts, hidden_size), 0.02)
+    router = normal((experts, hidden_size), 0.02)
+    x = normal((tokens, hidden_size), 1.0)
+    logits = (x.float() @ router.float().t()).contiguous()  # dense router, computed once
+    lo, hi = ep.shard_range(tokens, rank, world)
+    layer = ep.LocalExperts.shard(gate_up, gate_bias, down, down_bias, rank, world)
+    del gate_up, down
+    torch.cuda.empty_cache()
+    x_local, logits_local = x[lo:hi].contiguous(), logits[lo:hi].contiguous()
+    moe_flops = 2.0 * tokens * top_k * (2 * inter * hidden_size + hidden_size * inter)
+    for schedule in ("alltoall", "allreduce"):
+        moe = ep.ExpertParallelMoE(layer, top_k, schedule=schedule)
+        ms = timed(lambda: moe(x_local, logits_local), 3, max(args.steps, 5), barrier, world)
+        out[f"moe_{schedule}"] = {
+            "metric": "moe_layer_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
+            "ms_per_layer": ms, "tflops": moe_flops / (ms * 1e-3) / 1e12, "tokens": tokens,
+            "experts": experts, "top_k": top_k, "n_gpus": world, "scaling": "strong",
+            "schedule": schedule, "frac_of_bf16_peak":
+                moe_flops / (ms * 1e-3) / 1e12 / (world * peaks["bf16_tflops_sustained"])}
+    # decode-size batch (config 4's routed layer): 64 tokens
+    x64, l64 = x[:64 // world * world], logits[:64 // world * world]
+    lo, hi = ep.shard_range(x64.shape[0], rank, world)
+    moe = ep.ExpertParallelMoE(layer, top_k, schedule="allreduce")
+    ms = timed(lambda: moe(x64[lo:hi].contiguous(), l64[lo:hi].contiguous()), 3, 20, barrier,
+               world)
+    expert_bytes = experts * (2 * inter * hidden_size + hidden_size * inter) * 0.5625
+    out["moe_decode64"] = {"metric": "moe_layer_tokens_per_s", "value": x64.shape[0] / (ms * 1e-3),
+                           "unit": "tokens/s", "us_per_layer": ms * 1e3, "n_gpus": world,
+                           "schedule": "allreduce",
+                           "weight_gbs_if_all_experts_hit": expert_bytes / (ms * 1e-3) / 1e9}
+    del layer, moe
+    torch.cuda.empty_cache()
+
+    # config 3: embedding gather + column-sharded unembedding on the 201088 x 2880 table
+    ids = torch.randint(0, head.shape[0], (8192,), device=device, generator=generator,
+                        dtype=torch.int32)
+    rows = torch.empty((8192, hidden_size), dtype=torch.bfloat16, device=device)
+    ms = timed(lambda: ops.token_embedding(head, ids, out=rows), 3, 20, barrier, world)
+    gather_bytes = 8192 * (hidden_size // 2 + hidden_size // 16 + 2 * hidden_size + 4)
+    out["embedding_gather"] = {"rows": 8192, "us": ms * 1e3, "gbs": gather_bytes / (ms * 1e-3) / 1e9,
+                               "frac_of_hbm_peak": gather_bytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                               "note": "replicated per rank (rows are gathered where the token lives)"}
+    sharded = ep.ShardedUnembedding(head)
+    out["unembed_sharded"] = []
+    for m in (1, 64, 1024):
+        h = x[:m].contiguous()
+        ms = timed(lambda: sharded(h, gather_rows=False), 3, 10, barrier, world)
+        flops = 2.0 * m * hidden_size * head.shape[0]
+        out["unembed_sharded"].append({
+            "M": m, "n_gpus": world, "us": ms * 1e3, "tflops": flops / (ms * 1e-3) / 1e12,
+            "weight_gbs": head.shape[0] * hidden_size * 0.5625 / (ms * 1e-3) / 1e9,
+            "includes": "local linear on N/G columns + all-gather of the logit columns"})
+    return out
 
 
 def main() -> int:

@@ -232,6 +232,58 @@ typedef struct NmlSm100RoutedSwiglu {
   int32_t dtype;
 } NmlSm100RoutedSwiglu;
 
+/* Expert-parallel dispatch plan.  The reference shards experts by replicating all tokens on
+ * every device and all-reducing partial outputs (crates/nml-ir/src/lib.rs:9596-9728); these
+ * three entry points support the token exchange that replaces it: assignments are grouped by
+ * the rank that owns their expert (rank = id / experts_per_rank, the contiguous placement of
+ * crates/nml-sharding/src/lib.rs:180-213), in rank order and assignment order inside a rank.
+ *   send_order[slot]          assignment index carried by send slot `slot` (-1 past the total)
+ *   local_expert[slot]        expert index on the destination rank
+ *   slot_of_assignment[a]     send slot of assignment a, -1 for masked routes
+ *   send_counts[rank]         rows sent to each rank */
+typedef struct NmlSm100EpDispatchPlan {
+  size_t struct_size;
+  const int32_t *expert_ids;   /* [assignments] global ids, -1 = masked */
+  int32_t *send_order;         /* [assignments] */
+  int32_t *local_expert;       /* [assignments] */
+  int32_t *slot_of_assignment; /* [assignments] */
+  int32_t *send_counts;        /* [ranks] */
+  void *stream;
+  int64_t assignments;
+  int64_t ranks;               /* at most 64 */
+  int64_t experts_per_rank;
+} NmlSm100EpDispatchPlan;
+
+/* Token permute: output[r, :] = source[row_index[r] / index_divisor, :]; a negative index gives
+ * a zero row.  width must be a multiple of 8 and both buffers 16-byte aligned. */
+typedef struct NmlSm100GatherRows {
+  size_t struct_size;
+  const void *source;        /* [source_rows, width] dtype */
+  const int32_t *row_index;  /* [rows] */
+  void *output;              /* [rows, width] dtype */
+  void *stream;
+  int64_t rows;
+  int64_t source_rows;
+  int64_t width;
+  int32_t index_divisor;     /* experts_per_token when indices are assignment ids, else 1 */
+  int32_t dtype;
+} NmlSm100GatherRows;
+
+/* Token unpermute + k-way sum: output[t, :] = sum over routes r (route order, f32, one
+ * narrowing) of rows[row_index[t * k + r], :]; negative indices are skipped. */
+typedef struct NmlSm100CombineRows {
+  size_t struct_size;
+  const void *rows;          /* [row_count, hidden] dtype */
+  const int32_t *row_index;  /* [tokens * k] */
+  void *output;              /* [tokens, hidden] dtype */
+  void *stream;
+  int64_t tokens;
+  int64_t experts_per_token;
+  int64_t hidden_size;
+  int64_t row_count;
+  int32_t dtype;
+} NmlSm100CombineRows;
+
 /* Replaces nml_nvfp4_turing_linear (nml_nvfp4.h:94-96, turing_adapter.cu:669-733). */
 int32_t nml_nvfp4_sm100_linear(const NmlSm100Linear *request, char *error_message,
                                size_t error_message_capacity);
@@ -265,6 +317,15 @@ int32_t nml_nvfp4_sm100_combine(const NmlSm100Combine *request, char *error_mess
 /* Replaces the CPU target "nml.nvfp4.routed_swiglu" (crates/nml-kernel-nvfp4/src/ffi.rs:228-428). */
 int32_t nml_nvfp4_sm100_routed_swiglu(const NmlSm100RoutedSwiglu *request, char *error_message,
                                       size_t error_message_capacity);
+
+/* Expert-parallel token exchange support; together they replace lower_expert_parallel's
+ * replicate-and-all-reduce scheme (crates/nml-ir/src/lib.rs:9596-9728). */
+int32_t nml_nvfp4_sm100_ep_dispatch_plan(const NmlSm100EpDispatchPlan *request,
+                                         char *error_message, size_t error_message_capacity);
+int32_t nml_nvfp4_sm100_gather_rows(const NmlSm100GatherRows *request, char *error_message,
+                                    size_t error_message_capacity);
+int32_t nml_nvfp4_sm100_combine_rows(const NmlSm100CombineRows *request, char *error_message,
+                                     size_t error_message_capacity);
 
 /* Routed clamped-SwiGLU layer for callers that cannot hand over scratch memory.
  *

@@ -100,6 +100,25 @@ class RoutedSwiglu(ctypes.Structure):
                 ("experts_per_token", _i64), ("expert_offset", _i32), ("dtype", _i32)]
 
 
+class EpDispatchPlan(ctypes.Structure):
+    _fields_ = [("struct_size", _sz), ("expert_ids", _vp), ("send_order", _vp),
+                ("local_expert", _vp), ("slot_of_assignment", _vp), ("send_counts", _vp),
+                ("stream", _vp), ("assignments", _i64), ("ranks", _i64),
+                ("experts_per_rank", _i64)]
+
+
+class GatherRows(ctypes.Structure):
+    _fields_ = [("struct_size", _sz), ("source", _vp), ("row_index", _vp), ("output", _vp),
+                ("stream", _vp), ("rows", _i64), ("source_rows", _i64), ("width", _i64),
+                ("index_divisor", _i32), ("dtype", _i32)]
+
+
+class CombineRows(ctypes.Structure):
+    _fields_ = [("struct_size", _sz), ("rows", _vp), ("row_index", _vp), ("output", _vp),
+                ("stream", _vp), ("tokens", _i64), ("experts_per_token", _i64),
+                ("hidden_size", _i64), ("row_count", _i64), ("dtype", _i32)]
+
+
 # name -> request structure, for the entry points of the form fn(const Request*, char*, size_t)
 REQUEST_ENTRY_POINTS = {
     "nml_nvfp4_sm100_linear": Linear,
@@ -111,6 +130,9 @@ REQUEST_ENTRY_POINTS = {
     "nml_nvfp4_sm100_combine": Combine,
     "nml_nvfp4_sm100_routed_swiglu": RoutedSwiglu,
     "nml_nvfp4_sm100_routed_swiglu_static": RoutedSwiglu,
+    "nml_nvfp4_sm100_ep_dispatch_plan": EpDispatchPlan,
+    "nml_nvfp4_sm100_gather_rows": GatherRows,
+    "nml_nvfp4_sm100_combine_rows": CombineRows,
 }
 
 OTHER_ENTRY_POINTS = [

@@ -20,7 +20,7 @@ CSRC = HERE / "csrc"
 LIB_DIR = HERE / "lib"
 LIB_PATH = LIB_DIR / "libnml_nvfp4_sm100.so"
 SOURCES = ["abi.cu", "embedding.cu", "linear_simt.cu", "linear_umma.cu", "moe.cu",
-           "experts_umma.cu"]
+           "experts_umma.cu", "ep.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
@@ -40,15 +40,19 @@ def _stale() -> bool:
     return any(path.stat().st_mtime > built for path in inputs)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    if not force and not _stale():
+def build(force: bool = False, verbose: bool = False, defines=(), output: Path | None = None) -> Path:
+    """Compiles every source and links the shared object.  ``defines`` adds -D flags (for
+    example NML_SM100_PROFILE, the stall-accounting build used when tuning) and ``output``
+    redirects the result so that a tuning build never replaces the product library."""
+    target = Path(output) if output is not None else LIB_PATH
+    if output is None and not defines and not force and not _stale():
         return LIB_PATH
     LIB_DIR.mkdir(exist_ok=True)
     objects = []
     procs = []
     for source in SOURCES:
-        obj = LIB_DIR / (source + ".o")
-        cmd = [nvcc(), *ARCH_FLAGS, "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
+        obj = LIB_DIR / (source + (".tuning.o" if defines else ".o"))
+        cmd = [nvcc(), *ARCH_FLAGS, *[f"-D{d}" for d in defines], "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
                "-Xptxas", "-v" if verbose else "-warn-spills", "-c", str(CSRC / source), "-o",
                str(obj)]
         procs.append((source, subprocess.Popen(cmd, stdout=subprocess.PIPE,
@@ -64,16 +68,18 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             sys.stderr.write(f"--- {source}\n{out}\n")
     if failed:
         raise RuntimeError("nvcc failed")
-    link = [nvcc(), *ARCH_FLAGS, "-shared", "-cudart", "static", "-o", str(LIB_PATH), *objects]
+    link = [nvcc(), *ARCH_FLAGS, "-shared", "-cudart", "static", "-o", str(target), *objects]
     subprocess.run(link, check=True)
     for obj in objects:
         os.unlink(obj)
-    return LIB_PATH
+    return target
 
 
 if __name__ == "__main__":
     parser = argparse.ArgumentParser(description=__doc__)
     parser.add_argument("--force", action="store_true")
     parser.add_argument("--verbose", action="store_true")
+    parser.add_argument("--define", action="append", default=[])
+    parser.add_argument("--output", type=Path, default=None)
     arguments = parser.parse_args()
-    print(build(arguments.force, arguments.verbose))
+    print(build(arguments.force, arguments.verbose, tuple(arguments.define), arguments.output))

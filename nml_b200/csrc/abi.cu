@@ -83,6 +83,18 @@ int32_t launch_combine(const void* weighted, const int32_t* expert_ids, void* ou
                        int top_k, int hidden, int experts, int expert_offset, int dtype,
                        cudaStream_t stream, char* message, size_t capacity);
 
+int32_t launch_ep_dispatch_plan(const int32_t* expert_ids, int32_t* send_order,
+                                int32_t* slot_of_assignment, int32_t* local_expert,
+                                int32_t* send_counts, int assignments, int ranks,
+                                int experts_per_rank, cudaStream_t stream, char* message,
+                                size_t capacity);
+int32_t launch_gather_rows(const void* source, const int32_t* row_index, void* output,
+                           int64_t rows, int width, int divisor, int64_t source_rows, int dtype,
+                           cudaStream_t stream, char* message, size_t capacity);
+int32_t launch_combine_rows(const void* rows, const int32_t* row_index, void* output, int tokens,
+                            int top_k, int width, int64_t row_count, int dtype,
+                            cudaStream_t stream, char* message, size_t capacity);
+
 namespace {
 
 bool valid_dtype(int32_t dtype) { return dtype == NML_SM100_F16 || dtype == NML_SM100_BF16; }
@@ -713,4 +725,94 @@ extern "C" int32_t nml_nvfp4_sm100_routed_swiglu_static(const NmlSm100RoutedSwig
                         static_cast<int>(request->hidden_size),
                         static_cast<int>(request->experts), request->expert_offset,
                         request->dtype, stream, error_message, error_message_capacity);
+}
+
+
+extern "C" int32_t nml_nvfp4_sm100_ep_dispatch_plan(const NmlSm100EpDispatchPlan* request,
+                                                    char* error_message,
+                                                    size_t error_message_capacity) {
+  if (request == nullptr || request->struct_size < sizeof(NmlSm100EpDispatchPlan)) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "truncated NVFP4 dispatch plan request",
+                error_message, error_message_capacity);
+  }
+  if (request->expert_ids == nullptr || request->send_order == nullptr ||
+      request->local_expert == nullptr || request->slot_of_assignment == nullptr ||
+      request->send_counts == nullptr || request->stream == nullptr ||
+      !fits_i32(request->assignments) || request->ranks <= 0 || request->ranks > 64 ||
+      !fits_i32(request->experts_per_rank)) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "invalid NVFP4 dispatch plan request", error_message,
+                error_message_capacity);
+  }
+  if (current_device(error_message, error_message_capacity) == nullptr) {
+    return NML_SM100_LAUNCH_FAILURE;
+  }
+  return launch_ep_dispatch_plan(request->expert_ids, request->send_order,
+                                 request->slot_of_assignment, request->local_expert,
+                                 request->send_counts, static_cast<int>(request->assignments),
+                                 static_cast<int>(request->ranks),
+                                 static_cast<int>(request->experts_per_rank),
+                                 static_cast<cudaStream_t>(request->stream), error_message,
+                                 error_message_capacity);
+}
+
+extern "C" int32_t nml_nvfp4_sm100_gather_rows(const NmlSm100GatherRows* request,
+                                               char* error_message,
+                                               size_t error_message_capacity) {
+  if (request == nullptr || request->struct_size < sizeof(NmlSm100GatherRows)) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "truncated NVFP4 row gather request", error_message,
+                error_message_capacity);
+  }
+  if (request->source == nullptr || request->row_index == nullptr ||
+      request->output == nullptr || request->stream == nullptr || !fits_i32(request->rows) ||
+      !fits_i32(request->source_rows) || !fits_i32(request->width) || request->width % 8 != 0 ||
+      request->index_divisor <= 0 || reinterpret_cast<uintptr_t>(request->source) % 16 != 0 ||
+      reinterpret_cast<uintptr_t>(request->output) % 16 != 0) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "invalid NVFP4 row gather request", error_message,
+                error_message_capacity);
+  }
+  if (!valid_dtype(request->dtype)) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "NVFP4 row gather supports F16 and BF16 only",
+                error_message, error_message_capacity);
+  }
+  if (current_device(error_message, error_message_capacity) == nullptr) {
+    return NML_SM100_LAUNCH_FAILURE;
+  }
+  return launch_gather_rows(request->source, request->row_index, request->output, request->rows,
+                            static_cast<int>(request->width), request->index_divisor,
+                            request->source_rows, request->dtype,
+                            static_cast<cudaStream_t>(request->stream), error_message,
+                            error_message_capacity);
+}
+
+extern "C" int32_t nml_nvfp4_sm100_combine_rows(const NmlSm100CombineRows* request,
+                                                char* error_message,
+                                                size_t error_message_capacity) {
+  if (request == nullptr || request->struct_size < sizeof(NmlSm100CombineRows)) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "truncated NVFP4 row combine request", error_message,
+                error_message_capacity);
+  }
+  if (request->rows == nullptr || request->row_index == nullptr || request->output == nullptr ||
+      request->stream == nullptr || !fits_i32(request->tokens) ||
+      !fits_i32(request->hidden_size) || request->hidden_size % 8 != 0 ||
+      request->experts_per_token <= 0 || request->row_count < 0 ||
+      request->row_count > std::numeric_limits<int32_t>::max() ||
+      request->tokens > std::numeric_limits<int32_t>::max() / request->experts_per_token ||
+      reinterpret_cast<uintptr_t>(request->rows) % 16 != 0 ||
+      reinterpret_cast<uintptr_t>(request->output) % 16 != 0) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "invalid NVFP4 row combine request", error_message,
+                error_message_capacity);
+  }
+  if (!valid_dtype(request->dtype)) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "NVFP4 row combine supports F16 and BF16 only",
+                error_message, error_message_capacity);
+  }
+  if (current_device(error_message, error_message_capacity) == nullptr) {
+    return NML_SM100_LAUNCH_FAILURE;
+  }
+  return launch_combine_rows(request->rows, request->row_index, request->output,
+                             static_cast<int>(request->tokens),
+                             static_cast<int>(request->experts_per_token),
+                             static_cast<int>(request->hidden_size), request->row_count,
+                             request->dtype, static_cast<cudaStream_t>(request->stream),
+                             error_message, error_message_capacity);
 }

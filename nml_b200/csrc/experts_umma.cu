@@ -15,7 +15,7 @@ namespace {
 
 using namespace umma;
 
-template <int BM, int KS, int RAW, int WB, int AFMT, typename T, int MODE>
+template <int BM, int KS, int RAW, int WB, int DG, int AFMT, typename T, int MODE>
 int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* message,
                       size_t capacity) {
   using L = Layout<BM, KS, RAW, WB, true>;
@@ -52,7 +52,7 @@ int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* me
   p.top_k = args.experts_per_token;
   p.status = device.status_word;
 
-  auto kernel = gemm_kernel<BM, KS, RAW, WB, AFMT, T, MODE>;
+  auto kernel = gemm_kernel<BM, KS, RAW, WB, DG, AFMT, T, MODE>;
   static bool configured[64] = {};
   if (!reserve_smem(kernel, L::kSmemBytes, device.device, configured)) {
     return fail(NML_SM100_LAUNCH_FAILURE, "cannot reserve shared memory for the tcgen05 experts",
@@ -63,7 +63,7 @@ int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* me
   const int64_t max_units = slot_tiles * p.n_tiles;
   const unsigned grid =
       static_cast<unsigned>(max_units < device.sm_count ? max_units : device.sm_count);
-  kernel<<<grid, kThreadsGrouped, L::kSmemBytes, args.stream>>>(tmap_payload, tmap_payload, p);
+  kernel<<<grid, Roles<DG>::kThreadsGrouped, L::kSmemBytes, args.stream>>>(tmap_payload, tmap_payload, p);
   return launch_result(message, capacity);
 }
 
@@ -75,18 +75,18 @@ int32_t launch_for_load(const ExpertArgs& args, const DeviceInfo& device, char* 
                               ? 1
                               : (args.assignments + args.experts - 1) / args.experts;
   if (average <= 16) {
-    return launch_config<16, 4, 6, 3, AFMT, T, MODE>(args, device, message, capacity);
+    return launch_config<16, 4, 5, 4, 3, AFMT, T, MODE>(args, device, message, capacity);
   }
   if (average <= 32) {
-    return launch_config<32, 4, 5, 3, AFMT, T, MODE>(args, device, message, capacity);
+    return launch_config<32, 4, 4, 4, 3, AFMT, T, MODE>(args, device, message, capacity);
   }
   if (average <= 64) {
-    return launch_config<64, 4, 3, 3, AFMT, T, MODE>(args, device, message, capacity);
+    return launch_config<64, 4, 3, 4, 3, AFMT, T, MODE>(args, device, message, capacity);
   }
   if (average <= 160) {
-    return launch_config<128, 1, 7, 4, AFMT, T, MODE>(args, device, message, capacity);
+    return launch_config<128, 1, 5, 5, 3, AFMT, T, MODE>(args, device, message, capacity);
   }
-  return launch_config<256, 1, 4, 4, AFMT, T, MODE>(args, device, message, capacity);
+  return launch_config<256, 1, 4, 4, 3, AFMT, T, MODE>(args, device, message, capacity);
 }
 
 template <int MODE>

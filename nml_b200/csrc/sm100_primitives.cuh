@@ -230,6 +230,32 @@ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_address) 
   return desc;
 }
 
+// The same descriptor split in halves: only the low word (start address, leading offset)
+// changes between operand tiles, so an issue loop keeps the high word constant.
+constexpr uint32_t kUmmaDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_address) {
+  return ((smem_address & 0x3ffffu) >> 4) | (1u << 16);
+}
+
+__device__ __forceinline__ void umma_f16_split(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo,
+                                               uint32_t desc_hi, uint32_t idesc,
+                                               bool accumulate) {
+  const uint32_t acc = accumulate ? 1u : 0u;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 da, db;\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "mov.b64 da, {%1, %3};\n"
+      "mov.b64 db, {%2, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n"
+      "}\n"
+      :
+      : "r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(acc)
+      : "memory");
+}
+
 enum UmmaFormat : uint32_t { kUmmaF16 = 0, kUmmaBF16 = 1 };
 
 // Instruction descriptor for kind::f16: f32 accumulator, both operands K-major.

@@ -12,8 +12,8 @@
 //             block-scale bytes by 4-byte cp.async, X tiles [BM x 64] by TMA (dense) or by
 //             16-byte cp.async gathers of scheduled rows (grouped), 128B-swizzled
 //   W' ring   (WB buffers): decoded operand tile [128 x 64], UMMA K-major 128B swizzle
-// Warp roles: 0 producer, 1 MMA issuer + TMEM owner, 2-5 epilogue, 6-13 decode, 14-15 row
-// gather (grouped only).  Accumulators are double-buffered in TMEM; the kernel is persistent.
+// Warp roles: 0 producer, 1 MMA issuer + TMEM owner, 2-5 epilogue, then DG decode groups of
+// four warps, then two row-gather warps (grouped only).  Accumulators are double-buffered in TMEM; the kernel is persistent.
 //
 // Every mbarrier wait is bounded; a wait that runs out sets the barrier-timeout bit of the
 // device status word and all roles leave through the common teardown.
@@ -37,13 +37,21 @@ constexpr int kProducerWarp = 0;
 constexpr int kMmaWarp = 1;
 constexpr int kEpilogueWarps = 4;
 constexpr int kDecodeWarp0 = 6;
-constexpr int kDecodeWarps = 8;
-constexpr int kDecodeThreads = kDecodeWarps * 32;
-constexpr int kGatherWarp0 = kDecodeWarp0 + kDecodeWarps;  // 14
+constexpr int kGroupThreads = 128;  // one decode group: one thread per weight row of the tile
 constexpr int kGatherWarps = 2;
 constexpr int kGatherThreads = kGatherWarps * 32;
-constexpr int kThreadsDense = kGatherWarp0 * 32;                     // 448
-constexpr int kThreadsGrouped = (kGatherWarp0 + kGatherWarps) * 32;  // 512
+
+// Thread budget of a launch with DG decode groups.  Group g decodes the K steps whose
+// sequence number is congruent to g modulo DG, so DG K steps are in decode at once: the
+// decode of one K step is a long dependent instruction chain, and it is the number of
+// chains in flight, not the instruction count, that keeps the tensor pipe fed.
+template <int DG>
+struct Roles {
+  static constexpr int kDecodeWarps = 4 * DG;
+  static constexpr int kGatherWarp0 = kDecodeWarp0 + kDecodeWarps;
+  static constexpr int kThreadsDense = kGatherWarp0 * 32;
+  static constexpr int kThreadsGrouped = (kGatherWarp0 + kGatherWarps) * 32;
+};
 constexpr int kWBytes = kTileN * 128;
 constexpr int kSmemBudget = 227 * 1024;
 constexpr int kMaxGroups = 256;
@@ -278,6 +286,25 @@ __device__ __forceinline__ Unit get_unit(const Params& p, const Groups* groups, 
   return u;
 }
 
+// Stall accounting for tuning, compiled only with -DNML_SM100_PROFILE: cycles each role
+// leader spends in each wait, summed over CTAs into g_profile (read through
+// nml_nvfp4_sm100_profile_read in the translation unit that owns the kernel).
+#ifdef NML_SM100_PROFILE
+static __device__ unsigned long long g_profile[24];
+#define NML_PROF_DECL unsigned long long prof_acc[4] = {0, 0, 0, 0}; long long prof_t0 = 0;
+#define NML_PROF_BEGIN() prof_t0 = clock64()
+#define NML_PROF_END(slot) prof_acc[slot] += static_cast<unsigned long long>(clock64() - prof_t0)
+#define NML_PROF_FLUSH(base, leader)                                        \
+  if (leader) {                                                             \
+    for (int i = 0; i < 4; ++i) atomicAdd(&g_profile[(base) + i], prof_acc[i]); \
+  }
+#else
+#define NML_PROF_DECL
+#define NML_PROF_BEGIN()
+#define NML_PROF_END(slot)
+#define NML_PROF_FLUSH(base, leader)
+#endif
+
 struct RingState {
   int index = 0;
   uint32_t phase = 0;
@@ -292,11 +319,14 @@ struct RingState {
 
 // ---- the kernel ---------------------------------------------------------------------------
 
-template <int BM, int KS, int RAW, int WB, int AFMT, typename T, int MODE>
-__global__ void __launch_bounds__(MODE == kDense ? kThreadsDense : kThreadsGrouped, 1)
+template <int BM, int KS, int RAW, int WB, int DG, int AFMT, typename T, int MODE>
+__global__ void __launch_bounds__(MODE == kDense ? Roles<DG>::kThreadsDense
+                                                 : Roles<DG>::kThreadsGrouped, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
             const __grid_constant__ CUtensorMap tmap_x, const Params p) {
   constexpr bool GROUPED = MODE != kDense;
+  constexpr int kGatherWarp0 = Roles<DG>::kGatherWarp0;
+  static_assert(WB > DG, "the W' ring must hold one tile per decode group plus one");
   using L = Layout<BM, KS, RAW, WB, GROUPED>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -328,7 +358,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       mbar_init(&empty_raw[r], 1);
     }
     for (int w = 0; w < WB; ++w) {
-      mbar_init(&full_w[w], kDecodeThreads);
+      mbar_init(&full_w[w], kGroupThreads);
       mbar_init(&empty_w[w], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -362,24 +392,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
   };
   // Bounded wait that also honours an abort raised by another role.
   auto wait = [&](uint64_t* bar, uint32_t parity) -> bool {
-    if (*abort_flag) return false;
-    if (mbar_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;  // fast path: no shared-memory flag read
+    for (uint32_t poll = 0; poll < kWaitPolls; ++poll) {
+      if (mbar_try_wait(bar, parity)) return true;
+      if ((poll & 63u) == 63u && *abort_flag) return false;
+    }
     give_up();
     return false;
   };
+  // With one K step per raw stage the two rings advance in lockstep, so the commit that
+  // frees a W' buffer also frees the raw stage of the same index: one commit per K step.
+  constexpr bool kSharedEmpty = KS == 1;
+  static_assert(!kSharedEmpty || WB == RAW, "lockstep rings need equal depth");
+  uint64_t* raw_free = kSharedEmpty ? empty_w : empty_raw;
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------------ producer
     RingState raw;
     int issued = 0;
     bool ok = true;
+    NML_PROF_DECL
     for (int index = blockIdx.x; index < units && ok; index += gridDim.x) {
       const Unit u = get_unit<BM, GROUPED>(p, groups, index);
       for (int rs = 0; rs < raw_stages; ++rs) {
-        if (!wait(&empty_raw[raw.index], raw.phase ^ 1u)) {
+        NML_PROF_BEGIN();
+        if (!wait(&raw_free[raw.index], raw.phase ^ 1u)) {
           ok = false;
           break;
         }
+        NML_PROF_END(0);
         if (lane == 0) {
           mbar_arrive_expect_tx(&full_raw[raw.index],
                                 L::kPayloadBytes + (GROUPED ? 0 : KS * L::kXBytes));
@@ -418,6 +459,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       if (raw.index == RAW - 1) raw.phase ^= 1u;
       if (!mbar_wait(&full_raw[raw.index], raw.phase)) give_up();
     }
+    NML_PROF_FLUSH(0, lane == 0)
   } else if (warp == kMmaWarp) {
     // ----------------------------------------------------------------------- MMA
     if (lane == 0) {
@@ -427,39 +469,71 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       RingState raw, wb;
       int local = 0;
       bool ok = true;
+      const uint32_t w_desc_lo = umma_desc_lo(smem_u32(w_tile(0)));
+      const uint32_t x_desc_lo = umma_desc_lo(smem_u32(x_tile(0, 0)));
+      NML_PROF_DECL
+#ifdef NML_SM100_PROFILE
+      const long long prof_start = clock64();
+#endif
       for (int index = blockIdx.x; index < units && ok; index += gridDim.x, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
+        NML_PROF_BEGIN();
         if (!wait(&tmem_empty[acc], acc_phase ^ 1u)) break;
+        NML_PROF_END(0);
         tcgen05_fence_after_sync();
         const uint32_t d_address = tmem_base + acc * BM;
         for (int rs = 0; rs < raw_stages && ok; ++rs) {
+          NML_PROF_BEGIN();
           if (!wait(&full_raw[raw.index], raw.phase)) {
             ok = false;
             break;
           }
+          NML_PROF_END(1);
           const int sub_steps = min(KS, p.k_steps - rs * KS);
           for (int j = 0; j < sub_steps; ++j) {
+            NML_PROF_BEGIN();
             if (!wait(&full_w[wb.index], wb.phase)) {
               ok = false;
               break;
             }
+            NML_PROF_END(2);
+#ifdef NML_SM100_PROFILE
+            const long long issue_t0 = clock64();
+#endif
             tcgen05_fence_after_sync();
-            const uint64_t a_desc = umma_smem_desc_sw128(smem_u32(w_tile(wb.index)));
-            const uint64_t b_desc = umma_smem_desc_sw128(smem_u32(x_tile(raw.index, j)));
+            // Descriptors differ only in the start-address field (16-byte units); each
+            // K=16 slice is 32 bytes further along the swizzled 128-byte rows.
+            const uint32_t a_lo = w_desc_lo + wb.index * (kWBytes >> 4);
+            const uint32_t b_lo =
+                x_desc_lo + raw.index * (L::kRawBytes >> 4) + j * (L::kXBytes >> 4);
 #pragma unroll
             for (int q = 0; q < kTileK / kUmmaK; ++q) {
-              // each K=16 slice is 32 bytes further along the swizzled 128-byte rows
-              umma_f16(d_address, a_desc + 2 * q, b_desc + 2 * q, idesc, (rs | j | q) != 0);
+              umma_f16_split(d_address, a_lo + 2 * q, b_lo + 2 * q, kUmmaDescHiSw128, idesc,
+                             (rs | j | q) != 0);
             }
+#ifdef NML_SM100_PROFILE
+            const long long issue_t1 = clock64();
+#endif
             umma_commit(&empty_w[wb.index]);
+#ifdef NML_SM100_PROFILE
+            const long long issue_t2 = clock64();
+            atomicAdd(&g_profile[16], static_cast<unsigned long long>(issue_t1 - issue_t0));
+            atomicAdd(&g_profile[17], static_cast<unsigned long long>(issue_t2 - issue_t1));
+#endif
             wb.advance<WB>();
           }
-          if (ok) umma_commit(&empty_raw[raw.index]);
+          if constexpr (!kSharedEmpty) {
+            if (ok) umma_commit(&empty_raw[raw.index]);
+          }
           raw.advance<RAW>();
         }
         if (ok) umma_commit(&tmem_full[acc]);
       }
+#ifdef NML_SM100_PROFILE
+      prof_acc[3] = static_cast<unsigned long long>(clock64() - prof_start);
+#endif
+      NML_PROF_FLUSH(4, true)
     }
     __syncwarp();
   } else if (warp < kDecodeWarp0) {
@@ -470,11 +544,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     const T* bias = static_cast<const T*>(p.bias);
     const int row = quarter * 32 + lane;  // row of the weight tile this thread reads
     int local = 0;
+    NML_PROF_DECL
     for (int index = blockIdx.x; index < units; index += gridDim.x, ++local) {
       const Unit u = get_unit<BM, GROUPED>(p, groups, index);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
+      NML_PROF_BEGIN();
       if (!wait(&tmem_full[acc], acc_phase)) break;
+      NML_PROF_END(0);
+      NML_PROF_BEGIN();
       tcgen05_fence_after_sync();
       const int n = u.n0 + row;  // output column (dense, down) or weight row in the expert
       const bool n_ok = n < (MODE == kGateUp ? p.rows_per_expert : p.N);
@@ -547,63 +625,80 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       }
       tcgen05_fence_before_sync();
       mbar_arrive(&tmem_empty[acc]);
+      NML_PROF_END(1);
     }
+    NML_PROF_FLUSH(8, threadIdx.x == 64)
   } else if (warp < kGatherWarp0) {
     // -------------------------------------------------------------------- decode
-    const int t = threadIdx.x - kDecodeWarp0 * 32;  // 0..255
-    const int row = KS == 1 ? (t >> 1) : (t & 127);
-    const int half = KS == 1 ? (t & 1) : (t >> 7);
+    const int dt = threadIdx.x - kDecodeWarp0 * 32;
+    const int group = dt / kGroupThreads;
+    const int row = dt % kGroupThreads;  // weight row of the tile this thread decodes
     RingState raw, wb;
+    int sequence = 0;  // K steps seen so far by this CTA, over all units
     bool ok = true;
+    NML_PROF_DECL
     for (int index = blockIdx.x; index < units && ok; index += gridDim.x) {
       for (int rs = 0; rs < raw_stages && ok; ++rs) {
+        NML_PROF_BEGIN();
         if (!wait(&full_raw[raw.index], raw.phase)) {
           ok = false;
           break;
         }
+        NML_PROF_END(0);
         const int sub_steps = min(KS, p.k_steps - rs * KS);
-        for (int j = 0; j < sub_steps; ++j) {
+        for (int j = 0; j < sub_steps; ++j, ++sequence, wb.advance<WB>()) {
+          if (sequence % DG != group) continue;
+          NML_PROF_BEGIN();
           if (!wait(&empty_w[wb.index], wb.phase ^ 1u)) {
             ok = false;
             break;
           }
-          uint4 codes;
+          NML_PROF_END(1);
+          NML_PROF_BEGIN();
+          uint4 codes[2];
           if constexpr (KS == 1) {
-            codes = *reinterpret_cast<const uint4*>(payload_tile(raw.index) + t * 16);
+            const uint4* source =
+                reinterpret_cast<const uint4*>(payload_tile(raw.index) + row * 32);
+            codes[0] = source[0];
+            codes[1] = source[1];
           } else {
             // rows of 32*KS bytes, 128-byte swizzled by the TMA load
-            codes = *reinterpret_cast<const uint4*>(
-                payload_tile(raw.index) + row * (32 * KS) + (((2 * j + half) ^ (row & 7)) * 16));
+            const uint8_t* source = payload_tile(raw.index) + row * (32 * KS);
+            codes[0] = *reinterpret_cast<const uint4*>(source + (((2 * j) ^ (row & 7)) * 16));
+            codes[1] = *reinterpret_cast<const uint4*>(source + (((2 * j + 1) ^ (row & 7)) * 16));
           }
-          const uint32_t two_scales = *reinterpret_cast<const uint16_t*>(
-              scale_tile(raw.index) + row * (4 * KS) + j * 4 + half * 2);
-          uint32_t scale_a, scale_b;
+          const uint32_t four_scales = *reinterpret_cast<const uint32_t*>(
+              scale_tile(raw.index) + row * (4 * KS) + j * 4);
+          uint32_t scale[4];
           if constexpr (AFMT == kAf16) {
-            scales2_f16(two_scales, scale_a, scale_b);
+            scales2_f16(four_scales & 0xffffu, scale[0], scale[1]);
+            scales2_f16(four_scales >> 16, scale[2], scale[3]);
           } else {
-            scale_a = scale_bf16_dup(two_scales & 0xffu);
-            scale_b = scale_bf16_dup(two_scales >> 8);
+#pragma unroll
+            for (int b = 0; b < 4; ++b) scale[b] = scale_bf16_dup((four_scales >> (8 * b)) & 0xffu);
           }
           uint8_t* w_row = w_tile(wb.index) + row * 128;
-          const uint32_t words[4] = {codes.x, codes.y, codes.z, codes.w};
+          const uint32_t words[8] = {codes[0].x, codes[0].y, codes[0].z, codes[0].w,
+                                     codes[1].x, codes[1].y, codes[1].z, codes[1].w};
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
+          for (int jj = 0; jj < 8; ++jj) {
             uint32_t o[4];
             if constexpr (AFMT == kAf16) {
-              decode8_f16(words[jj], jj < 2 ? scale_a : scale_b, o);
+              decode8_f16(words[jj], scale[jj >> 1], o);
             } else {
-              decode8_bf16(words[jj], jj < 2 ? scale_a : scale_b, o);
+              decode8_bf16(words[jj], scale[jj >> 1], o);
             }
-            const int chunk = (half * 4 + jj) ^ (row & 7);
+            const int chunk = jj ^ (row & 7);
             *reinterpret_cast<uint4*>(w_row + chunk * 16) = make_uint4(o[0], o[1], o[2], o[3]);
           }
           fence_proxy_async_smem();
           mbar_arrive(&full_w[wb.index]);
-          wb.advance<WB>();
+          NML_PROF_END(2);
         }
         raw.advance<RAW>();
       }
     }
+    NML_PROF_FLUSH(12, dt == 0)
   } else {
     // -------------------------------------------------------------------- gather
     if constexpr (GROUPED) {
@@ -649,7 +744,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         }
         __syncwarp();
         for (int rs = 0; rs < raw_stages; ++rs) {
-          if (!wait(&empty_raw[raw.index], raw.phase ^ 1u)) {
+          if (!wait(&raw_free[raw.index], raw.phase ^ 1u)) {
             ok = false;
             break;
           }

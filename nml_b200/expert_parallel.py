@@ -1,0 +1,268 @@
+"""Expert-parallel routed layer and column-sharded unembedding over one process per GPU.
+
+Placement follows the reference's contiguous rule for sharded axes
+(crates/nml-sharding/src/lib.rs:180-213): rank r of G owns experts [r*E/G, (r+1)*E/G) and
+output columns [r*N/G, (r+1)*N/G).  The reference executes sharded experts by replicating all
+tokens on every device and all-reducing the partial outputs
+(crates/nml-ir/src/lib.rs:9596-9728).  Two schedules are provided:
+
+``alltoall``  tokens stay sharded by batch; each routed assignment travels to the rank that
+              owns its expert and back (two NCCL all-to-all-v), the owner computes only rows
+              routed to it, and the token's home rank sums its k returned rows in route order.
+              Every per-assignment row is produced by the same kernels as on one GPU, so the
+              result equals the single-GPU result bit for bit.
+``allreduce`` the reference's scheme: hidden states are all-gathered, every rank runs its local
+              experts over all tokens and partial outputs are summed with an all-reduce.  No
+              host synchronisation; meant for decode-size batches.
+
+The device work (routing, dispatch plan, row gather, expert projections, indexed combine) goes
+through the C ABI.  ``backend`` exists so that the distributed logic can be exercised by CPU
+ranks over gloo with a stand-in for those device calls; the product backend is
+``CudaBackend`` and there is no CPU implementation in this package.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from . import _abi, ops
+
+
+def shard_range(extent: int, rank: int, world: int) -> tuple[int, int]:
+    """Contiguous shard [start, stop) of an axis; the extent must divide evenly
+    (crates/nml-sharding/src/lib.rs:152-158)."""
+    if extent % world != 0:
+        raise ValueError(f"axis extent {extent} does not divide evenly over {world} devices")
+    length = extent // world
+    return rank * length, (rank + 1) * length
+
+
+class CudaBackend:
+    """Device operations of the expert-parallel layer, all through the C ABI."""
+
+    def route(self, logits, top_k, dtype, active):
+        return ops.route(logits, top_k, dtype, active)
+
+    def dispatch_plan(self, expert_ids: torch.Tensor, ranks: int, experts_per_rank: int):
+        assignments = expert_ids.numel()
+        device = expert_ids.device
+        send_order = torch.empty(assignments, dtype=torch.int32, device=device)
+        local_expert = torch.empty(assignments, dtype=torch.int32, device=device)
+        slot_of = torch.empty(assignments, dtype=torch.int32, device=device)
+        counts = torch.empty(ranks, dtype=torch.int32, device=device)
+        request = _abi.EpDispatchPlan(
+            expert_ids=expert_ids.data_ptr(), send_order=send_order.data_ptr(),
+            local_expert=local_expert.data_ptr(), slot_of_assignment=slot_of.data_ptr(),
+            send_counts=counts.data_ptr(), stream=ops._stream(expert_ids),
+            assignments=assignments, ranks=ranks, experts_per_rank=experts_per_rank)
+        _abi.call("nml_nvfp4_sm100_ep_dispatch_plan", request)
+        return send_order, local_expert, slot_of, counts
+
+    def gather_rows(self, source: torch.Tensor, row_index: torch.Tensor, divisor: int):
+        rows, width = row_index.numel(), source.shape[1]
+        out = torch.empty((rows, width), dtype=source.dtype, device=source.device)
+        if rows == 0:
+            return out
+        request = _abi.GatherRows(source=source.data_ptr(), row_index=row_index.data_ptr(),
+                                  output=out.data_ptr(), stream=ops._stream(source), rows=rows,
+                                  source_rows=source.shape[0], width=width,
+                                  index_divisor=divisor, dtype=ops._code(source.dtype))
+        _abi.call("nml_nvfp4_sm100_gather_rows", request)
+        return out
+
+    def combine_rows(self, rows: torch.Tensor, row_index: torch.Tensor, tokens: int, top_k: int):
+        out = torch.empty((tokens, rows.shape[1]), dtype=rows.dtype, device=rows.device)
+        source = rows if rows.shape[0] > 0 else torch.zeros((1, rows.shape[1]), dtype=rows.dtype,
+                                                            device=rows.device)
+        request = _abi.CombineRows(rows=source.data_ptr(), row_index=row_index.data_ptr(),
+                                   output=out.data_ptr(), stream=ops._stream(rows),
+                                   tokens=tokens, experts_per_token=top_k,
+                                   hidden_size=rows.shape[1], row_count=rows.shape[0],
+                                   dtype=ops._code(rows.dtype))
+        _abi.call("nml_nvfp4_sm100_combine_rows", request)
+        return out
+
+    def routed_experts(self, hidden, expert_ids, routing_weights, layer, expert_offset=0):
+        return ops.routed_experts(hidden, expert_ids, routing_weights, layer.gate_up,
+                                  layer.gate_up_bias, layer.down, layer.down_bias,
+                                  expert_offset=expert_offset)
+
+    def linear(self, hidden, weight, bias=None):
+        return ops.linear(hidden, weight, bias)
+
+
+@dataclass
+class LocalExperts:
+    """The expert parameters one rank holds (slices on axis 0 of the global tensors)."""
+
+    gate_up: object       # NvFp4Parameter [L, 2I, H]
+    gate_up_bias: object  # [L, 2I]
+    down: object          # NvFp4Parameter [L, H, I]
+    down_bias: object     # [L, H]
+    experts_total: int
+    expert_offset: int
+
+    @property
+    def experts_local(self) -> int:
+        return self.gate_up_bias.shape[0]
+
+    @staticmethod
+    def shard(gate_up, gate_up_bias, down, down_bias, rank: int, world: int) -> "LocalExperts":
+        """Slices global (replicated) expert parameters for ``rank``."""
+        experts = gate_up_bias.shape[0]
+        start, stop = shard_range(experts, rank, world)
+        return LocalExperts(gate_up.slice_rows(start, stop), gate_up_bias[start:stop].contiguous(),
+                            down.slice_rows(start, stop), down_bias[start:stop].contiguous(),
+                            experts, start)
+
+
+class ExpertParallelMoE:
+    """Routed clamped-SwiGLU layer with experts sharded over the ranks of ``group``.
+
+    ``forward(hidden, router_logits)`` takes this rank's tokens ``[T_local, H]`` and their
+    f32 router logits ``[T_local, E]`` (the router is a replicated dense linear) and returns
+    this rank's output rows ``[T_local, H]``.
+    """
+
+    def __init__(self, layer: LocalExperts, experts_per_token: int, group=None,
+                 schedule: str = "alltoall", backend=None):
+        if schedule not in ("alltoall", "allreduce"):
+            raise ValueError("schedule must be 'alltoall' or 'allreduce'")
+        self.layer = layer
+        self.top_k = experts_per_token
+        self.group = group
+        self.schedule = schedule
+        self.backend = backend or CudaBackend()
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if layer.experts_total != layer.experts_local * self.world:
+            raise ValueError("expert count must divide evenly over the devices of the group")
+        if layer.expert_offset != self.rank * layer.experts_local:
+            raise ValueError("local experts must be the contiguous shard of this rank")
+        self.last_counts = None  # (rows sent per rank, rows received per rank) of the last call
+
+    # ------------------------------------------------------------------ all-to-all
+    def _forward_alltoall(self, hidden, router_logits, active_tokens):
+        backend, group, k = self.backend, self.group, self.top_k
+        tokens, width = hidden.shape
+        ids, weights = backend.route(router_logits, k, hidden.dtype, active_tokens)
+        order, local_expert, slot_of, counts = backend.dispatch_plan(
+            ids.reshape(-1), self.world, self.layer.experts_local)
+        recv_counts = torch.empty_like(counts)
+        if self.world > 1:
+            dist.all_to_all_single(recv_counts, counts, group=group)
+        else:
+            recv_counts.copy_(counts)
+        # NCCL needs the split sizes on the host: the one synchronisation of this schedule.
+        send_c = [int(c) for c in counts.cpu().tolist()]
+        recv_c = [int(c) for c in recv_counts.cpu().tolist()]
+        self.last_counts = (send_c, recv_c)
+        n_send, n_recv = sum(send_c), sum(recv_c)
+
+        send_rows = backend.gather_rows(hidden, order[:n_send], k)  # token permute
+        flat_weights = weights.reshape(-1).view(torch.int16)
+        send_meta = torch.stack(
+            [local_expert[:n_send],
+             flat_weights.index_select(0, order[:n_send].long()).to(torch.int32)], dim=1
+        ).contiguous()
+        recv_rows = torch.empty((n_recv, width), dtype=hidden.dtype, device=hidden.device)
+        recv_meta = torch.empty((n_recv, 2), dtype=torch.int32, device=hidden.device)
+        if self.world > 1:
+            dist.all_to_all_single(recv_rows, send_rows, recv_c, send_c, group=group)
+            dist.all_to_all_single(recv_meta, send_meta, recv_c, send_c, group=group)
+        else:
+            recv_rows, recv_meta = send_rows, send_meta
+
+        if n_recv > 0:
+            recv_ids = recv_meta[:, 0].contiguous().reshape(n_recv, 1)
+            recv_weights = recv_meta[:, 1].to(torch.int16).view(hidden.dtype).reshape(n_recv, 1)
+            computed = backend.routed_experts(recv_rows, recv_ids, recv_weights.contiguous(),
+                                              self.layer)
+        else:
+            computed = recv_rows
+        returned = torch.empty((n_send, width), dtype=hidden.dtype, device=hidden.device)
+        if self.world > 1:
+            dist.all_to_all_single(returned, computed, send_c, recv_c, group=group)
+        else:
+            returned = computed
+        return backend.combine_rows(returned, slot_of, tokens, k)  # unpermute + k-way sum
+
+    # ------------------------------------------------------------------ all-reduce
+    def _forward_allreduce(self, hidden, router_logits, active_tokens):
+        backend, group, k = self.backend, self.group, self.top_k
+        tokens, width = hidden.shape
+        ids, weights = backend.route(router_logits, k, hidden.dtype, active_tokens)
+        if self.world > 1:
+            all_hidden = torch.empty((self.world * tokens, width), dtype=hidden.dtype,
+                                     device=hidden.device)
+            all_ids = torch.empty((self.world * tokens, k), dtype=ids.dtype, device=ids.device)
+            all_weights = torch.empty((self.world * tokens, k), dtype=weights.dtype,
+                                      device=weights.device)
+            dist.all_gather_into_tensor(all_hidden, hidden.contiguous(), group=group)
+            dist.all_gather_into_tensor(all_ids, ids, group=group)
+            dist.all_gather_into_tensor(all_weights, weights, group=group)
+        else:
+            all_hidden, all_ids, all_weights = hidden, ids, weights
+        partial = backend.routed_experts(all_hidden, all_ids, all_weights, self.layer,
+                                         expert_offset=self.layer.expert_offset)
+        if self.world > 1:
+            dist.all_reduce(partial, group=group)
+            return partial[self.rank * tokens:(self.rank + 1) * tokens].contiguous()
+        return partial
+
+    def forward(self, hidden: torch.Tensor, router_logits: torch.Tensor,
+                active_tokens: torch.Tensor | None = None) -> torch.Tensor:
+        if hidden.dim() != 2 or router_logits.dim() != 2 or \
+                router_logits.shape[0] != hidden.shape[0] or \
+                router_logits.shape[1] != self.layer.experts_total:
+            raise ValueError("routing tensors do not match the token and hidden extents")
+        if self.schedule == "alltoall":
+            return self._forward_alltoall(hidden, router_logits, active_tokens)
+        return self._forward_allreduce(hidden, router_logits, active_tokens)
+
+    __call__ = forward
+
+
+class ShardedUnembedding:
+    """The vocabulary projection with output columns sharded over the ranks of ``group``.
+
+    Rank r holds rows [r*N/G, (r+1)*N/G) of the packed table (payload and block scales sliced
+    on axis 0, global scale replicated).  ``forward`` all-gathers the batch-sharded hidden
+    rows, runs the local linear and all-gathers the logit columns; every logit is produced by
+    the same kernel as on one GPU, so the result is bit-identical to the unsharded call.
+    """
+
+    def __init__(self, weight, group=None, backend=None, already_sharded: bool = False):
+        self.group = group
+        self.backend = backend or CudaBackend()
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if already_sharded:
+            self.weight = weight
+            self.columns_total = weight.shape[0] * self.world
+        else:
+            start, stop = shard_range(weight.shape[0], self.rank, self.world)
+            self.weight = weight.slice_rows(start, stop)
+            self.columns_total = weight.shape[0]
+
+    def forward(self, hidden: torch.Tensor, gather_rows: bool = True,
+                gather_columns: bool = True) -> torch.Tensor:
+        rows = hidden.shape[0]
+        if self.world > 1 and gather_rows:
+            all_hidden = torch.empty((self.world * rows, hidden.shape[1]), dtype=hidden.dtype,
+                                     device=hidden.device)
+            dist.all_gather_into_tensor(all_hidden, hidden.contiguous(), group=self.group)
+        else:
+            all_hidden = hidden
+        local = self.backend.linear(all_hidden, self.weight)  # [rows_total, N / G]
+        if self.world == 1 or not gather_columns:
+            return local
+        gathered = torch.empty((self.world * local.shape[0], local.shape[1]), dtype=local.dtype,
+                               device=local.device)
+        dist.all_gather_into_tensor(gathered, local.contiguous(), group=self.group)
+        return gathered.view(self.world, local.shape[0], local.shape[1]).permute(
+            1, 0, 2).reshape(local.shape[0], self.columns_total)
+
+    __call__ = forward
