@@ -256,6 +256,9 @@ def run_ours(args) -> None:
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
+        # NCCL prints its version banner on stdout at any NCCL_DEBUG level; the contract is
+        # one JSON line on stdout.
+        os.environ.pop("NCCL_DEBUG", None)
         dist.init_process_group("nccl", device_id=device)
     _abi.load()
     shapes, rows = select(args)

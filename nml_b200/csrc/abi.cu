@@ -134,7 +134,11 @@ size_t align_up(size_t value, size_t alignment) {
 
 struct RoutedWorkspace {
   size_t sorted_offset, block_experts_offset, active_offset, activated_offset, weighted_offset;
-  size_t total;
+  size_t total;           // bytes of the assignment-ordered layout (gathered rows)
+  // Slot-ordered layout used for large batches: hidden rows permuted into schedule-slot order
+  // and the activations kept in slot order, so both projections read contiguous rows by TMA.
+  size_t permuted_offset, slot_activated_offset;
+  size_t total_permuted;  // bytes including the two slot-ordered regions
   int64_t blocks, positions;
 };
 
@@ -156,8 +160,17 @@ bool routed_workspace(int64_t tokens, int64_t hidden, int64_t intermediate, int6
   w->weighted_offset = offset;
   offset = align_up(offset + static_cast<size_t>(assignments) * hidden * 2, 256);
   w->total = offset;
+  w->permuted_offset = offset;
+  offset = align_up(offset + static_cast<size_t>(w->positions) * hidden * 2, 256);
+  w->slot_activated_offset = offset;
+  offset = align_up(offset + static_cast<size_t>(w->positions) * intermediate * 2, 256);
+  w->total_permuted = offset;
   return true;
 }
+
+// Batches with more than this many expected slots per expert use the slot-ordered layout
+// when the workspace has room for it.
+constexpr int64_t kPermuteThreshold = 64;
 
 template <typename Request>
 bool has_field(const Request* request, size_t offset, size_t size) {
@@ -486,9 +499,10 @@ extern "C" size_t nml_nvfp4_sm100_routed_swiglu_workspace_bytes(int64_t tokens,
                                                                 int64_t experts,
                                                                 int64_t experts_per_token) {
   RoutedWorkspace w;
-  return routed_workspace(tokens, hidden_size, intermediate_size, experts, experts_per_token, &w)
-             ? w.total
-             : 0;
+  if (!routed_workspace(tokens, hidden_size, intermediate_size, experts, experts_per_token, &w)) {
+    return 0;
+  }
+  return tokens * experts_per_token > kPermuteThreshold * experts ? w.total_permuted : w.total;
 }
 
 extern "C" int32_t nml_nvfp4_sm100_routed_swiglu(const NmlSm100RoutedSwiglu* request,
@@ -555,6 +569,9 @@ extern "C" int32_t nml_nvfp4_sm100_routed_swiglu(const NmlSm100RoutedSwiglu* req
   args.experts_per_token = static_cast<int>(request->experts_per_token);
   args.dtype = request->dtype;
 
+  args.inputs = static_cast<int>(request->hidden_size);
+  args.outputs = static_cast<int>(request->intermediate_size);
+  args.gate_up = true;
   args.input = request->hidden;
   args.payload = request->gate_payload;
   args.block_scales = request->gate_scales;
@@ -562,13 +579,35 @@ extern "C" int32_t nml_nvfp4_sm100_routed_swiglu(const NmlSm100RoutedSwiglu* req
   args.bias = request->gate_bias;
   args.routing_weights = nullptr;
   args.output = activated;
-  args.inputs = static_cast<int>(request->hidden_size);
-  args.outputs = static_cast<int>(request->intermediate_size);
-  args.gate_up = true;
-  status = dispatch_experts(args, *device, error_message, error_message_capacity);
-  if (status != NML_SM100_OK) return status;
+  // Large batches: permute the hidden rows into slot order once (token permute) so that both
+  // projections stream contiguous rows by TMA instead of gathering through the load/store
+  // unit; the result rows go back to assignment order in the down epilogue (unpermute).
+  const bool slot_ordered =
+      static_cast<int64_t>(assignments) > kPermuteThreshold * request->experts &&
+      request->workspace_bytes >= w.total_permuted && get_kernel_policy() != 1 &&
+      experts_umma_supported(args) && request->hidden_size % 8 == 0 &&
+      request->intermediate_size % 64 == 0 &&
+      reinterpret_cast<uintptr_t>(request->hidden) % 16 == 0;
+  if (slot_ordered) {
+    void* permuted = base + w.permuted_offset;
+    void* slot_activated = base + w.slot_activated_offset;
+    status = launch_gather_rows(request->hidden, sorted, permuted, w.positions,
+                                static_cast<int>(request->hidden_size),
+                                static_cast<int>(request->experts_per_token), request->tokens,
+                                request->dtype, stream, error_message, error_message_capacity);
+    if (status != NML_SM100_OK) return status;
+    args.input = permuted;
+    args.output = slot_activated;
+    args.slot_input = true;
+    status = launch_experts_umma(args, *device, error_message, error_message_capacity);
+    if (status != NML_SM100_OK) return status;
+    args.input = slot_activated;
+  } else {
+    status = dispatch_experts(args, *device, error_message, error_message_capacity);
+    if (status != NML_SM100_OK) return status;
+    args.input = activated;
+  }
 
-  args.input = activated;
   args.payload = request->down_payload;
   args.block_scales = request->down_scales;
   args.global_scale = request->down_global;
@@ -578,6 +617,11 @@ extern "C" int32_t nml_nvfp4_sm100_routed_swiglu(const NmlSm100RoutedSwiglu* req
   args.inputs = static_cast<int>(request->intermediate_size);
   args.outputs = static_cast<int>(request->hidden_size);
   args.gate_up = false;
+  if (slot_ordered && !experts_umma_supported(args)) {
+    return fail(NML_SM100_INVALID_ARGUMENT,
+                "NVFP4 routed SwiGLU: the down projection cannot read slot-ordered rows",
+                error_message, error_message_capacity);
+  }
   status = dispatch_experts(args, *device, error_message, error_message_capacity);
   if (status != NML_SM100_OK) return status;
 

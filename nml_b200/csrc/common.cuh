@@ -159,6 +159,9 @@ struct ExpertArgs {
   int experts, experts_per_token;
   int dtype;
   bool gate_up;      // true: two weight rows per output column + SwiGLU; false: down
+  // Orchestrated layer only: `input` holds one row per schedule slot (rows permuted into slot
+  // order); gate/up then also writes its result rows in slot order.
+  bool slot_input = false;
 };
 
 int32_t launch_experts_simt(const ExpertArgs& args, const DeviceInfo& device, char* message,

@@ -15,15 +15,25 @@ namespace {
 
 using namespace umma;
 
-template <int BM, int KS, int RAW, int WB, int DG, int AFMT, typename T, int MODE>
+template <int BM, int KS, int RAW, int WB, int DG, int AFMT, typename T, int MODE, bool XTMA>
 int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* message,
                       size_t capacity) {
   using L = Layout<BM, KS, RAW, WB, true>;
   const int rows_per_expert = args.gate_up ? 2 * args.outputs : args.outputs;
   const int64_t weight_rows = static_cast<int64_t>(args.experts) * rows_per_expert;
-  CUtensorMap tmap_payload;
+  CUtensorMap tmap_payload, tmap_x;
   if (!encode_payload_map<KS>(&tmap_payload, args.payload, weight_rows, args.inputs)) {
     return fail(NML_SM100_LAUNCH_FAILURE, "tensor map encoding failed", message, capacity);
+  }
+  if constexpr (XTMA) {
+    // rows of the input are schedule slots
+    if (!encode_activation_map<T>(&tmap_x, args.input,
+                                  static_cast<int64_t>(args.schedule_blocks) * 16, args.inputs,
+                                  BM)) {
+      return fail(NML_SM100_LAUNCH_FAILURE, "tensor map encoding failed", message, capacity);
+    }
+  } else {
+    tmap_x = tmap_payload;  // unused
   }
   Params p = {};
   p.block_scales = args.block_scales;
@@ -52,7 +62,7 @@ int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* me
   p.top_k = args.experts_per_token;
   p.status = device.status_word;
 
-  auto kernel = gemm_kernel<BM, KS, RAW, WB, DG, AFMT, T, MODE>;
+  auto kernel = gemm_kernel<BM, KS, RAW, WB, DG, AFMT, T, MODE, XTMA>;
   static bool configured[64] = {};
   if (!reserve_smem(kernel, L::kSmemBytes, device.device, configured)) {
     return fail(NML_SM100_LAUNCH_FAILURE, "cannot reserve shared memory for the tcgen05 experts",
@@ -63,11 +73,12 @@ int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* me
   const int64_t max_units = slot_tiles * p.n_tiles;
   const unsigned grid =
       static_cast<unsigned>(max_units < device.sm_count ? max_units : device.sm_count);
-  kernel<<<grid, Roles<DG>::kThreadsGrouped, L::kSmemBytes, args.stream>>>(tmap_payload, tmap_payload, p);
+  kernel<<<grid, XTMA ? Roles<DG>::kThreadsDense : Roles<DG>::kThreadsGrouped, L::kSmemBytes,
+           args.stream>>>(tmap_payload, tmap_x, p);
   return launch_result(message, capacity);
 }
 
-template <int AFMT, typename T, int MODE>
+template <int AFMT, typename T, int MODE, bool XTMA>
 int32_t launch_for_load(const ExpertArgs& args, const DeviceInfo& device, char* message,
                         size_t capacity) {
   // Expected slots per expert under balanced routing decide the slot-tile height.
@@ -75,27 +86,33 @@ int32_t launch_for_load(const ExpertArgs& args, const DeviceInfo& device, char* 
                               ? 1
                               : (args.assignments + args.experts - 1) / args.experts;
   if (average <= 16) {
-    return launch_config<16, 4, 5, 4, 3, AFMT, T, MODE>(args, device, message, capacity);
+    return launch_config<16, 4, 5, 4, 2, AFMT, T, MODE, XTMA>(args, device, message, capacity);
   }
   if (average <= 32) {
-    return launch_config<32, 4, 4, 4, 3, AFMT, T, MODE>(args, device, message, capacity);
+    return launch_config<32, 4, 4, 4, 2, AFMT, T, MODE, XTMA>(args, device, message, capacity);
   }
   if (average <= 64) {
-    return launch_config<64, 4, 3, 4, 3, AFMT, T, MODE>(args, device, message, capacity);
+    return launch_config<64, 4, 3, 4, 2, AFMT, T, MODE, XTMA>(args, device, message, capacity);
   }
   if (average <= 160) {
-    return launch_config<128, 1, 5, 5, 3, AFMT, T, MODE>(args, device, message, capacity);
+    return launch_config<128, 1, 5, 5, 2, AFMT, T, MODE, XTMA>(args, device, message, capacity);
   }
-  return launch_config<256, 1, 4, 4, 3, AFMT, T, MODE>(args, device, message, capacity);
+  return launch_config<256, 1, 4, 4, 2, AFMT, T, MODE, XTMA>(args, device, message, capacity);
 }
 
 template <int MODE>
 int32_t launch_mode(const ExpertArgs& args, const DeviceInfo& device, char* message,
                     size_t capacity) {
-  if (args.dtype == NML_SM100_F16) {
-    return launch_for_load<kAf16, __half, MODE>(args, device, message, capacity);
+  if (args.slot_input) {
+    if (args.dtype == NML_SM100_F16) {
+      return launch_for_load<kAf16, __half, MODE, true>(args, device, message, capacity);
+    }
+    return launch_for_load<kAbf16, __nv_bfloat16, MODE, true>(args, device, message, capacity);
   }
-  return launch_for_load<kAbf16, __nv_bfloat16, MODE>(args, device, message, capacity);
+  if (args.dtype == NML_SM100_F16) {
+    return launch_for_load<kAf16, __half, MODE, false>(args, device, message, capacity);
+  }
+  return launch_for_load<kAbf16, __nv_bfloat16, MODE, false>(args, device, message, capacity);
 }
 
 }  // namespace
@@ -114,5 +131,14 @@ int32_t launch_experts_umma(const ExpertArgs& args, const DeviceInfo& device, ch
   return args.gate_up ? launch_mode<kGateUp>(args, device, message, capacity)
                       : launch_mode<kDown>(args, device, message, capacity);
 }
+
+#ifdef NML_SM100_PROFILE
+// Reads and clears the stall counters of the grouped kernels (tuning builds only).
+extern "C" int nml_nvfp4_sm100_profile_read_experts(unsigned long long* out24) {
+  unsigned long long zero[24] = {};
+  if (cudaMemcpyFromSymbol(out24, umma::g_profile, sizeof(zero)) != cudaSuccess) return 1;
+  return cudaMemcpyToSymbol(umma::g_profile, zero, sizeof(zero)) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 }  // namespace nml_sm100

@@ -41,7 +41,7 @@ int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* me
   p.output = args.output;
   p.status = device.status_word;
 
-  auto kernel = gemm_kernel<BM, KS, RAW, WB, DG, AFMT, T, kDense>;
+  auto kernel = gemm_kernel<BM, KS, RAW, WB, DG, AFMT, T, kDense, true>;
   static bool configured[64] = {};
   if (!reserve_smem(kernel, L::kSmemBytes, device.device, configured)) {
     return fail(NML_SM100_LAUNCH_FAILURE, "cannot reserve shared memory for the tcgen05 linear",

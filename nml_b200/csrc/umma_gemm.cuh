@@ -13,7 +13,7 @@
 //             16-byte cp.async gathers of scheduled rows (grouped), 128B-swizzled
 //   W' ring   (WB buffers): decoded operand tile [128 x 64], UMMA K-major 128B swizzle
 // Warp roles: 0 producer, 1 MMA issuer + TMEM owner, 2-5 epilogue, then DG decode groups of
-// four warps, then two row-gather warps (grouped only).  Accumulators are double-buffered in TMEM; the kernel is persistent.
+// four warps, then four row-gather warps (grouped only).  Accumulators are double-buffered in TMEM; the kernel is persistent.
 //
 // Every mbarrier wait is bounded; a wait that runs out sets the barrier-timeout bit of the
 // device status word and all roles leave through the common teardown.
@@ -38,7 +38,7 @@ constexpr int kMmaWarp = 1;
 constexpr int kEpilogueWarps = 4;
 constexpr int kDecodeWarp0 = 6;
 constexpr int kGroupThreads = 128;  // one decode group: one thread per weight row of the tile
-constexpr int kGatherWarps = 2;
+constexpr int kGatherWarps = 4;
 constexpr int kGatherThreads = kGatherWarps * 32;
 
 // Thread budget of a launch with DG decode groups.  Group g decodes the K steps whose
@@ -65,7 +65,9 @@ struct Layout {
   static constexpr int kRawOffset = WB * kWBytes;
   static constexpr int kBarrierOffset = kRawOffset + RAW * kRawBytes;
   static constexpr int kBarrierBytes = 2048;
-  static constexpr int kGroupBytes = GROUPED ? (kMaxGroups * 16 + 64) : 0;
+  // grouped: group table + one slot table (assignment id, routing weight) per epilogue warp
+  static constexpr int kSlotTableBytes = GROUPED ? kEpilogueWarps * BM * 6 : 0;
+  static constexpr int kGroupBytes = GROUPED ? (kMaxGroups * 16 + 64) + kSlotTableBytes : 0;
   static constexpr int kSmemBytes = kBarrierOffset + kBarrierBytes + kGroupBytes + 1024;
   static constexpr int kTmemColumns = 2 * BM < 32 ? 32 : 2 * BM;
   static_assert(kSmemBytes <= kSmemBudget, "shared memory budget exceeded");
@@ -319,14 +321,18 @@ struct RingState {
 
 // ---- the kernel ---------------------------------------------------------------------------
 
-template <int BM, int KS, int RAW, int WB, int DG, int AFMT, typename T, int MODE>
-__global__ void __launch_bounds__(MODE == kDense ? Roles<DG>::kThreadsDense
-                                                 : Roles<DG>::kThreadsGrouped, 1)
+// XTMA: the activation operand arrives by TMA from a row-contiguous tensor (always for
+// dense; for grouped modes when the caller permuted the rows into schedule-slot order, in
+// which case gate/up also writes its result in slot order).  Otherwise (grouped only) rows
+// are gathered by assignment with cp.async.
+template <int BM, int KS, int RAW, int WB, int DG, int AFMT, typename T, int MODE, bool XTMA>
+__global__ void __launch_bounds__(XTMA ? Roles<DG>::kThreadsDense : Roles<DG>::kThreadsGrouped, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
             const __grid_constant__ CUtensorMap tmap_x, const Params p) {
   constexpr bool GROUPED = MODE != kDense;
   constexpr int kGatherWarp0 = Roles<DG>::kGatherWarp0;
   static_assert(WB > DG, "the W' ring must hold one tile per decode group plus one");
+  static_assert(GROUPED || XTMA, "the dense mode always loads activations by TMA");
   using L = Layout<BM, KS, RAW, WB, GROUPED>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -345,8 +351,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
   uint64_t* tmem_empty = tmem_full + 2;    // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* row_table = reinterpret_cast<int*>(tmem_slot + 2);  // [BM] gather source rows
-  static_assert((2 * RAW + 2 * WB + 4) * 8 + 8 + 256 * 4 <= L::kBarrierBytes, "barrier area");
+  static_assert((2 * RAW + 2 * WB + 4) * 8 + 8 <= L::kBarrierBytes, "barrier area");
   Groups* groups = reinterpret_cast<Groups*>(smem + L::kBarrierOffset + L::kBarrierBytes);
 
   const int warp = threadIdx.x >> 5;
@@ -354,7 +359,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
 
   if (threadIdx.x == 0) {
     for (int r = 0; r < RAW; ++r) {
-      mbar_init(&full_raw[r], 1 + 32 + (GROUPED ? kGatherThreads : 0));
+      mbar_init(&full_raw[r], 1 + 32 + (XTMA ? 0 : kGatherThreads));
       mbar_init(&empty_raw[r], 1);
     }
     for (int w = 0; w < WB; ++w) {
@@ -371,7 +376,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
   if (warp == kProducerWarp) {
     if (lane == 0) {
       tma_prefetch_descriptor(&tmap_payload);
-      if constexpr (!GROUPED) tma_prefetch_descriptor(&tmap_x);
+      if constexpr (XTMA) tma_prefetch_descriptor(&tmap_x);
     }
     if constexpr (GROUPED) build_groups(groups, p, BM, lane);
   }
@@ -423,10 +428,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         NML_PROF_END(0);
         if (lane == 0) {
           mbar_arrive_expect_tx(&full_raw[raw.index],
-                                L::kPayloadBytes + (GROUPED ? 0 : KS * L::kXBytes));
+                                L::kPayloadBytes + (XTMA ? KS * L::kXBytes : 0));
           tma_load_2d(payload_tile(raw.index), &tmap_payload, &full_raw[raw.index],
                       rs * KS * 32, u.weight_row0);
-          if constexpr (!GROUPED) {
+          if constexpr (XTMA) {
 #pragma unroll
             for (int j = 0; j < KS; ++j) {
               tma_load_2d(x_tile(raw.index, j), &tmap_x, &full_raw[raw.index],
@@ -554,6 +559,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       NML_PROF_END(0);
       NML_PROF_BEGIN();
       tcgen05_fence_after_sync();
+      // Grouped modes that address the output by assignment keep the unit's slot -> (assignment,
+      // routing weight) map in a table private to this warp, filled with coalesced loads.
+      constexpr bool kSlotOutput = MODE == kGateUp && XTMA;  // result rows in slot order
+      constexpr bool kNeedsTable = GROUPED && !kSlotOutput;
+      int32_t* slot_assignment = nullptr;
+      uint16_t* slot_weight = nullptr;
+      if constexpr (kNeedsTable) {
+        uint8_t* table = reinterpret_cast<uint8_t*>(groups) + (kMaxGroups * 16 + 64) +
+                         (warp & 3) * (BM * 6);
+        slot_assignment = reinterpret_cast<int32_t*>(table);
+        slot_weight = reinterpret_cast<uint16_t*>(table + BM * 4);
+        __syncwarp();
+        for (int r = lane; r < BM; r += 32) {
+          int32_t a = -1;
+          uint16_t weight_bits = 0;
+          if (r < u.rows) {
+            const int32_t candidate = p.sorted_assignments[u.m0 + r];
+            if (candidate >= 0 && candidate < p.assignments) {
+              a = candidate;
+              if constexpr (MODE == kDown) {
+                weight_bits = static_cast<const uint16_t*>(p.routing_weights)[a];
+              }
+            }
+          }
+          slot_assignment[r] = a;
+          slot_weight[r] = weight_bits;
+        }
+        __syncwarp();
+      }
       const int n = u.n0 + row;  // output column (dense, down) or weight row in the expert
       const bool n_ok = n < (MODE == kGateUp ? p.rows_per_expert : p.N);
       float bias_value = 0.0f;
@@ -588,14 +622,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         } else if constexpr (MODE == kDown) {
 #pragma unroll
           for (int j = 0; j < kChunk; ++j) {
-            if (c + j < u.rows) {
-              const int a = p.sorted_assignments[u.m0 + c + j];
-              if (n_ok && a >= 0 && a < p.assignments) {
-                const float weight =
-                    Elem<T>::load(static_cast<const T*>(p.routing_weights)[a]);
-                out[static_cast<int64_t>(a) * p.N + n] =
-                    Elem<T>::store(fmaf(__uint_as_float(v[j]), g, bias_value) * weight);
-              }
+            const int a = slot_assignment[c + j];
+            if (n_ok && a >= 0) {
+              const float weight = Elem<T>::from_bits(slot_weight[c + j]);
+              out[static_cast<int64_t>(a) * p.N + n] =
+                  Elem<T>::store(fmaf(__uint_as_float(v[j]), g, bias_value) * weight);
             }
           }
         } else {
@@ -613,9 +644,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
             const int j = 2 * q + (odd ? 1 : 0);
             const float gate = odd ? received : mine_even;
             const float up = odd ? mine_odd : received;
-            if (c + j < u.rows) {
-              const int a = p.sorted_assignments[u.m0 + c + j];
-              if (n_ok && a >= 0 && a < p.assignments) {
+            if constexpr (kSlotOutput) {
+              if (n_ok && c + j < u.rows) {
+                out[static_cast<int64_t>(u.m0 + c + j) * p.N + column] =
+                    Elem<T>::store(clamped_swiglu(gate, up));
+              }
+            } else {
+              const int a = slot_assignment[c + j];
+              if (n_ok && a >= 0) {
                 out[static_cast<int64_t>(a) * p.N + column] =
                     Elem<T>::store(clamped_swiglu(gate, up));
               }
@@ -701,16 +737,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     NML_PROF_FLUSH(12, dt == 0)
   } else {
     // -------------------------------------------------------------------- gather
-    if constexpr (GROUPED) {
-      const int t = threadIdx.x - kGatherWarp0 * 32;  // 0..63
+    if constexpr (!XTMA) {
+      // Thread t copies 16-byte chunk (t & 7) of rows (t >> 3) + 16 i.  All its rows share
+      // (row & 7), so the swizzled chunk position is a per-thread constant, and the source
+      // byte offsets of its rows live in registers for the whole unit.
+      constexpr int kRowsPerThread = BM / 16;
+      const int t = threadIdx.x - kGatherWarp0 * 32;  // 0..127
       const int chunk = t & 7;
-      const int row0 = t >> 3;  // rows row0 + 8 i; (row & 7) == row0 for all of them
-      const int position = (chunk ^ row0) * 16;
+      const int row0 = t >> 3;
+      const int position = (chunk ^ (row0 & 7)) * 16;
       const uint8_t* input = static_cast<const uint8_t*>(p.input);
       constexpr int kLag = RAW > 2 ? 2 : RAW - 1;  // stages whose copies may still be landing
       RingState raw, arrive;
       int in_flight = 0;
       bool ok = true;
+      NML_PROF_DECL
       auto retire = [&](int keep) {
         while (in_flight > keep) {
           if (in_flight - 1 >= 2) {
@@ -728,50 +769,52 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       };
       for (int index = blockIdx.x; index < units && ok; index += gridDim.x) {
         const Unit u = get_unit<BM, GROUPED>(p, groups, index);
-        // Each gather warp owns the table entries of the rows it copies (row & 7 in its
-        // group of four), so a warp-level sync is all the table needs.
-        __syncwarp();
-        for (int r = row0 & ~3; r < BM; r += 8) {
-          const int mine = r + (lane >> 3);
-          if ((lane & 7) == 0 && mine < BM) {
-            int source = -1;
-            if (mine < u.rows) {
-              const int a = p.sorted_assignments[u.m0 + mine];
-              if (a >= 0 && a < p.assignments) source = MODE == kGateUp ? a / p.top_k : a;
+        int64_t source_offset[kRowsPerThread];  // byte offset of the source row, -1 = zero row
+#pragma unroll
+        for (int i = 0; i < kRowsPerThread; ++i) {
+          const int r = row0 + 16 * i;
+          int64_t offset = -1;
+          if (r < u.rows) {
+            const int a = p.sorted_assignments[u.m0 + r];
+            if (a >= 0 && a < p.assignments) {
+              offset = static_cast<int64_t>(MODE == kGateUp ? a / p.top_k : a) * p.K * 2;
             }
-            row_table[mine] = source;
           }
+          source_offset[i] = offset;
         }
-        __syncwarp();
         for (int rs = 0; rs < raw_stages; ++rs) {
+          NML_PROF_BEGIN();
           if (!wait(&raw_free[raw.index], raw.phase ^ 1u)) {
             ok = false;
             break;
           }
+          NML_PROF_END(0);
+          NML_PROF_BEGIN();
 #pragma unroll
           for (int j = 0; j < KS; ++j) {
             const int k_step = rs * KS + j;
             if (k_step < p.k_steps) {
-              const int64_t column_bytes = (static_cast<int64_t>(k_step) * kTileK + chunk * 8) * 2;
-              uint8_t* tile = x_tile(raw.index, j) + position;
-#pragma unroll 4
-              for (int r = row0; r < BM; r += 8) {
-                const int source = row_table[r];
-                const bool valid = source >= 0;
-                cp_async_16_zfill(tile + r * 128,
-                                  input + (valid ? static_cast<int64_t>(source) : 0) * p.K * 2 +
-                                      column_bytes,
-                                  valid);
+              const uint8_t* column = input + (static_cast<int64_t>(k_step) * kTileK + chunk * 8) * 2;
+              uint8_t* tile = x_tile(raw.index, j) + position + row0 * 128;
+#pragma unroll
+              for (int i = 0; i < kRowsPerThread; ++i) {
+                const bool valid = source_offset[i] >= 0;
+                cp_async_16_zfill(tile + i * (16 * 128),
+                                  column + (valid ? source_offset[i] : 0), valid);
               }
             }
           }
           asm volatile("cp.async.commit_group;" ::: "memory");
           ++in_flight;
           raw.advance<RAW>();
+          NML_PROF_END(1);
+          NML_PROF_BEGIN();
           retire(kLag);
+          NML_PROF_END(2);
         }
       }
       retire(0);
+      NML_PROF_FLUSH(20, t == 0)
     }
   }
 
