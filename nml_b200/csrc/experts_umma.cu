@@ -15,7 +15,8 @@ namespace {
 
 using namespace umma;
 
-template <int BM, int KS, int RAW, int WB, int DG, int AFMT, typename T, int MODE, bool XTMA>
+template <int BM, int KS, int RAW, int WB, int DG, int MI, int AFMT, typename T, int MODE,
+          bool XTMA>
 int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* message,
                       size_t capacity) {
   using L = Layout<BM, KS, RAW, WB, true>;
@@ -62,7 +63,7 @@ int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* me
   p.top_k = args.experts_per_token;
   p.status = device.status_word;
 
-  auto kernel = gemm_kernel<BM, KS, RAW, WB, DG, AFMT, T, MODE, XTMA>;
+  auto kernel = gemm_kernel<BM, KS, RAW, WB, DG, MI, AFMT, T, MODE, XTMA>;
   static bool configured[64] = {};
   if (!reserve_smem(kernel, L::kSmemBytes, device.device, configured)) {
     return fail(NML_SM100_LAUNCH_FAILURE, "cannot reserve shared memory for the tcgen05 experts",
@@ -73,8 +74,8 @@ int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* me
   const int64_t max_units = slot_tiles * p.n_tiles;
   const unsigned grid =
       static_cast<unsigned>(max_units < device.sm_count ? max_units : device.sm_count);
-  kernel<<<grid, XTMA ? Roles<DG>::kThreadsDense : Roles<DG>::kThreadsGrouped, L::kSmemBytes,
-           args.stream>>>(tmap_payload, tmap_x, p);
+  kernel<<<grid, launch_threads<DG, MI, XTMA>(), L::kSmemBytes, args.stream>>>(tmap_payload,
+                                                                               tmap_x, p);
   return launch_result(message, capacity);
 }
 
@@ -86,18 +87,18 @@ int32_t launch_for_load(const ExpertArgs& args, const DeviceInfo& device, char* 
                               ? 1
                               : (args.assignments + args.experts - 1) / args.experts;
   if (average <= 16) {
-    return launch_config<16, 4, 5, 4, 2, AFMT, T, MODE, XTMA>(args, device, message, capacity);
+    return launch_config<16, 4, 5, 4, 2, 2, AFMT, T, MODE, XTMA>(args, device, message, capacity);
   }
   if (average <= 32) {
-    return launch_config<32, 4, 4, 4, 2, AFMT, T, MODE, XTMA>(args, device, message, capacity);
+    return launch_config<32, 4, 4, 4, 2, 2, AFMT, T, MODE, XTMA>(args, device, message, capacity);
   }
   if (average <= 64) {
-    return launch_config<64, 4, 3, 4, 2, AFMT, T, MODE, XTMA>(args, device, message, capacity);
+    return launch_config<64, 4, 3, 4, 2, 2, AFMT, T, MODE, XTMA>(args, device, message, capacity);
   }
   if (average <= 160) {
-    return launch_config<128, 1, 5, 5, 2, AFMT, T, MODE, XTMA>(args, device, message, capacity);
+    return launch_config<128, 1, 5, 5, 2, 1, AFMT, T, MODE, XTMA>(args, device, message, capacity);
   }
-  return launch_config<256, 1, 4, 4, 2, AFMT, T, MODE, XTMA>(args, device, message, capacity);
+  return launch_config<256, 1, 4, 4, 2, 1, AFMT, T, MODE, XTMA>(args, device, message, capacity);
 }
 
 template <int MODE>

@@ -12,7 +12,7 @@ namespace {
 
 using namespace umma;
 
-template <int BM, int KS, int RAW, int WB, int DG, int AFMT, typename T>
+template <int BM, int KS, int RAW, int WB, int DG, int MI, int AFMT, typename T>
 int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* message,
                       size_t capacity) {
   using L = Layout<BM, KS, RAW, WB, false>;
@@ -41,7 +41,7 @@ int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* me
   p.output = args.output;
   p.status = device.status_word;
 
-  auto kernel = gemm_kernel<BM, KS, RAW, WB, DG, AFMT, T, kDense, true>;
+  auto kernel = gemm_kernel<BM, KS, RAW, WB, DG, MI, AFMT, T, kDense, true>;
   static bool configured[64] = {};
   if (!reserve_smem(kernel, L::kSmemBytes, device.device, configured)) {
     return fail(NML_SM100_LAUNCH_FAILURE, "cannot reserve shared memory for the tcgen05 linear",
@@ -49,7 +49,7 @@ int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* me
   }
   const int64_t tiles = static_cast<int64_t>(p.n_tiles) * p.m_tiles;
   const unsigned grid = static_cast<unsigned>(tiles < device.sm_count ? tiles : device.sm_count);
-  kernel<<<grid, Roles<DG>::kThreadsDense, L::kSmemBytes, args.stream>>>(tmap_payload, tmap_x, p);
+  kernel<<<grid, launch_threads<DG, MI, true>(), L::kSmemBytes, args.stream>>>(tmap_payload, tmap_x, p);
   note_linear_kernel(AFMT == kAf16 ? "umma_swapab_af16" : "umma_swapab_abf16");
   return launch_result(message, capacity);
 }
@@ -83,15 +83,15 @@ int32_t launch_for_rows(const LinearArgs& args, const DeviceInfo& device, char* 
                         size_t capacity) {
   switch (choose_tile_rows(args.rows, args.outputs, device.sm_count)) {
     case 16:
-      return launch_config<16, 4, 5, 4, 3, AFMT, T>(args, device, message, capacity);
+      return launch_config<16, 4, 5, 4, 3, 2, AFMT, T>(args, device, message, capacity);
     case 32:
-      return launch_config<32, 4, 4, 4, 3, AFMT, T>(args, device, message, capacity);
+      return launch_config<32, 4, 4, 4, 3, 2, AFMT, T>(args, device, message, capacity);
     case 64:
-      return launch_config<64, 4, 3, 4, 3, AFMT, T>(args, device, message, capacity);
+      return launch_config<64, 4, 3, 4, 3, 2, AFMT, T>(args, device, message, capacity);
     case 128:
-      return launch_config<128, 1, 6, 6, 3, AFMT, T>(args, device, message, capacity);
+      return launch_config<128, 1, 6, 6, 3, 1, AFMT, T>(args, device, message, capacity);
     default:
-      return launch_config<256, 1, 4, 4, 3, AFMT, T>(args, device, message, capacity);
+      return launch_config<256, 1, 4, 4, 3, 1, AFMT, T>(args, device, message, capacity);
   }
 }
 

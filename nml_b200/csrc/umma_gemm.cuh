@@ -45,6 +45,11 @@ constexpr int kGatherThreads = kGatherWarps * 32;
 // sequence number is congruent to g modulo DG, so DG K steps are in decode at once: the
 // decode of one K step is a long dependent instruction chain, and it is the number of
 // chains in flight, not the instruction count, that keeps the tensor pipe fed.
+// Threads of a launch: the roles above, the gather warps unless activations come by TMA, and
+// one more warp when a second MMA issuer is used.
+template <int DG, int MI, bool XTMA>
+constexpr int launch_threads();
+
 template <int DG>
 struct Roles {
   static constexpr int kDecodeWarps = 4 * DG;
@@ -52,6 +57,10 @@ struct Roles {
   static constexpr int kThreadsDense = kGatherWarp0 * 32;
   static constexpr int kThreadsGrouped = (kGatherWarp0 + kGatherWarps) * 32;
 };
+template <int DG, int MI, bool XTMA>
+constexpr int launch_threads() {
+  return (XTMA ? Roles<DG>::kThreadsDense : Roles<DG>::kThreadsGrouped) + (MI == 2 ? 32 : 0);
+}
 constexpr int kWBytes = kTileN * 128;
 constexpr int kSmemBudget = 227 * 1024;
 constexpr int kMaxGroups = 256;
@@ -325,15 +334,19 @@ struct RingState {
 // dense; for grouped modes when the caller permuted the rows into schedule-slot order, in
 // which case gate/up also writes its result in slot order).  Otherwise (grouped only) rows
 // are gathered by assignment with cp.async.
-template <int BM, int KS, int RAW, int WB, int DG, int AFMT, typename T, int MODE, bool XTMA>
-__global__ void __launch_bounds__(XTMA ? Roles<DG>::kThreadsDense : Roles<DG>::kThreadsGrouped, 1)
+template <int BM, int KS, int RAW, int WB, int DG, int MI, int AFMT, typename T, int MODE,
+          bool XTMA>
+__global__ void __launch_bounds__(launch_threads<DG, MI, XTMA>(), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
             const __grid_constant__ CUtensorMap tmap_x, const Params p) {
   constexpr bool GROUPED = MODE != kDense;
   constexpr int kGatherWarp0 = Roles<DG>::kGatherWarp0;
+  constexpr int kMmaWarpB = XTMA ? kGatherWarp0 : kGatherWarp0 + kGatherWarps;
+  static_assert(MI == 1 || (MI == 2 && 2 * MI * BM <= 512), "two issuers need 4 accumulators");
   static_assert(WB > DG, "the W' ring must hold one tile per decode group plus one");
   static_assert(GROUPED || XTMA, "the dense mode always loads activations by TMA");
   using L = Layout<BM, KS, RAW, WB, GROUPED>;
+  constexpr int kTmemColumns = MI * L::kTmemColumns;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
 
@@ -360,14 +373,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
   if (threadIdx.x == 0) {
     for (int r = 0; r < RAW; ++r) {
       mbar_init(&full_raw[r], 1 + 32 + (XTMA ? 0 : kGatherThreads));
-      mbar_init(&empty_raw[r], 1);
+      mbar_init(&empty_raw[r], MI);
     }
     for (int w = 0; w < WB; ++w) {
       mbar_init(&full_w[w], kGroupThreads);
       mbar_init(&empty_w[w], 1);
     }
     for (int a = 0; a < 2; ++a) {
-      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_full[a], MI);
       mbar_init(&tmem_empty[a], kEpilogueWarps * 32);
     }
     *abort_flag = 0;
@@ -381,7 +394,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     if constexpr (GROUPED) build_groups(groups, p, BM, lane);
   }
   if (warp == kMmaWarp) {
-    tmem_alloc(tmem_slot, L::kTmemColumns);
+    tmem_alloc(tmem_slot, kTmemColumns);
     tmem_relinquish_alloc_permit();
   }
   tcgen05_fence_before_sync();
@@ -465,8 +478,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       if (!mbar_wait(&full_raw[raw.index], raw.phase)) give_up();
     }
     NML_PROF_FLUSH(0, lane == 0)
-  } else if (warp == kMmaWarp) {
+  } else if (warp == kMmaWarp || (MI == 2 && warp == kMmaWarpB)) {
     // ----------------------------------------------------------------------- MMA
+    // With MI == 2 two threads (in two warps) issue alternate K steps of a unit into two
+    // accumulators that the epilogue adds in a fixed order.  Issuing four MMAs and a commit
+    // costs one thread several hundred cycles, which bounds small tiles; splitting the
+    // issue stream halves that bound and stays deterministic.
+    const int issuer = warp == kMmaWarp ? 0 : 1;
     if (lane == 0) {
       constexpr uint32_t a_format = AFMT == kAf16 ? kUmmaF16 : kUmmaBF16;
       constexpr uint32_t b_format = std::is_same<T, __half>::value ? kUmmaF16 : kUmmaBF16;
@@ -487,7 +505,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         if (!wait(&tmem_empty[acc], acc_phase ^ 1u)) break;
         NML_PROF_END(0);
         tcgen05_fence_after_sync();
-        const uint32_t d_address = tmem_base + acc * BM;
+        const uint32_t d_address = tmem_base + (acc * MI + issuer) * BM;
+        int step = 0;  // K step inside the unit
         for (int rs = 0; rs < raw_stages && ok; ++rs) {
           NML_PROF_BEGIN();
           if (!wait(&full_raw[raw.index], raw.phase)) {
@@ -496,37 +515,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
           }
           NML_PROF_END(1);
           const int sub_steps = min(KS, p.k_steps - rs * KS);
-          for (int j = 0; j < sub_steps; ++j) {
+          for (int j = 0; j < sub_steps; ++j, ++step, wb.advance<WB>()) {
+            if (MI == 2 && (step & 1) != issuer) continue;
             NML_PROF_BEGIN();
             if (!wait(&full_w[wb.index], wb.phase)) {
               ok = false;
               break;
             }
             NML_PROF_END(2);
-#ifdef NML_SM100_PROFILE
-            const long long issue_t0 = clock64();
-#endif
             tcgen05_fence_after_sync();
             // Descriptors differ only in the start-address field (16-byte units); each
             // K=16 slice is 32 bytes further along the swizzled 128-byte rows.
             const uint32_t a_lo = w_desc_lo + wb.index * (kWBytes >> 4);
             const uint32_t b_lo =
                 x_desc_lo + raw.index * (L::kRawBytes >> 4) + j * (L::kXBytes >> 4);
+            const bool first = step < MI;  // this issuer's first K step of the unit
 #pragma unroll
             for (int q = 0; q < kTileK / kUmmaK; ++q) {
               umma_f16_split(d_address, a_lo + 2 * q, b_lo + 2 * q, kUmmaDescHiSw128, idesc,
-                             (rs | j | q) != 0);
+                             !(first && q == 0));
             }
-#ifdef NML_SM100_PROFILE
-            const long long issue_t1 = clock64();
-#endif
             umma_commit(&empty_w[wb.index]);
-#ifdef NML_SM100_PROFILE
-            const long long issue_t2 = clock64();
-            atomicAdd(&g_profile[16], static_cast<unsigned long long>(issue_t1 - issue_t0));
-            atomicAdd(&g_profile[17], static_cast<unsigned long long>(issue_t2 - issue_t1));
-#endif
-            wb.advance<WB>();
           }
           if constexpr (!kSharedEmpty) {
             if (ok) umma_commit(&empty_raw[raw.index]);
@@ -538,7 +547,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
 #ifdef NML_SM100_PROFILE
       prof_acc[3] = static_cast<unsigned long long>(clock64() - prof_start);
 #endif
-      NML_PROF_FLUSH(4, true)
+      NML_PROF_FLUSH(4, issuer == 0)
     }
     __syncwarp();
   } else if (warp < kDecodeWarp0) {
@@ -599,12 +608,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
 #pragma unroll 1
       for (int c = 0; c < BM; c += kChunk) {
         const uint32_t address =
-            tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BM + c;
+            tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * MI * BM + c;
         uint32_t v[kChunk];
         if constexpr (kChunk == 32) {
           tmem_load_32x32(address, v);
         } else {
           tmem_load_32x16(address, v);
+        }
+        if constexpr (MI == 2) {
+          // second issuer's partial sums (odd K steps); absent when the unit has one K step
+          uint32_t v2[kChunk];
+          if constexpr (kChunk == 32) {
+            tmem_load_32x32(address + BM, v2);
+          } else {
+            tmem_load_32x16(address + BM, v2);
+          }
+          tmem_load_wait();
+          if (p.k_steps > 1) {
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j) {
+              v[j] = __float_as_uint(__fadd_rn(__uint_as_float(v[j]), __uint_as_float(v2[j])));
+            }
+          }
         }
         tmem_load_wait();
         if (c >= u.rows) continue;  // uniform: nothing valid left in this chunk
@@ -822,7 +847,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
   __syncthreads();
   if (warp == kMmaWarp) {
     tcgen05_fence_after_sync();
-    tmem_dealloc(tmem_base, L::kTmemColumns);
+    tmem_dealloc(tmem_base, kTmemColumns);
   }
 }
 
