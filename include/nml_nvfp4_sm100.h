@@ -376,12 +376,14 @@ int32_t nml_nvfp4_sm100_plan_capacity(int64_t assignments, int64_t experts, int6
 int32_t nml_nvfp4_sm100_device_status(void *stream, int32_t clear, int32_t *status);
 
 /* Kernel selection override for experiments and tests: 0 = automatic, 1 = force the
- * portable SIMT kernels, 2 = force the tcgen05 kernels where the shape allows.
+ * portable SIMT kernels, 2 = force the tcgen05 kernels where the shape allows, 3 = as 2 but
+ * keep the decoded weight tiles in a shared-memory ring instead of tensor memory.
  * Process-wide; returns the previous value. */
 int32_t nml_nvfp4_sm100_set_kernel_policy(int32_t policy);
 
 /* Name of the kernel family the last nml_nvfp4_sm100_linear call on this thread selected
- * ("umma_swapab_af16", "umma_swapab_abf16", "simt"), for tests and benchmark records. */
+ * ("umma_tmem_weights_af16", "umma_tmem_weights_abf16", "umma_swapab_af16",
+ * "umma_swapab_abf16", "simt"), for tests and benchmark records. */
 const char *nml_nvfp4_sm100_last_linear_kernel(void);
 
 /* ABI version of this header. */

@@ -27,6 +27,7 @@ STATIC_SCRATCH_BYTES = 8 << 20
 POLICY_AUTO = 0
 POLICY_SIMT = 1
 POLICY_UMMA = 2
+POLICY_UMMA_SMEM = 3  # tcgen05 with the decoded-weight ring in shared memory
 
 _vp = ctypes.c_void_p
 _i64 = ctypes.c_int64

@@ -8,6 +8,8 @@
 // UMMA operand tile with 16-byte cp.async; there is no permuted copy of the tokens in HBM.
 // Gate/up keeps the checkpoint's interleaved rows (2i = gate, 2i+1 = up): lane pairs of the
 // epilogue exchange accumulators and write swiglu(gate, up) for intermediate column i.
+#include <cstdlib>
+
 #include "umma_gemm.cuh"
 
 namespace nml_sm100 {
@@ -15,11 +17,11 @@ namespace {
 
 using namespace umma;
 
-template <int BM, int KS, int RAW, int WB, int DG, int MI, int AFMT, typename T, int MODE,
-          bool XTMA>
+template <int BM, int KS, int RAW, int WB, int DG, int MI, int PA, bool WT, int AFMT, typename T,
+          int MODE, bool XTMA>
 int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* message,
                       size_t capacity) {
-  using L = Layout<BM, KS, RAW, WB, true>;
+  using L = Layout<BM, KS, RAW, WB, true, WT>;
   const int rows_per_expert = args.gate_up ? 2 * args.outputs : args.outputs;
   const int64_t weight_rows = static_cast<int64_t>(args.experts) * rows_per_expert;
   CUtensorMap tmap_payload, tmap_x;
@@ -30,7 +32,7 @@ int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* me
     // rows of the input are schedule slots
     if (!encode_activation_map<T>(&tmap_x, args.input,
                                   static_cast<int64_t>(args.schedule_blocks) * 16, args.inputs,
-                                  BM)) {
+                                  BM, KS)) {
       return fail(NML_SM100_LAUNCH_FAILURE, "tensor map encoding failed", message, capacity);
     }
   } else {
@@ -62,8 +64,11 @@ int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* me
   p.experts = args.experts;
   p.top_k = args.experts_per_token;
   p.status = device.status_word;
+#ifdef NML_SM100_PROFILE
+  p.knockout = std::getenv("NML_SM100_KNOCKOUT") ? std::atoi(std::getenv("NML_SM100_KNOCKOUT")) : 0;
+#endif
 
-  auto kernel = gemm_kernel<BM, KS, RAW, WB, DG, MI, AFMT, T, MODE, XTMA>;
+  auto kernel = gemm_kernel<BM, KS, RAW, WB, DG, MI, PA, WT, AFMT, T, MODE, XTMA>;
   static bool configured[64] = {};
   if (!reserve_smem(kernel, L::kSmemBytes, device.device, configured)) {
     return fail(NML_SM100_LAUNCH_FAILURE, "cannot reserve shared memory for the tcgen05 experts",
@@ -86,19 +91,41 @@ int32_t launch_for_load(const ExpertArgs& args, const DeviceInfo& device, char* 
   const int64_t average = args.assignments <= args.experts
                               ? 1
                               : (args.assignments + args.experts - 1) / args.experts;
+  // Decoded weights in tensor memory: needs the unit's block scales (128 rows x K/16 bytes)
+  // to fit one buffer and every tile's scale range to form a legal bulk copy.
+  const int rows_per_expert = args.gate_up ? 2 * args.outputs : args.outputs;
+  const bool tmem_weights =
+      get_kernel_policy() != 3 && args.inputs / 16 * kTileN <= kScaleBufferBytes &&
+      rows_per_expert % 4 == 0 && reinterpret_cast<uintptr_t>(args.block_scales) % 16 == 0;
+  if (tmem_weights && average <= 160) {
+    if (average <= 16) {
+      return launch_config<16, 4, 6, 8, 2, 2, 8, true, AFMT, T, MODE, XTMA>(args, device, message,
+                                                                            capacity);
+    }
+    if (average <= 32) {
+      return launch_config<32, 4, 5, 8, 2, 1, 4, true, AFMT, T, MODE, XTMA>(args, device, message,
+                                                                            capacity);
+    }
+    if (average <= 64) {
+      return launch_config<64, 4, 3, 8, 2, 1, 2, true, AFMT, T, MODE, XTMA>(args, device, message,
+                                                                            capacity);
+    }
+    return launch_config<128, 1, 8, 8, 2, 1, 1, true, AFMT, T, MODE, XTMA>(args, device, message,
+                                                                           capacity);
+  }
   if (average <= 16) {
-    return launch_config<16, 4, 5, 4, 2, 2, AFMT, T, MODE, XTMA>(args, device, message, capacity);
+    return launch_config<16, 4, 5, 4, 2, 2, 8, false, AFMT, T, MODE, XTMA>(args, device, message, capacity);
   }
   if (average <= 32) {
-    return launch_config<32, 4, 4, 4, 2, 2, AFMT, T, MODE, XTMA>(args, device, message, capacity);
+    return launch_config<32, 4, 4, 4, 2, 2, 8, false, AFMT, T, MODE, XTMA>(args, device, message, capacity);
   }
   if (average <= 64) {
-    return launch_config<64, 4, 3, 4, 2, 2, AFMT, T, MODE, XTMA>(args, device, message, capacity);
+    return launch_config<64, 4, 3, 4, 2, 1, 4, false, AFMT, T, MODE, XTMA>(args, device, message, capacity);
   }
   if (average <= 160) {
-    return launch_config<128, 1, 5, 5, 2, 1, AFMT, T, MODE, XTMA>(args, device, message, capacity);
+    return launch_config<128, 1, 5, 5, 2, 1, 1, false, AFMT, T, MODE, XTMA>(args, device, message, capacity);
   }
-  return launch_config<256, 1, 4, 4, 2, 1, AFMT, T, MODE, XTMA>(args, device, message, capacity);
+  return launch_config<256, 1, 4, 4, 2, 1, 1, false, AFMT, T, MODE, XTMA>(args, device, message, capacity);
 }
 
 template <int MODE>

@@ -5,6 +5,8 @@
 // between 64, 128 and 256 minimises waves x per-tile time on the device's SM count.  Small
 // tiles (decode shapes, HBM-bound) use raw stages of four K steps so that ~100 KB of packed
 // weight bytes are in flight per SM; large tiles are MMA-bound and use one K step per stage.
+#include <cstdlib>
+
 #include "umma_gemm.cuh"
 
 namespace nml_sm100 {
@@ -12,13 +14,13 @@ namespace {
 
 using namespace umma;
 
-template <int BM, int KS, int RAW, int WB, int DG, int MI, int AFMT, typename T>
+template <int BM, int KS, int RAW, int WB, int DG, int MI, int PA, bool WT, int AFMT, typename T>
 int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* message,
                       size_t capacity) {
-  using L = Layout<BM, KS, RAW, WB, false>;
+  using L = Layout<BM, KS, RAW, WB, false, WT>;
   CUtensorMap tmap_payload, tmap_x;
   if (!encode_payload_map<KS>(&tmap_payload, args.payload, args.outputs, args.inputs) ||
-      !encode_activation_map<T>(&tmap_x, args.activation, args.rows, args.inputs, BM)) {
+      !encode_activation_map<T>(&tmap_x, args.activation, args.rows, args.inputs, BM, KS)) {
     return fail(NML_SM100_LAUNCH_FAILURE, "tensor map encoding failed", message, capacity);
   }
   Params p = {};
@@ -40,8 +42,11 @@ int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* me
   p.n_fastest = weight_bytes <= (32ll << 20) ? 1 : 0;
   p.output = args.output;
   p.status = device.status_word;
+#ifdef NML_SM100_PROFILE
+  p.knockout = std::getenv("NML_SM100_KNOCKOUT") ? std::atoi(std::getenv("NML_SM100_KNOCKOUT")) : 0;
+#endif
 
-  auto kernel = gemm_kernel<BM, KS, RAW, WB, DG, MI, AFMT, T, kDense, true>;
+  auto kernel = gemm_kernel<BM, KS, RAW, WB, DG, MI, PA, WT, AFMT, T, kDense, true>;
   static bool configured[64] = {};
   if (!reserve_smem(kernel, L::kSmemBytes, device.device, configured)) {
     return fail(NML_SM100_LAUNCH_FAILURE, "cannot reserve shared memory for the tcgen05 linear",
@@ -50,7 +55,8 @@ int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* me
   const int64_t tiles = static_cast<int64_t>(p.n_tiles) * p.m_tiles;
   const unsigned grid = static_cast<unsigned>(tiles < device.sm_count ? tiles : device.sm_count);
   kernel<<<grid, launch_threads<DG, MI, true>(), L::kSmemBytes, args.stream>>>(tmap_payload, tmap_x, p);
-  note_linear_kernel(AFMT == kAf16 ? "umma_swapab_af16" : "umma_swapab_abf16");
+  note_linear_kernel(WT ? (AFMT == kAf16 ? "umma_tmem_weights_af16" : "umma_tmem_weights_abf16")
+                        : (AFMT == kAf16 ? "umma_swapab_af16" : "umma_swapab_abf16"));
   return launch_result(message, capacity);
 }
 
@@ -81,17 +87,38 @@ int choose_tile_rows(int rows, int outputs, int sm_count) {
 template <int AFMT, typename T>
 int32_t launch_for_rows(const LinearArgs& args, const DeviceInfo& device, char* message,
                         size_t capacity) {
-  switch (choose_tile_rows(args.rows, args.outputs, device.sm_count)) {
+  const int tile_rows = choose_tile_rows(args.rows, args.outputs, device.sm_count);
+  // Decoded weights in tensor memory: needs the unit's block scales (128 rows x K/16 bytes)
+  // to fit one buffer and to form a legal bulk copy.
+  const bool tmem_weights =
+      get_kernel_policy() != 3 && args.inputs / 16 * kTileN <= kScaleBufferBytes &&
+      args.outputs % 4 == 0 && reinterpret_cast<uintptr_t>(args.block_scales) % 16 == 0;
+  if (tmem_weights) {
+    switch (tile_rows) {
+      case 16:
+        return launch_config<16, 4, 6, 8, 3, 2, 8, true, AFMT, T>(args, device, message, capacity);
+      case 32:
+        return launch_config<32, 4, 5, 8, 3, 1, 4, true, AFMT, T>(args, device, message, capacity);
+      case 64:
+        return launch_config<64, 4, 3, 8, 3, 1, 2, true, AFMT, T>(args, device, message, capacity);
+      case 128:
+        return launch_config<128, 1, 8, 8, 3, 1, 1, true, AFMT, T>(args, device, message,
+                                                                   capacity);
+      default:
+        break;
+    }
+  }
+  switch (tile_rows) {
     case 16:
-      return launch_config<16, 4, 5, 4, 3, 2, AFMT, T>(args, device, message, capacity);
+      return launch_config<16, 4, 5, 4, 3, 2, 8, false, AFMT, T>(args, device, message, capacity);
     case 32:
-      return launch_config<32, 4, 4, 4, 3, 2, AFMT, T>(args, device, message, capacity);
+      return launch_config<32, 4, 4, 4, 3, 2, 8, false, AFMT, T>(args, device, message, capacity);
     case 64:
-      return launch_config<64, 4, 3, 4, 3, 2, AFMT, T>(args, device, message, capacity);
+      return launch_config<64, 4, 3, 4, 3, 1, 4, false, AFMT, T>(args, device, message, capacity);
     case 128:
-      return launch_config<128, 1, 6, 6, 3, 1, AFMT, T>(args, device, message, capacity);
+      return launch_config<128, 1, 6, 6, 3, 1, 1, false, AFMT, T>(args, device, message, capacity);
     default:
-      return launch_config<256, 1, 4, 4, 3, 1, AFMT, T>(args, device, message, capacity);
+      return launch_config<256, 1, 4, 4, 3, 1, 1, false, AFMT, T>(args, device, message, capacity);
   }
 }
 

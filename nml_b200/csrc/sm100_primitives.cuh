@@ -107,6 +107,18 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
       : "memory");
 }
 
+// 3-D tiled load; x is the innermost coordinate.
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar,
+                                            int32_t x, int32_t y, int32_t z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      :
+      : "r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x),
+        "r"(y), "r"(z)
+      : "memory");
+}
+
 // ---- cp.async (LDGSTS) -------------------------------------------------------
 __device__ __forceinline__ void cp_async_4(void* dst, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src)
@@ -214,6 +226,21 @@ __device__ __forceinline__ void tmem_load_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// Each thread writes 8 consecutive 32-bit columns of its own TMEM lane (the warp's lanes are
+// 32 * (warp % 4) + lane; the address carries the warp's first lane).
+__device__ __forceinline__ void tmem_store_32x8(uint32_t address, const uint32_t (&v)[8]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+      :
+      : "r"(address), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]),
+        "r"(v[6]), "r"(v[7])
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_store_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // ---- UMMA descriptors ---------------------------------------------------------
 // Shared-memory operand descriptor for a K-major tile stored as rows of 128
 // bytes with the 128-byte swizzle (16-byte chunk index XOR row-in-group-of-8),
@@ -253,6 +280,35 @@ __device__ __forceinline__ void umma_f16_split(uint32_t tmem_d, uint32_t a_lo, u
       "}\n"
       :
       : "r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(acc)
+      : "memory");
+}
+
+// A operand in tensor memory (lane = row of A, 32-bit column c = elements 2c and 2c + 1 of
+// the K = 16 slice), B operand in shared memory.
+__device__ __forceinline__ void umma_f16_tmem_a(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo,
+                                                uint32_t desc_hi, uint32_t idesc,
+                                                bool accumulate) {
+  const uint32_t acc = accumulate ? 1u : 0u;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 db;\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "mov.b64 db, {%2, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n"
+      "}\n"
+      :
+      : "r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(acc)
+      : "memory");
+}
+
+// Untiled bulk copy global -> shared; both addresses and the size are multiples of 16 bytes.
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes,
+                                          uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      :
+      : "r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
 

@@ -65,14 +65,21 @@ constexpr int kWBytes = kTileN * 128;
 constexpr int kSmemBudget = 227 * 1024;
 constexpr int kMaxGroups = 256;
 
-template <int BM, int KS, int RAW, int WB, bool GROUPED>
+// WT: the decoded weight tiles live in tensor memory (the MMA reads its A operand there) and
+// the block scales of a whole unit arrive with one bulk copy into one of two buffers;
+// otherwise the decoded tiles form a shared-memory ring and every raw stage carries its own
+// scale bytes.
+constexpr int kScaleBufferBytes = 24 * 1024;  // 128 rows x K/16 bytes, so K <= 3072 with WT
+
+template <int BM, int KS, int RAW, int WB, bool GROUPED, bool WT = false>
 struct Layout {
   static constexpr int kPayloadBytes = kTileN * 32 * KS;
-  static constexpr int kScaleBytes = kTileN * 4 * KS < 1024 ? 1024 : kTileN * 4 * KS;
+  static constexpr int kScaleBytes = WT ? 0 : (kTileN * 4 * KS < 1024 ? 1024 : kTileN * 4 * KS);
   static constexpr int kXBytes = BM * 128;                 // one K step
   static constexpr int kRawBytes = kPayloadBytes + kScaleBytes + kXBytes * KS;
-  static constexpr int kRawOffset = WB * kWBytes;
-  static constexpr int kBarrierOffset = kRawOffset + RAW * kRawBytes;
+  static constexpr int kRawOffset = WT ? 0 : WB * kWBytes;
+  static constexpr int kScaleBufferOffset = kRawOffset + RAW * kRawBytes;
+  static constexpr int kBarrierOffset = kScaleBufferOffset + (WT ? 2 * kScaleBufferBytes : 0);
   static constexpr int kBarrierBytes = 2048;
   // grouped: group table + one slot table (assignment id, routing weight) per epilogue warp
   static constexpr int kSlotTableBytes = GROUPED ? kEpilogueWarps * BM * 6 : 0;
@@ -106,6 +113,7 @@ struct Params {
   const void* routing_weights;
   int assignments, schedule_blocks, experts, top_k;
   int* status;
+  int knockout;  // tuning builds only: bit 0 skips the decode arithmetic, bit 1 the MMA issue
 };
 
 // One unit of work: a 128-row weight tile against BM activation rows / schedule slots.
@@ -334,19 +342,32 @@ struct RingState {
 // dense; for grouped modes when the caller permuted the rows into schedule-slot order, in
 // which case gate/up also writes its result in slot order).  Otherwise (grouped only) rows
 // are gathered by assignment with cp.async.
-template <int BM, int KS, int RAW, int WB, int DG, int MI, int AFMT, typename T, int MODE,
-          bool XTMA>
+// PA: partial accumulators per tile.  Consecutive tcgen05.mma into one accumulator form a
+// dependent chain whose per-instruction latency (not its throughput) bounds tiles with few
+// activation rows, so the K=16 slices rotate over PA accumulators (instruction i of a unit
+// goes to accumulator i % PA) and the epilogue adds them in index order.
+template <int BM, int KS, int RAW, int WB, int DG, int MI, int PA, bool WT, int AFMT,
+          typename T, int MODE, bool XTMA>
 __global__ void __launch_bounds__(launch_threads<DG, MI, XTMA>(), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
             const __grid_constant__ CUtensorMap tmap_x, const Params p) {
   constexpr bool GROUPED = MODE != kDense;
   constexpr int kGatherWarp0 = Roles<DG>::kGatherWarp0;
   constexpr int kMmaWarpB = XTMA ? kGatherWarp0 : kGatherWarp0 + kGatherWarps;
-  static_assert(MI == 1 || (MI == 2 && 2 * MI * BM <= 512), "two issuers need 4 accumulators");
+  static_assert(2 * PA * BM <= 512, "partial accumulators exceed tensor memory");
+  static_assert(MI == 1 || PA == 8, "two issuers need disjoint partial accumulators");
   static_assert(WB > DG, "the W' ring must hold one tile per decode group plus one");
   static_assert(GROUPED || XTMA, "the dense mode always loads activations by TMA");
-  using L = Layout<BM, KS, RAW, WB, GROUPED>;
-  constexpr int kTmemColumns = MI * L::kTmemColumns;
+  using L = Layout<BM, KS, RAW, WB, GROUPED, WT>;
+  constexpr int kAccColumns = PA * L::kTmemColumns;   // two accumulator sets of PA partials
+  constexpr int kWColumns = kTileK / 2;                // one decoded K step: 64 x 16 bit per row
+  constexpr int kTmemNeeded = kAccColumns + (WT ? WB * kWColumns : 0);
+  constexpr int kTmemColumns = kTmemNeeded <= 32    ? 32
+                               : kTmemNeeded <= 64  ? 64
+                               : kTmemNeeded <= 128 ? 128
+                               : kTmemNeeded <= 256 ? 256
+                                                    : 512;
+  static_assert(kTmemNeeded <= 512, "tensor memory budget exceeded");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
 
@@ -355,6 +376,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
   auto x_tile = [&](int r, int j) { return raw_base(r) + j * L::kXBytes; };
   auto payload_tile = [&](int r) { return raw_base(r) + KS * L::kXBytes; };
   auto scale_tile = [&](int r) { return raw_base(r) + KS * L::kXBytes + L::kPayloadBytes; };
+  auto scale_buffer = [&](int b) { return smem + L::kScaleBufferOffset + b * kScaleBufferBytes; };
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarrierOffset);
   uint64_t* full_raw = bars;               // [RAW]
   uint64_t* empty_raw = bars + RAW;        // [RAW]
@@ -362,9 +384,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
   uint64_t* empty_w = full_w + WB;         // [WB]
   uint64_t* tmem_full = empty_w + WB;      // [2]
   uint64_t* tmem_empty = tmem_full + 2;    // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  uint64_t* full_scale = tmem_empty + 2;   // [2] (WT)
+  uint64_t* empty_scale = full_scale + 2;  // [2] (WT)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(empty_scale + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  static_assert((2 * RAW + 2 * WB + 4) * 8 + 8 <= L::kBarrierBytes, "barrier area");
+  static_assert((2 * RAW + 2 * WB + 8) * 8 + 8 <= L::kBarrierBytes, "barrier area");
   Groups* groups = reinterpret_cast<Groups*>(smem + L::kBarrierOffset + L::kBarrierBytes);
 
   const int warp = threadIdx.x >> 5;
@@ -372,16 +396,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
 
   if (threadIdx.x == 0) {
     for (int r = 0; r < RAW; ++r) {
-      mbar_init(&full_raw[r], 1 + 32 + (XTMA ? 0 : kGatherThreads));
+      mbar_init(&full_raw[r], 1 + (WT ? 0 : 32) + (XTMA ? 0 : kGatherWarps));
       mbar_init(&empty_raw[r], MI);
     }
     for (int w = 0; w < WB; ++w) {
-      mbar_init(&full_w[w], kGroupThreads);
+      mbar_init(&full_w[w], kGroupThreads / 32);
       mbar_init(&empty_w[w], 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], MI);
-      mbar_init(&tmem_empty[a], kEpilogueWarps * 32);
+      mbar_init(&tmem_empty[a], kEpilogueWarps);
+      mbar_init(&full_scale[a], 1);
+      mbar_init(&empty_scale[a], 4 * DG);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -428,10 +454,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     // ------------------------------------------------------------------ producer
     RingState raw;
     int issued = 0;
+    int local = 0;
     bool ok = true;
     NML_PROF_DECL
-    for (int index = blockIdx.x; index < units && ok; index += gridDim.x) {
+    for (int index = blockIdx.x; index < units && ok; index += gridDim.x, ++local) {
       const Unit u = get_unit<BM, GROUPED>(p, groups, index);
+      if constexpr (WT) {
+        // all block scales of the unit's weight rows: one contiguous range of the tensor
+        const int b = local & 1;
+        if (!wait(&empty_scale[b], ((local >> 1) & 1) ^ 1u)) break;
+        if (lane == 0) {
+          const int rows = min(kTileN, p.weight_rows_total - u.weight_row0);
+          const uint32_t bytes = static_cast<uint32_t>(rows * p.scale_width);
+          mbar_arrive_expect_tx(&full_scale[b], bytes);
+          bulk_load(scale_buffer(b),
+                    p.block_scales + static_cast<int64_t>(u.weight_row0) * p.scale_width, bytes,
+                    &full_scale[b]);
+        }
+      }
       for (int rs = 0; rs < raw_stages; ++rs) {
         NML_PROF_BEGIN();
         if (!wait(&raw_free[raw.index], raw.phase ^ 1u)) {
@@ -445,27 +485,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
           tma_load_2d(payload_tile(raw.index), &tmap_payload, &full_raw[raw.index],
                       rs * KS * 32, u.weight_row0);
           if constexpr (XTMA) {
-#pragma unroll
-            for (int j = 0; j < KS; ++j) {
-              tma_load_2d(x_tile(raw.index, j), &tmap_x, &full_raw[raw.index],
-                          (rs * KS + j) * kTileK, u.m0);
+            if constexpr (KS == 1) {
+              tma_load_2d(x_tile(raw.index, 0), &tmap_x, &full_raw[raw.index], rs * kTileK,
+                          u.m0);
+            } else {
+              // the activation map is a 3-D view [K/64][rows][64]: one box carries KS K steps
+              tma_load_3d(x_tile(raw.index, 0), &tmap_x, &full_raw[raw.index], 0, u.m0,
+                          rs * KS);
             }
           }
         }
+        if constexpr (!WT) {
+          // block scales: 4 bytes per row and K step (scale rows are not TMA-legal)
 #pragma unroll
-        for (int j = 0; j < KS; ++j) {
-          const int k_step = rs * KS + j;
-          if (k_step < p.k_steps) {
+          for (int j = 0; j < KS; ++j) {
+            const int k_step = rs * KS + j;
+            if (k_step < p.k_steps) {
 #pragma unroll
-            for (int i = 0; i < kTileN / 32; ++i) {
-              const int row = lane + 32 * i;
-              const int n = min(u.weight_row0 + row, p.weight_rows_total - 1);
-              cp_async_4(scale_tile(raw.index) + row * (4 * KS) + j * 4,
-                         p.block_scales + static_cast<int64_t>(n) * p.scale_width + k_step * 4);
+              for (int i = 0; i < kTileN / 32; ++i) {
+                const int row = lane + 32 * i;
+                const int n = min(u.weight_row0 + row, p.weight_rows_total - 1);
+                cp_async_4(scale_tile(raw.index) + row * (4 * KS) + j * 4,
+                           p.block_scales + static_cast<int64_t>(n) * p.scale_width + k_step * 4);
+              }
             }
           }
+          cp_async_mbar_arrive_noinc(&full_raw[raw.index]);
+        } else {
+          __syncwarp();
         }
-        cp_async_mbar_arrive_noinc(&full_raw[raw.index]);
         ++issued;
         raw.advance<RAW>();
       }
@@ -476,6 +524,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       raw.index = raw.index == 0 ? RAW - 1 : raw.index - 1;
       if (raw.index == RAW - 1) raw.phase ^= 1u;
       if (!mbar_wait(&full_raw[raw.index], raw.phase)) give_up();
+    }
+    if constexpr (WT) {
+      for (int back = 1; back <= 2 && back <= local; ++back) {
+        const int unit = local - back;
+        if (!mbar_wait(&full_scale[unit & 1], (unit >> 1) & 1)) give_up();
+      }
     }
     NML_PROF_FLUSH(0, lane == 0)
   } else if (warp == kMmaWarp || (MI == 2 && warp == kMmaWarpB)) {
@@ -492,11 +546,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       RingState raw, wb;
       int local = 0;
       bool ok = true;
-      const uint32_t w_desc_lo = umma_desc_lo(smem_u32(w_tile(0)));
+      const uint32_t w_desc_lo = WT ? 0u : umma_desc_lo(smem_u32(w_tile(0)));
       const uint32_t x_desc_lo = umma_desc_lo(smem_u32(x_tile(0, 0)));
       NML_PROF_DECL
 #ifdef NML_SM100_PROFILE
       const long long prof_start = clock64();
+      unsigned long long prof_fine[4] = {0, 0, 0, 0};
 #endif
       for (int index = blockIdx.x; index < units && ok; index += gridDim.x, ++local) {
         const int acc = local & 1;
@@ -505,7 +560,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         if (!wait(&tmem_empty[acc], acc_phase ^ 1u)) break;
         NML_PROF_END(0);
         tcgen05_fence_after_sync();
-        const uint32_t d_address = tmem_base + (acc * MI + issuer) * BM;
+        const uint32_t d_base = tmem_base + acc * PA * BM;
         int step = 0;  // K step inside the unit
         for (int rs = 0; rs < raw_stages && ok; ++rs) {
           NML_PROF_BEGIN();
@@ -523,22 +578,54 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
               break;
             }
             NML_PROF_END(2);
-            tcgen05_fence_after_sync();
+#ifdef NML_SM100_PROFILE
+            const long long fence_t0 = clock64();
+#endif
+            // Orders this thread's MMAs after the decode threads' tensor-memory stores.  A
+            // decoded tile in shared memory needs no such fence: its writers fenced the async
+            // proxy before they arrived on the barrier.
+            if constexpr (WT) tcgen05_fence_after_sync();
+#ifdef NML_SM100_PROFILE
+            prof_fine[3] += static_cast<unsigned long long>(clock64() - fence_t0);
+#endif
             // Descriptors differ only in the start-address field (16-byte units); each
             // K=16 slice is 32 bytes further along the swizzled 128-byte rows.
-            const uint32_t a_lo = w_desc_lo + wb.index * (kWBytes >> 4);
+            const uint32_t a_lo = WT ? tmem_base + kAccColumns + wb.index * kWColumns
+                                     : w_desc_lo + wb.index * (kWBytes >> 4);
             const uint32_t b_lo =
                 x_desc_lo + raw.index * (L::kRawBytes >> 4) + j * (L::kXBytes >> 4);
-            const bool first = step < MI;  // this issuer's first K step of the unit
+#ifdef NML_SM100_PROFILE
+            const long long issue_t0 = clock64();
+            if (!(p.knockout & 2))
+#endif
 #pragma unroll
             for (int q = 0; q < kTileK / kUmmaK; ++q) {
-              umma_f16_split(d_address, a_lo + 2 * q, b_lo + 2 * q, kUmmaDescHiSw128, idesc,
-                             !(first && q == 0));
+              const int instruction = step * (kTileK / kUmmaK) + q;
+              if constexpr (WT) {
+                umma_f16_tmem_a(d_base + (instruction % PA) * BM, a_lo + q * (kUmmaK / 2),
+                                b_lo + 2 * q, kUmmaDescHiSw128, idesc, instruction >= PA);
+              } else {
+                umma_f16_split(d_base + (instruction % PA) * BM, a_lo + 2 * q, b_lo + 2 * q,
+                               kUmmaDescHiSw128, idesc, instruction >= PA);
+              }
             }
+#ifdef NML_SM100_PROFILE
+            const long long issue_t1 = clock64();
+#endif
             umma_commit(&empty_w[wb.index]);
+#ifdef NML_SM100_PROFILE
+            prof_fine[0] += static_cast<unsigned long long>(issue_t1 - issue_t0);
+            prof_fine[1] += static_cast<unsigned long long>(clock64() - issue_t1);
+#endif
           }
           if constexpr (!kSharedEmpty) {
+#ifdef NML_SM100_PROFILE
+            const long long commit_t0 = clock64();
+#endif
             if (ok) umma_commit(&empty_raw[raw.index]);
+#ifdef NML_SM100_PROFILE
+            prof_fine[2] += static_cast<unsigned long long>(clock64() - commit_t0);
+#endif
           }
           raw.advance<RAW>();
         }
@@ -548,6 +635,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       prof_acc[3] = static_cast<unsigned long long>(clock64() - prof_start);
 #endif
       NML_PROF_FLUSH(4, issuer == 0)
+#ifdef NML_SM100_PROFILE
+      if (issuer == 0) {
+        for (int i = 0; i < 4; ++i) atomicAdd(&g_profile[16 + i], prof_fine[i]);
+      }
+#endif
     }
     __syncwarp();
   } else if (warp < kDecodeWarp0) {
@@ -608,30 +700,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
 #pragma unroll 1
       for (int c = 0; c < BM; c += kChunk) {
         const uint32_t address =
-            tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * MI * BM + c;
+            tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * PA * BM + c;
         uint32_t v[kChunk];
         if constexpr (kChunk == 32) {
           tmem_load_32x32(address, v);
         } else {
           tmem_load_32x16(address, v);
         }
-        if constexpr (MI == 2) {
-          // second issuer's partial sums (odd K steps); absent when the unit has one K step
-          uint32_t v2[kChunk];
-          if constexpr (kChunk == 32) {
-            tmem_load_32x32(address + BM, v2);
-          } else {
-            tmem_load_32x16(address + BM, v2);
-          }
-          tmem_load_wait();
-          if (p.k_steps > 1) {
+        tmem_load_wait();
+        if constexpr (PA > 1) {
+          // add the other partial accumulators in index order; a unit with few K steps has
+          // touched only the first 4 * k_steps of them
+          const int used = min(PA, p.k_steps * (kTileK / kUmmaK));
+#pragma unroll 1
+          for (int partial = 1; partial < used; ++partial) {
+            uint32_t extra[kChunk];
+            if constexpr (kChunk == 32) {
+              tmem_load_32x32(address + partial * BM, extra);
+            } else {
+              tmem_load_32x16(address + partial * BM, extra);
+            }
+            tmem_load_wait();
 #pragma unroll
             for (int j = 0; j < kChunk; ++j) {
-              v[j] = __float_as_uint(__fadd_rn(__uint_as_float(v[j]), __uint_as_float(v2[j])));
+              v[j] = __float_as_uint(__fadd_rn(__uint_as_float(v[j]), __uint_as_float(extra[j])));
             }
           }
         }
-        tmem_load_wait();
         if (c >= u.rows) continue;  // uniform: nothing valid left in this chunk
         if constexpr (MODE == kDense) {
           if (n_ok) {
@@ -685,7 +780,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         }
       }
       tcgen05_fence_before_sync();
-      mbar_arrive(&tmem_empty[acc]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
       NML_PROF_END(1);
     }
     NML_PROF_FLUSH(8, threadIdx.x == 64)
@@ -693,12 +789,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     // -------------------------------------------------------------------- decode
     const int dt = threadIdx.x - kDecodeWarp0 * 32;
     const int group = dt / kGroupThreads;
-    const int row = dt % kGroupThreads;  // weight row of the tile this thread decodes
+    // Weight row of the tile this thread decodes.  A warp may only touch the tensor-memory
+    // lanes 32 * (warp % 4) + lane, and with the weights in tensor memory row = lane.
+    const int row = ((warp & 3) << 5) | lane;
     RingState raw, wb;
     int sequence = 0;  // K steps seen so far by this CTA, over all units
     bool ok = true;
+    int local = 0;
     NML_PROF_DECL
-    for (int index = blockIdx.x; index < units && ok; index += gridDim.x) {
+    for (int index = blockIdx.x; index < units && ok; index += gridDim.x, ++local) {
+      const uint8_t* unit_scales = nullptr;
+      if constexpr (WT) {
+        if (!wait(&full_scale[local & 1], (local >> 1) & 1)) break;
+        unit_scales = scale_buffer(local & 1) + row * p.scale_width;
+      }
       for (int rs = 0; rs < raw_stages && ok; ++rs) {
         NML_PROF_BEGIN();
         if (!wait(&full_raw[raw.index], raw.phase)) {
@@ -716,6 +820,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
           }
           NML_PROF_END(1);
           NML_PROF_BEGIN();
+#ifdef NML_SM100_PROFILE
+          if (p.knockout & 1) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full_w[wb.index]);
+            continue;
+          }
+#endif
           uint4 codes[2];
           if constexpr (KS == 1) {
             const uint4* source =
@@ -728,8 +840,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
             codes[0] = *reinterpret_cast<const uint4*>(source + (((2 * j) ^ (row & 7)) * 16));
             codes[1] = *reinterpret_cast<const uint4*>(source + (((2 * j + 1) ^ (row & 7)) * 16));
           }
-          const uint32_t four_scales = *reinterpret_cast<const uint32_t*>(
-              scale_tile(raw.index) + row * (4 * KS) + j * 4);
+          const uint32_t four_scales =
+              WT ? *reinterpret_cast<const uint32_t*>(unit_scales + (rs * KS + j) * 4)
+                 : *reinterpret_cast<const uint32_t*>(scale_tile(raw.index) + row * (4 * KS) +
+                                                      j * 4);
           uint32_t scale[4];
           if constexpr (AFMT == kAf16) {
             scales2_f16(four_scales & 0xffffu, scale[0], scale[1]);
@@ -738,25 +852,57 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
 #pragma unroll
             for (int b = 0; b < 4; ++b) scale[b] = scale_bf16_dup((four_scales >> (8 * b)) & 0xffu);
           }
-          uint8_t* w_row = w_tile(wb.index) + row * 128;
           const uint32_t words[8] = {codes[0].x, codes[0].y, codes[0].z, codes[0].w,
                                      codes[1].x, codes[1].y, codes[1].z, codes[1].w};
+          if constexpr (WT) {
+            // 32-bit column c of this thread's lane holds elements 2c and 2c + 1 of the row
+            const uint32_t w_address = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
+                                       kAccColumns + wb.index * kWColumns;
+            __syncwarp();
 #pragma unroll
-          for (int jj = 0; jj < 8; ++jj) {
-            uint32_t o[4];
-            if constexpr (AFMT == kAf16) {
-              decode8_f16(words[jj], scale[jj >> 1], o);
-            } else {
-              decode8_bf16(words[jj], scale[jj >> 1], o);
+            for (int pair = 0; pair < 4; ++pair) {
+              uint32_t o[8];
+#pragma unroll
+              for (int half = 0; half < 2; ++half) {
+                uint32_t q4[4];
+                if constexpr (AFMT == kAf16) {
+                  decode8_f16(words[2 * pair + half], scale[pair], q4);
+                } else {
+                  decode8_bf16(words[2 * pair + half], scale[pair], q4);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) o[4 * half + i] = q4[i];
+              }
+              tmem_store_32x8(w_address + pair * 8, o);
             }
-            const int chunk = jj ^ (row & 7);
-            *reinterpret_cast<uint4*>(w_row + chunk * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+            tmem_store_wait();
+            tcgen05_fence_before_sync();
+          } else {
+            uint8_t* w_row = w_tile(wb.index) + row * 128;
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) {
+              uint32_t o[4];
+              if constexpr (AFMT == kAf16) {
+                decode8_f16(words[jj], scale[jj >> 1], o);
+              } else {
+                decode8_bf16(words[jj], scale[jj >> 1], o);
+              }
+              const int chunk = jj ^ (row & 7);
+              *reinterpret_cast<uint4*>(w_row + chunk * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+            fence_proxy_async_smem();
           }
-          fence_proxy_async_smem();
-          mbar_arrive(&full_w[wb.index]);
+          // one arrival per warp: 128 arrivals on one barrier word serialise
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&full_w[wb.index]);
           NML_PROF_END(2);
         }
         raw.advance<RAW>();
+      }
+      if constexpr (WT) {
+        // this warp has read its last scale of the unit: the buffer may be refilled
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_scale[local & 1]);
       }
     }
     NML_PROF_FLUSH(12, dt == 0)
@@ -787,7 +933,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
             asm volatile("cp.async.wait_group 0;" ::: "memory");
           }
           fence_proxy_async_smem();
-          mbar_arrive(&full_raw[arrive.index]);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&full_raw[arrive.index]);
           arrive.advance<RAW>();
           --in_flight;
         }
@@ -899,9 +1046,26 @@ inline bool encode_payload_map(CUtensorMap* map, const uint8_t* payload, int64_t
 
 // Activation tensor [M, K] of 16-bit elements; one box is BM rows x 64 columns, 128B swizzle.
 template <typename T>
-inline bool encode_activation_map(CUtensorMap* map, const void* x, int64_t rows, int K, int BM) {
+inline bool encode_activation_map(CUtensorMap* map, const void* x, int64_t rows, int K, int BM,
+                                  int KS = 1) {
   EncodeTiledFn encode = encode_tiled();
   if (encode == nullptr) return false;
+  if (KS > 1) {
+    // 3-D view [K/64][rows][64] of the same row-major tensor: one box is KS consecutive
+    // 64-column slabs of BM rows, each slab a 128B-swizzled UMMA operand tile.
+    const cuuint64_t dims3[3] = {kTileK, static_cast<cuuint64_t>(rows),
+                                 static_cast<cuuint64_t>(K / kTileK)};
+    const cuuint64_t strides3[2] = {static_cast<cuuint64_t>(K) * 2, kTileK * 2};
+    const cuuint32_t box3[3] = {kTileK, static_cast<cuuint32_t>(BM), static_cast<cuuint32_t>(KS)};
+    const cuuint32_t elem3[3] = {1, 1, 1};
+    const CUtensorMapDataType type3 = std::is_same<T, __half>::value
+                                          ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                          : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    return encode(map, type3, 3, const_cast<void*>(x), dims3, strides3, box3, elem3,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  }
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
   const cuuint32_t box[2] = {kTileK, static_cast<cuuint32_t>(BM)};

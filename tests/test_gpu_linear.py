@@ -78,17 +78,35 @@ UMMA_CASES = [(1, 64, 128), (16, 128, 128), (17, 256, 200), (64, 2880, 2880), (1
               (130, 512, 384), (300, 1024, 256), (1, 2880, 5760)]
 
 
+# POLICY_UMMA picks the variant with decoded weights in tensor memory where the shape allows
+# it (outputs a multiple of 4, K <= 3072); POLICY_UMMA_SMEM forces the shared-memory ring.
 @pytest.mark.parametrize("M,K,N", UMMA_CASES)
 def test_tensor_core_kernel_f16_activations(M, K, N):
     from nml_b200 import _abi
     run_linear(M, K, N, oracle.F16, _abi.POLICY_UMMA, with_bias=(M % 2 == 0), seed=M + N,
-               expect_kernel="umma_swapab_af16")
+               expect_kernel="umma_tmem_weights_af16" if M <= 200 else "umma_swapab_af16")
 
 
 @pytest.mark.parametrize("M,K,N", UMMA_CASES)
 def test_tensor_core_kernel_bf16_activations(M, K, N):
     from nml_b200 import _abi
     run_linear(M, K, N, oracle.BF16, _abi.POLICY_UMMA, with_bias=(M % 2 == 1), seed=M + N,
+               expect_kernel="umma_tmem_weights_abf16" if M <= 200 else "umma_swapab_abf16")
+
+
+@pytest.mark.parametrize("dtype", [oracle.BF16, oracle.F16])
+@pytest.mark.parametrize("M,K,N", UMMA_CASES + [(16, 4096, 2880), (64, 128, 130)])
+def test_tensor_core_kernel_shared_memory_weight_ring(M, K, N, dtype):
+    from nml_b200 import _abi
+    run_linear(M, K, N, dtype, _abi.POLICY_UMMA_SMEM, with_bias=(M % 2 == 1), seed=M + N + 1,
+               expect_kernel="umma_swapab_a")
+
+
+@pytest.mark.parametrize("M,K,N", [(16, 4096, 2880), (64, 128, 130), (33, 3136, 512)])
+def test_tensor_core_kernel_falls_back_to_shared_memory_ring(M, K, N):
+    # K above the scale buffer, or an output count that breaks the bulk scale copy
+    from nml_b200 import _abi
+    run_linear(M, K, N, oracle.BF16, _abi.POLICY_UMMA, seed=M + N + 2,
                expect_kernel="umma_swapab_abf16")
 
 

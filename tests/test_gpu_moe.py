@@ -211,13 +211,16 @@ def test_contract_experts_closed_form_inputs(dtype, t, tokens):
     (700, 8, 4, 512, 384, oracle.BF16),    # ~350: 256-slot tiles, several slot tiles per expert
     (96, 32, 4, 2880, 2880, oracle.BF16),  # GPT-OSS widths, 128-row tail tile on the down side
 ])
-def test_routed_experts_tensor_core_kernel(tokens, E, k, H, I, dtype):
+@pytest.mark.parametrize("weights_in_smem", [False, True])
+def test_routed_experts_tensor_core_kernel(tokens, E, k, H, I, dtype, weights_in_smem):
+    # both homes of the decoded weight tiles: tensor memory (default) and the shared-memory ring
     from nml_b200 import _abi
     mask = None
     if tokens >= 40:
         mask = np.ones(tokens, np.uint8)
         mask[rng(tokens).integers(0, tokens, tokens // 9)] = 0
-    run_routed(tokens, H, E, I, k, dtype, _abi.POLICY_UMMA, seed=tokens + E, mask=mask)
+    policy = _abi.POLICY_UMMA_SMEM if weights_in_smem else _abi.POLICY_UMMA
+    run_routed(tokens, H, E, I, k, dtype, policy, seed=tokens + E, mask=mask)
 
 
 def test_tensor_core_experts_match_portable_kernel_with_expert_offset():
