@@ -369,7 +369,8 @@ int32_t nml_nvfp4_sm100_plan_capacity(int64_t assignments, int64_t experts, int6
 
 /* Device status word of the current device: 0 when healthy, else an OR of the bits below.
  * Kernels never trap; a bounded wait that runs out or an out-of-range index records a
- * bit here and the kernel returns.  Reading synchronises `stream`; `clear` resets it. */
+ * bit here and the kernel returns.  Bits 8 and up say which wait of the tcgen05 kernel ran
+ * out (diagnostic only).  Reading synchronises `stream`; `clear` resets it. */
 #define NML_SM100_STATUS_BARRIER_TIMEOUT 1
 #define NML_SM100_STATUS_TMEM_ALLOC 2
 #define NML_SM100_STATUS_INDEX_RANGE 4

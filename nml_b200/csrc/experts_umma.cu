@@ -154,6 +154,14 @@ bool experts_umma_supported(const ExpertArgs& args) {
          reinterpret_cast<uintptr_t>(args.block_scales) % 4 == 0;
 }
 
+#ifdef NML_SM100_DEBUG_WAITS
+extern "C" int nml_nvfp4_sm100_debug_waits(int* out) {
+  static int zero[160 * 11 * 8] = {};
+  if (cudaMemcpyFromSymbol(out, umma::g_wait_debug, sizeof(zero)) != cudaSuccess) return 1;
+  return cudaMemcpyToSymbol(umma::g_wait_debug, zero, sizeof(zero)) == cudaSuccess ? 0 : 1;
+}
+#endif
+
 int32_t launch_experts_umma(const ExpertArgs& args, const DeviceInfo& device, char* message,
                             size_t capacity) {
   return args.gate_up ? launch_mode<kGateUp>(args, device, message, capacity)

@@ -110,9 +110,9 @@ int32_t launch_for_rows(const LinearArgs& args, const DeviceInfo& device, char* 
   }
   switch (tile_rows) {
     case 16:
-      return launch_config<16, 4, 5, 4, 3, 2, 8, false, AFMT, T>(args, device, message, capacity);
+      return launch_config<16, 4, 5, 4, 3, 1, 8, false, AFMT, T>(args, device, message, capacity);
     case 32:
-      return launch_config<32, 4, 4, 4, 3, 2, 8, false, AFMT, T>(args, device, message, capacity);
+      return launch_config<32, 4, 4, 4, 3, 1, 8, false, AFMT, T>(args, device, message, capacity);
     case 64:
       return launch_config<64, 4, 3, 4, 3, 1, 4, false, AFMT, T>(args, device, message, capacity);
     case 128:

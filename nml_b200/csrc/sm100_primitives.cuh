@@ -195,6 +195,89 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                : "memory");
 }
 
+// ---- warp-uniform issue -------------------------------------------------------
+// The forms below are executed by every lane of a converged warp; one elected lane issues
+// the instruction.  Code that reaches a tcgen05.mma under `if (lane == 0)` is divergent to
+// the compiler, which then moves every descriptor from vector to uniform registers again
+// for each instruction: about 80 cycles of the issuing thread per MMA beside busy warps,
+// against about 25 when the surrounding loop is uniform.
+__device__ __forceinline__ void umma_commit_elect(uint64_t* bar) {
+  asm volatile(
+      "{\n"
+      ".reg .pred pe;\n"
+      "elect.sync _|pe, 0xffffffff;\n"
+      "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+      "}\n"
+      :
+      : "r"(smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_f16_elect(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred pe, pa;\n"
+      "elect.sync _|pe, 0xffffffff;\n"
+      "setp.ne.b32 pa, %4, 0;\n"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, pa;\n"
+      "}\n"
+      :
+      : "r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// A operand in tensor memory (lane = row of A, 32-bit column c = elements 2c and 2c + 1 of
+// the K = 16 slice), B operand in shared memory.
+__device__ __forceinline__ void umma_f16_tmem_a_elect(uint32_t tmem_d, uint32_t tmem_a,
+                                                      uint64_t b_desc, uint32_t idesc,
+                                                      uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred pe, pa;\n"
+      "elect.sync _|pe, 0xffffffff;\n"
+      "setp.ne.b32 pa, %4, 0;\n"
+      "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, pa;\n"
+      "}\n"
+      :
+      : "r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Bounded wait with no result, so that the caller's control flow stays uniform.  When the
+// polls run out it raises the CTA's abort flag and the BARRIER_TIMEOUT status bit; once the
+// abort flag is up, by this or any other role, every later call returns at once, so the
+// caller runs out its (bounded) loops on whatever data is there and the host sees the status.
+__device__ __forceinline__ void mbar_wait_or_abort(uint64_t* bar, uint32_t parity,
+                                                   volatile int* abort_flag, int* status,
+                                                   int site) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      ".reg .u32 n, f;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%0], %1;\n"
+      "@p bra WAIT_DONE;\n"
+      "mov.u32 n, 0;\n"
+      "WAIT_LOOP:\n"
+      "ld.volatile.shared.u32 f, [%2];\n"
+      "setp.ne.u32 q, f, 0;\n"
+      "@q bra WAIT_DONE;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%0], %1;\n"
+      "@p bra WAIT_DONE;\n"
+      "add.u32 n, n, 1;\n"
+      "setp.lt.u32 q, n, %4;\n"
+      "@q bra WAIT_LOOP;\n"
+      "st.volatile.shared.u32 [%2], 1;\n"
+      "red.global.or.b32 [%3], %5;\n"
+      "WAIT_DONE:\n"
+      "}\n"
+      :
+      : "r"(smem_u32(bar)), "r"(parity),
+        "r"(smem_u32(const_cast<int*>(abort_flag))), "l"(status), "r"(kWaitPolls),
+        "r"(1 | (0x100 << site))
+      : "memory");
+}
+
 // 32 lanes x 32 consecutive 32-bit columns: thread L of the warp receives
 // columns [c, c+32) of TMEM lane (lane_base + L).
 __device__ __forceinline__ void tmem_load_32x32(uint32_t address, uint32_t (&v)[32]) {

@@ -324,6 +324,27 @@ static __device__ unsigned long long g_profile[24];
 #define NML_PROF_FLUSH(base, leader)
 #endif
 
+// Which bounded wait ran out: bit (8 + site) of the device status word.
+enum WaitSite : int {
+  kSiteProducerRaw = 0,
+  kSiteProducerScale = 1,
+  kSiteProducerDrain = 2,
+  kSiteMmaAccumulator = 3,
+  kSiteMmaRaw = 4,
+  kSiteMmaWeights = 5,
+  kSiteEpilogue = 6,
+  kSiteDecodeRaw = 7,
+  kSiteDecodeWeights = 8,
+  kSiteDecodeScale = 9,
+  kSiteGather = 10,
+};
+
+#ifdef NML_SM100_DEBUG_WAITS
+// Where each role of each CTA stood when a wait ran out (diagnostic builds only).
+static __device__ int g_wait_debug[160][11][8];
+struct WaitPosition { int unit = -1, stage = -1, step = -1; };
+#endif
+
 struct RingState {
   int index = 0;
   uint32_t phase = 0;
@@ -430,18 +451,43 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
   const int units = total_units<BM, GROUPED>(p, groups);
   const int raw_stages = (p.k_steps + KS - 1) / KS;
 
-  auto give_up = [&]() {
+  // `site` says which wait ran out (diagnostic bits 8.. of the status word).
+  auto give_up = [&](int site) {
     *abort_flag = 1;
-    atomicOr(p.status, NML_SM100_STATUS_BARRIER_TIMEOUT);
+    atomicOr(p.status, NML_SM100_STATUS_BARRIER_TIMEOUT | (0x100 << site));
   };
   // Bounded wait that also honours an abort raised by another role.
-  auto wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+#ifdef NML_SM100_DEBUG_WAITS
+  WaitPosition wait_position;
+  auto record = [&](uint64_t* bar, uint32_t parity, int site, int how) {
+    if (blockIdx.x < 160 && (threadIdx.x & 31) == 0) {
+      int* d = g_wait_debug[blockIdx.x][site];
+      d[0] = how;
+      d[1] = wait_position.unit;
+      d[2] = wait_position.stage;
+      d[3] = wait_position.step;
+      d[4] = static_cast<int>(bar - bars);
+      d[5] = static_cast<int>(parity);
+      d[6] = threadIdx.x >> 5;
+      d[7] = static_cast<int>(*reinterpret_cast<volatile uint64_t*>(bar) & 0xffffffffu);
+    }
+  };
+#endif
+  auto wait = [&](uint64_t* bar, uint32_t parity, int site) -> bool {
     if (mbar_try_wait(bar, parity)) return true;  // fast path: no shared-memory flag read
     for (uint32_t poll = 0; poll < kWaitPolls; ++poll) {
       if (mbar_try_wait(bar, parity)) return true;
-      if ((poll & 63u) == 63u && *abort_flag) return false;
+      if ((poll & 63u) == 63u && *abort_flag) {
+#ifdef NML_SM100_DEBUG_WAITS
+        record(bar, parity, site, 2);
+#endif
+        return false;
+      }
     }
-    give_up();
+#ifdef NML_SM100_DEBUG_WAITS
+    record(bar, parity, site, 1);
+#endif
+    give_up(site);
     return false;
   };
   // With one K step per raw stage the two rings advance in lockstep, so the commit that
@@ -459,10 +505,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     NML_PROF_DECL
     for (int index = blockIdx.x; index < units && ok; index += gridDim.x, ++local) {
       const Unit u = get_unit<BM, GROUPED>(p, groups, index);
+#ifdef NML_SM100_DEBUG_WAITS
+      wait_position.unit = local;
+#endif
       if constexpr (WT) {
         // all block scales of the unit's weight rows: one contiguous range of the tensor
         const int b = local & 1;
-        if (!wait(&empty_scale[b], ((local >> 1) & 1) ^ 1u)) break;
+        if (!wait(&empty_scale[b], ((local >> 1) & 1) ^ 1u, kSiteProducerScale)) break;
         if (lane == 0) {
           const int rows = min(kTileN, p.weight_rows_total - u.weight_row0);
           const uint32_t bytes = static_cast<uint32_t>(rows * p.scale_width);
@@ -474,7 +523,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       }
       for (int rs = 0; rs < raw_stages; ++rs) {
         NML_PROF_BEGIN();
-        if (!wait(&raw_free[raw.index], raw.phase ^ 1u)) {
+#ifdef NML_SM100_DEBUG_WAITS
+        wait_position.stage = rs;
+#endif
+        if (!wait(&raw_free[raw.index], raw.phase ^ 1u, kSiteProducerRaw)) {
           ok = false;
           break;
         }
@@ -523,77 +575,105 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     for (int i = 0; i < pending; ++i) {
       raw.index = raw.index == 0 ? RAW - 1 : raw.index - 1;
       if (raw.index == RAW - 1) raw.phase ^= 1u;
-      if (!mbar_wait(&full_raw[raw.index], raw.phase)) give_up();
+      if (!mbar_wait(&full_raw[raw.index], raw.phase)) give_up(kSiteProducerDrain);
     }
     if constexpr (WT) {
       for (int back = 1; back <= 2 && back <= local; ++back) {
         const int unit = local - back;
-        if (!mbar_wait(&full_scale[unit & 1], (unit >> 1) & 1)) give_up();
+        if (!mbar_wait(&full_scale[unit & 1], (unit >> 1) & 1)) give_up(kSiteProducerDrain);
       }
     }
     NML_PROF_FLUSH(0, lane == 0)
   } else if (warp == kMmaWarp || (MI == 2 && warp == kMmaWarpB)) {
     // ----------------------------------------------------------------------- MMA
-    // With MI == 2 two threads (in two warps) issue alternate K steps of a unit into two
-    // accumulators that the epilogue adds in a fixed order.  Issuing four MMAs and a commit
-    // costs one thread several hundred cycles, which bounds small tiles; splitting the
-    // issue stream halves that bound and stays deterministic.
+    // With MI == 2 two warps issue alternate K steps into disjoint partial accumulators that
+    // the epilogue adds in a fixed order, so the split stays deterministic.  Ownership
+    // follows the parity of the K step's position in the CTA's whole sequence (not inside
+    // the unit): with an even ring depth every W' slot then has one consumer for good.  A
+    // parity wait cannot tell "phase k done" from "phase k - 1 not yet done", so a consumer
+    // may only wait on a slot whose previous use it has consumed itself; an issuer that took
+    // over a slot at a unit boundary (odd K steps per unit) could run ahead of the other
+    // issuer and pass that wait a whole phase early.
     const int issuer = warp == kMmaWarp ? 0 : 1;
-    if (lane == 0) {
+    static_assert(MI == 1 || WB % 2 == 0, "two issuers need an even W' ring depth");
+    // The decode side has the mirror-image rule: group g may wait for the consumption of
+    // position Q - WB only when Q - 2 WB is known consumed.  Its own history gives
+    // Q - i DG - WB consumed; with one in-order issuer i = 1 suffices (WB >= DG), with two
+    // the position must also share Q's parity, i.e. i DG even.
+    static_assert(MI == 1 || (DG % 2 == 0 ? DG : 2 * DG) <= WB,
+                  "W' ring too shallow for two issuers");
+    // Every lane runs this loop and one elected lane issues: the loop then is uniform to the
+    // compiler, which keeps descriptors and addresses in uniform registers.  The waits return
+    // nothing (see mbar_wait_or_abort), so a timeout does not make the control flow divergent.
+    {
       constexpr uint32_t a_format = AFMT == kAf16 ? kUmmaF16 : kUmmaBF16;
       constexpr uint32_t b_format = std::is_same<T, __half>::value ? kUmmaF16 : kUmmaBF16;
       constexpr uint32_t idesc = umma_idesc_f16(a_format, b_format, kTileN, BM);
+      constexpr uint64_t desc_hi = static_cast<uint64_t>(kUmmaDescHiSw128) << 32;
       RingState raw, wb;
       int local = 0;
-      bool ok = true;
-      const uint32_t w_desc_lo = WT ? 0u : umma_desc_lo(smem_u32(w_tile(0)));
-      const uint32_t x_desc_lo = umma_desc_lo(smem_u32(x_tile(0, 0)));
+      int sequence = 0;  // K steps seen so far by this CTA, over all units
+      const uint64_t w_desc = desc_hi | (WT ? 0u : umma_desc_lo(smem_u32(w_tile(0))));
+      const uint64_t x_desc = desc_hi | umma_desc_lo(smem_u32(x_tile(0, 0)));
       NML_PROF_DECL
 #ifdef NML_SM100_PROFILE
       const long long prof_start = clock64();
       unsigned long long prof_fine[4] = {0, 0, 0, 0};
 #endif
-      for (int index = blockIdx.x; index < units && ok; index += gridDim.x, ++local) {
+      for (int index = blockIdx.x; index < units; index += gridDim.x, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
         NML_PROF_BEGIN();
-        if (!wait(&tmem_empty[acc], acc_phase ^ 1u)) break;
+#ifdef NML_SM100_DEBUG_WAITS
+        wait_position.unit = local;
+#endif
+        mbar_wait_or_abort(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, p.status,
+                           kSiteMmaAccumulator);
+#ifdef NML_SM100_DEBUG_WAITS
+        if (*abort_flag && issuer == 0) record(&tmem_empty[acc], acc_phase ^ 1u, kSiteMmaAccumulator, 3);
+#endif
         NML_PROF_END(0);
         tcgen05_fence_after_sync();
         const uint32_t d_base = tmem_base + acc * PA * BM;
         int step = 0;  // K step inside the unit
-        for (int rs = 0; rs < raw_stages && ok; ++rs) {
+        for (int rs = 0; rs < raw_stages; ++rs) {
           NML_PROF_BEGIN();
-          if (!wait(&full_raw[raw.index], raw.phase)) {
-            ok = false;
-            break;
+#ifdef NML_SM100_DEBUG_WAITS
+          wait_position.stage = rs;
+#endif
+          mbar_wait_or_abort(&full_raw[raw.index], raw.phase, abort_flag, p.status,
+                             kSiteMmaRaw);
+#ifdef NML_SM100_DEBUG_WAITS
+          if (*abort_flag && g_wait_debug[blockIdx.x & 127][kSiteMmaRaw + issuer * 0][0] == 0) {
+            record(&full_raw[raw.index], raw.phase, issuer == 0 ? kSiteMmaRaw : kSiteMmaAccumulator, 3);
           }
+#endif
           NML_PROF_END(1);
           const int sub_steps = min(KS, p.k_steps - rs * KS);
-          for (int j = 0; j < sub_steps; ++j, ++step, wb.advance<WB>()) {
-            if (MI == 2 && (step & 1) != issuer) continue;
+          for (int j = 0; j < sub_steps; ++j, ++step, ++sequence, wb.advance<WB>()) {
+            if (MI == 2 && (sequence & 1) != issuer) continue;
             NML_PROF_BEGIN();
-            if (!wait(&full_w[wb.index], wb.phase)) {
-              ok = false;
-              break;
+#ifdef NML_SM100_DEBUG_WAITS
+            wait_position.step = step;
+#endif
+            mbar_wait_or_abort(&full_w[wb.index], wb.phase, abort_flag, p.status,
+                               kSiteMmaWeights);
+#ifdef NML_SM100_DEBUG_WAITS
+            if (*abort_flag && g_wait_debug[blockIdx.x & 127][issuer == 0 ? kSiteMmaWeights : kSiteProducerDrain][0] == 0) {
+              record(&full_w[wb.index], wb.phase, issuer == 0 ? kSiteMmaWeights : kSiteProducerDrain, 3);
             }
+#endif
             NML_PROF_END(2);
-#ifdef NML_SM100_PROFILE
-            const long long fence_t0 = clock64();
-#endif
-            // Orders this thread's MMAs after the decode threads' tensor-memory stores.  A
-            // decoded tile in shared memory needs no such fence: its writers fenced the async
-            // proxy before they arrived on the barrier.
+            // Orders the MMAs after the decode threads' tensor-memory stores.  A decoded tile
+            // in shared memory needs no such fence: its writers fenced the async proxy before
+            // they arrived on the barrier.
             if constexpr (WT) tcgen05_fence_after_sync();
-#ifdef NML_SM100_PROFILE
-            prof_fine[3] += static_cast<unsigned long long>(clock64() - fence_t0);
-#endif
             // Descriptors differ only in the start-address field (16-byte units); each
             // K=16 slice is 32 bytes further along the swizzled 128-byte rows.
-            const uint32_t a_lo = WT ? tmem_base + kAccColumns + wb.index * kWColumns
-                                     : w_desc_lo + wb.index * (kWBytes >> 4);
-            const uint32_t b_lo =
-                x_desc_lo + raw.index * (L::kRawBytes >> 4) + j * (L::kXBytes >> 4);
+            const uint32_t a_tmem = tmem_base + kAccColumns + wb.index * kWColumns;
+            const uint64_t a_desc = w_desc + wb.index * (kWBytes >> 4);
+            const uint64_t b_desc =
+                x_desc + raw.index * (L::kRawBytes >> 4) + j * (L::kXBytes >> 4);
 #ifdef NML_SM100_PROFILE
             const long long issue_t0 = clock64();
             if (!(p.knockout & 2))
@@ -601,18 +681,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
 #pragma unroll
             for (int q = 0; q < kTileK / kUmmaK; ++q) {
               const int instruction = step * (kTileK / kUmmaK) + q;
+              const uint32_t d = d_base + (instruction % PA) * BM;
+              const uint32_t accumulate = instruction >= PA ? 1u : 0u;
               if constexpr (WT) {
-                umma_f16_tmem_a(d_base + (instruction % PA) * BM, a_lo + q * (kUmmaK / 2),
-                                b_lo + 2 * q, kUmmaDescHiSw128, idesc, instruction >= PA);
+                umma_f16_tmem_a_elect(d, a_tmem + q * (kUmmaK / 2), b_desc + 2 * q, idesc,
+                                      accumulate);
               } else {
-                umma_f16_split(d_base + (instruction % PA) * BM, a_lo + 2 * q, b_lo + 2 * q,
-                               kUmmaDescHiSw128, idesc, instruction >= PA);
+                umma_f16_elect(d, a_desc + 2 * q, b_desc + 2 * q, idesc, accumulate);
               }
             }
 #ifdef NML_SM100_PROFILE
             const long long issue_t1 = clock64();
 #endif
-            umma_commit(&empty_w[wb.index]);
+            umma_commit_elect(&empty_w[wb.index]);
 #ifdef NML_SM100_PROFILE
             prof_fine[0] += static_cast<unsigned long long>(issue_t1 - issue_t0);
             prof_fine[1] += static_cast<unsigned long long>(clock64() - issue_t1);
@@ -622,21 +703,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
 #ifdef NML_SM100_PROFILE
             const long long commit_t0 = clock64();
 #endif
-            if (ok) umma_commit(&empty_raw[raw.index]);
+            umma_commit_elect(&empty_raw[raw.index]);
 #ifdef NML_SM100_PROFILE
             prof_fine[2] += static_cast<unsigned long long>(clock64() - commit_t0);
 #endif
           }
           raw.advance<RAW>();
         }
-        if (ok) umma_commit(&tmem_full[acc]);
+        umma_commit_elect(&tmem_full[acc]);
       }
 #ifdef NML_SM100_PROFILE
       prof_acc[3] = static_cast<unsigned long long>(clock64() - prof_start);
 #endif
-      NML_PROF_FLUSH(4, issuer == 0)
+      NML_PROF_FLUSH(4, issuer == 0 && lane == 0)
 #ifdef NML_SM100_PROFILE
-      if (issuer == 0) {
+      if (issuer == 0 && lane == 0) {
         for (int i = 0; i < 4; ++i) atomicAdd(&g_profile[16 + i], prof_fine[i]);
       }
 #endif
@@ -656,7 +737,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       NML_PROF_BEGIN();
-      if (!wait(&tmem_full[acc], acc_phase)) break;
+#ifdef NML_SM100_DEBUG_WAITS
+      wait_position.unit = local;
+#endif
+      if (!wait(&tmem_full[acc], acc_phase, kSiteEpilogue)) break;
       NML_PROF_END(0);
       NML_PROF_BEGIN();
       tcgen05_fence_after_sync();
@@ -800,12 +884,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     for (int index = blockIdx.x; index < units && ok; index += gridDim.x, ++local) {
       const uint8_t* unit_scales = nullptr;
       if constexpr (WT) {
-        if (!wait(&full_scale[local & 1], (local >> 1) & 1)) break;
+        if (!wait(&full_scale[local & 1], (local >> 1) & 1, kSiteDecodeScale)) break;
         unit_scales = scale_buffer(local & 1) + row * p.scale_width;
       }
       for (int rs = 0; rs < raw_stages && ok; ++rs) {
         NML_PROF_BEGIN();
-        if (!wait(&full_raw[raw.index], raw.phase)) {
+#ifdef NML_SM100_DEBUG_WAITS
+        wait_position.unit = local;
+        wait_position.stage = rs;
+#endif
+        if (!wait(&full_raw[raw.index], raw.phase, kSiteDecodeRaw)) {
           ok = false;
           break;
         }
@@ -814,7 +902,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         for (int j = 0; j < sub_steps; ++j, ++sequence, wb.advance<WB>()) {
           if (sequence % DG != group) continue;
           NML_PROF_BEGIN();
-          if (!wait(&empty_w[wb.index], wb.phase ^ 1u)) {
+#ifdef NML_SM100_DEBUG_WAITS
+          wait_position.step = sequence;
+#endif
+          if (!wait(&empty_w[wb.index], wb.phase ^ 1u, kSiteDecodeWeights)) {
             ok = false;
             break;
           }
@@ -956,7 +1047,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         }
         for (int rs = 0; rs < raw_stages; ++rs) {
           NML_PROF_BEGIN();
-          if (!wait(&raw_free[raw.index], raw.phase ^ 1u)) {
+#ifdef NML_SM100_DEBUG_WAITS
+          wait_position.stage = rs;
+          wait_position.step = in_flight;
+#endif
+          if (!wait(&raw_free[raw.index], raw.phase ^ 1u, kSiteGather)) {
             ok = false;
             break;
           }

@@ -79,19 +79,20 @@ UMMA_CASES = [(1, 64, 128), (16, 128, 128), (17, 256, 200), (64, 2880, 2880), (1
 
 
 # POLICY_UMMA picks the variant with decoded weights in tensor memory where the shape allows
-# it (outputs a multiple of 4, K <= 3072); POLICY_UMMA_SMEM forces the shared-memory ring.
+# it (outputs a multiple of 4, K <= 3072, tiles of at most 128 activation rows, which all of
+# these cases get); POLICY_UMMA_SMEM forces the shared-memory ring.
 @pytest.mark.parametrize("M,K,N", UMMA_CASES)
 def test_tensor_core_kernel_f16_activations(M, K, N):
     from nml_b200 import _abi
     run_linear(M, K, N, oracle.F16, _abi.POLICY_UMMA, with_bias=(M % 2 == 0), seed=M + N,
-               expect_kernel="umma_tmem_weights_af16" if M <= 200 else "umma_swapab_af16")
+               expect_kernel="umma_tmem_weights_af16")
 
 
 @pytest.mark.parametrize("M,K,N", UMMA_CASES)
 def test_tensor_core_kernel_bf16_activations(M, K, N):
     from nml_b200 import _abi
     run_linear(M, K, N, oracle.BF16, _abi.POLICY_UMMA, with_bias=(M % 2 == 1), seed=M + N,
-               expect_kernel="umma_tmem_weights_abf16" if M <= 200 else "umma_swapab_abf16")
+               expect_kernel="umma_tmem_weights_abf16")
 
 
 @pytest.mark.parametrize("dtype", [oracle.BF16, oracle.F16])
