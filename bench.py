@@ -13,8 +13,8 @@ data-path collective).
 
 Prints ONE JSON line (rank 0).  `value` is whole-job TFLOP/s with inputs resident in HBM;
 `e2e` is the same pass driven from pinned host buffers with the host<->device copies inside
-the timed region; `roofline` describes the dominant kernel (the tcgen05 linear, 256-row
-activation tiles) against the measured bf16 tensor peak; `cpu_baseline` times the CPU
+the timed region; `roofline` describes the dominant kernel (the tcgen05 linear with its
+192/256-row activation tiles) against the measured bf16 tensor peak; `cpu_baseline` times the CPU
 restatement of the reference's kernel on this host.  `--impl reference` times only that CPU
 restatement (the reference itself is Rust behind Bazel and cannot be built here).
 """
@@ -224,14 +224,6 @@ def run_reference_arm(args) -> None:
 
 # ---------------------------------------------------------------------- GPU arm
 
-def tile_rows(m: int) -> int:
-    """Activation-tile height the tcgen05 linear selects for M rows."""
-    for tile in (16, 32, 64, 128):
-        if m <= tile:
-            return tile
-    return 256
-
-
 def select(args):
     shapes = SHAPES
     rows = ROWS
@@ -285,6 +277,8 @@ def run_ours(args) -> None:
     cases = [(name, k, n, m) for name, k, n in shapes for m in rows]
     torch.cuda.synchronize()
 
+    selected = {}  # case -> (kernel family, activation rows per tile) the library chose
+
     def one_pass(events=None):
         for index, (name, k, n, m) in enumerate(cases):
             if events is not None:
@@ -292,6 +286,9 @@ def run_ours(args) -> None:
             ops.linear(activations[(k, m)], weights[name], out=outputs[(name, m)])
             if events is not None:
                 events[index][1].record()
+            elif (name, k, n, m) not in selected:
+                selected[(name, k, n, m)] = (_abi.last_linear_kernel(),
+                                             _abi.last_linear_tile_rows())
 
     def barrier():
         if world > 1:
@@ -335,13 +332,16 @@ def run_ours(args) -> None:
                  for s in range(args.steps)]
         durations[case] = sum(times) / len(times)
     peaks = measured_peaks()
-    dominant = [c for c in cases if tile_rows(c[3]) == 256]
+    # the dominant kernel: the tcgen05 linear with its largest activation tiles (M >= 512)
+    dominant = [c for c in cases if selected.get(c, ("", 0))[1] >= 192]
     roofline = None
     if dominant:
         d_flops = sum(2.0 * m * k * n for _, k, n, m in dominant)
         d_time = sum(durations[c] for c in dominant)
         achieved = d_flops / d_time / 1e12
-        roofline = {"bound": "tensor", "kernel": "linear_umma_kernel<BM=256, bf16 operands>",
+        variants = sorted({f"{selected[c][0]}/BM={selected[c][1]}" for c in dominant})
+        roofline = {"bound": "tensor",
+                    "kernel": "umma::gemm_kernel dense, bf16 operands: " + ", ".join(variants),
                     "achieved": achieved, "peak": peaks["bf16_tflops_sustained"],
                     "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops_sustained"],
                     "peak_source": f"bf16_tflops_sustained of {peaks['source']} "
@@ -349,7 +349,7 @@ def run_ours(args) -> None:
                                    "bf16 decodes of the NVFP4 weights",
                     "launches_per_step": len(dominant),
                     "avg_launch_ms": d_time / len(dominant) * 1e3,
-                    "traffic": NCU_TRAFFIC.get("linear_umma_bm256")}
+                    "traffic": NCU_TRAFFIC["gemm_kernel_large_tiles"]}
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -367,7 +367,8 @@ def run_ours(args) -> None:
     }
 
     if rank == 0 and not args.no_detail:
-        line["shapes"] = shape_table(cases, durations, weights, activations, outputs, peaks)
+        line["shapes"] = shape_table(cases, durations, weights, activations, outputs, peaks,
+                                     selected)
     if not args.no_e2e:
         line["e2e"] = end_to_end(args, cases, weights, activations, outputs, world, barrier,
                                  flops_per_pass)
@@ -390,10 +391,10 @@ def run_ours(args) -> None:
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from ncu captures, filled in from
 # the summaries under profiles/ (None until a capture exists).
-NCU_TRAFFIC = {"linear_umma_bm256": None}
+NCU_TRAFFIC = {"gemm_kernel_large_tiles": None}
 
 
-def shape_table(cases, durations, weights, activations, outputs, peaks):
+def shape_table(cases, durations, weights, activations, outputs, peaks, selected):
     """Per (shape, M) figures.  Large M: device time of the launch inside the timed region.
     M <= 64 is HBM-bound and the four small weights fit in L2, so those cases are timed
     again over a rotation of distinct weight copies (>= 600 MB in total) to read them cold
@@ -405,7 +406,8 @@ def shape_table(cases, durations, weights, activations, outputs, peaks):
         flops = 2.0 * m * k * n
         nbytes = linear_bytes(m, k, n)
         warm = durations[(name, k, n, m)]
-        entry = {"shape": f"{k}->{n}", "name": name, "M": m, "tile_rows": tile_rows(m),
+        family, tile = selected.get((name, k, n, m), ("", 0))
+        entry = {"shape": f"{k}->{n}", "name": name, "M": m, "tile_rows": tile, "kernel": family,
                  "us": warm * 1e6, "tflops": flops / warm / 1e12, "gbs": nbytes / warm / 1e9}
         if m <= 64:
             weight = weights[name]

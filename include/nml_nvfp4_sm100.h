@@ -386,6 +386,8 @@ int32_t nml_nvfp4_sm100_set_kernel_policy(int32_t policy);
  * ("umma_tmem_weights_af16", "umma_tmem_weights_abf16", "umma_swapab_af16",
  * "umma_swapab_abf16", "simt"), for tests and benchmark records. */
 const char *nml_nvfp4_sm100_last_linear_kernel(void);
+/* Activation rows per tile of that launch (0 for the SIMT kernel). */
+int32_t nml_nvfp4_sm100_last_linear_tile_rows(void);
 
 /* ABI version of this header. */
 #define NML_NVFP4_SM100_ABI_VERSION 1

@@ -142,6 +142,7 @@ OTHER_ENTRY_POINTS = [
     "nml_nvfp4_sm100_device_status",
     "nml_nvfp4_sm100_set_kernel_policy",
     "nml_nvfp4_sm100_last_linear_kernel",
+    "nml_nvfp4_sm100_last_linear_tile_rows",
     "nml_nvfp4_sm100_abi_version",
 ]
 
@@ -183,6 +184,8 @@ def load() -> ctypes.CDLL:
     lib.nml_nvfp4_sm100_set_kernel_policy.argtypes = [_i32]
     lib.nml_nvfp4_sm100_last_linear_kernel.restype = ctypes.c_char_p
     lib.nml_nvfp4_sm100_last_linear_kernel.argtypes = []
+    lib.nml_nvfp4_sm100_last_linear_tile_rows.restype = _i32
+    lib.nml_nvfp4_sm100_last_linear_tile_rows.argtypes = []
     lib.nml_nvfp4_sm100_abi_version.restype = _i32
     lib.nml_nvfp4_sm100_abi_version.argtypes = []
     _LIB = lib
@@ -218,6 +221,10 @@ def plan_capacity(assignments: int, experts: int):
 
 def set_kernel_policy(policy: int) -> int:
     return load().nml_nvfp4_sm100_set_kernel_policy(policy)
+
+
+def last_linear_tile_rows() -> int:
+    return int(load().nml_nvfp4_sm100_last_linear_tile_rows())
 
 
 def last_linear_kernel() -> str:

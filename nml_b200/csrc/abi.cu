@@ -20,13 +20,17 @@ static __device__ __align__(256) unsigned char g_static_scratch[NML_SM100_STATIC
 namespace {
 std::atomic<int> g_kernel_policy{0};
 thread_local const char* t_last_linear_kernel = "none";
+thread_local int t_last_linear_tile_rows = 0;
 constexpr int kMaxDevices = 64;
 DeviceInfo g_devices[kMaxDevices];
 std::atomic<int> g_device_ready[kMaxDevices];
 }  // namespace
 
 int get_kernel_policy() { return g_kernel_policy.load(std::memory_order_relaxed); }
-void note_linear_kernel(const char* name) { t_last_linear_kernel = name; }
+void note_linear_kernel(const char* name, int tile_rows) {
+  t_last_linear_kernel = name;
+  t_last_linear_tile_rows = tile_rows;
+}
 
 const DeviceInfo* current_device(char* message, size_t capacity) {
   int device = 0;
@@ -189,6 +193,7 @@ extern "C" int32_t nml_nvfp4_sm100_set_kernel_policy(int32_t policy) {
 }
 
 extern "C" const char* nml_nvfp4_sm100_last_linear_kernel(void) { return t_last_linear_kernel; }
+extern "C" int32_t nml_nvfp4_sm100_last_linear_tile_rows(void) { return t_last_linear_tile_rows; }
 
 extern "C" int32_t nml_nvfp4_sm100_plan_capacity(int64_t assignments, int64_t experts,
                                                  int64_t* blocks, int64_t* positions) {

@@ -171,6 +171,6 @@ int32_t launch_experts_umma(const ExpertArgs& args, const DeviceInfo& device, ch
                             size_t capacity);
 
 int get_kernel_policy();
-void note_linear_kernel(const char* name);
+void note_linear_kernel(const char* name, int tile_rows);
 
 }  // namespace nml_sm100

@@ -17,11 +17,16 @@ namespace {
 
 using namespace umma;
 
-template <int BM, int KS, int RAW, int WB, int DG, int MI, int PA, bool WT, int AFMT, typename T,
-          int MODE, bool XTMA>
+constexpr int32_t kDoesNotFit = -1000;  // internal: the variant's shared memory exceeds the SM's
+
+template <int BM, int KS, int PS, int XS, int WB, int DG, int MI, int PA, bool WT, int AFMT,
+          typename T, int MODE, bool XTMA>
 int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* message,
                       size_t capacity) {
-  using L = Layout<BM, KS, RAW, WB, true, WT>;
+  using L = Layout<BM, KS, PS, XS, WB, true, WT>;
+  const int scale_buffer_bytes = WT ? ((args.inputs / 16 * kTileN + 127) / 128) * 128 : 0;
+  const int smem_bytes = L::kSmemBytes + 2 * scale_buffer_bytes;
+  if (smem_bytes > kSmemBudget) return kDoesNotFit;
   const int rows_per_expert = args.gate_up ? 2 * args.outputs : args.outputs;
   const int64_t weight_rows = static_cast<int64_t>(args.experts) * rows_per_expert;
   CUtensorMap tmap_payload, tmap_x;
@@ -64,13 +69,15 @@ int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* me
   p.experts = args.experts;
   p.top_k = args.experts_per_token;
   p.status = device.status_word;
+  p.scale_buffer_bytes = scale_buffer_bytes;
+  fill_decode_constants(&p.decode);
 #ifdef NML_SM100_PROFILE
   p.knockout = std::getenv("NML_SM100_KNOCKOUT") ? std::atoi(std::getenv("NML_SM100_KNOCKOUT")) : 0;
 #endif
 
-  auto kernel = gemm_kernel<BM, KS, RAW, WB, DG, MI, PA, WT, AFMT, T, MODE, XTMA>;
+  auto kernel = gemm_kernel<BM, KS, PS, XS, WB, DG, MI, PA, WT, AFMT, T, MODE, XTMA>;
   static bool configured[64] = {};
-  if (!reserve_smem(kernel, L::kSmemBytes, device.device, configured)) {
+  if (!reserve_smem(kernel, WT ? kSmemBudget : L::kSmemBytes, device.device, configured)) {
     return fail(NML_SM100_LAUNCH_FAILURE, "cannot reserve shared memory for the tcgen05 experts",
                 message, capacity);
   }
@@ -79,8 +86,8 @@ int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* me
   const int64_t max_units = slot_tiles * p.n_tiles;
   const unsigned grid =
       static_cast<unsigned>(max_units < device.sm_count ? max_units : device.sm_count);
-  kernel<<<grid, launch_threads<DG, MI, XTMA>(), L::kSmemBytes, args.stream>>>(tmap_payload,
-                                                                               tmap_x, p);
+  kernel<<<grid, launch_threads<DG, MI, XTMA>(), smem_bytes, args.stream>>>(tmap_payload, tmap_x,
+                                                                            p);
   return launch_result(message, capacity);
 }
 
@@ -91,41 +98,46 @@ int32_t launch_for_load(const ExpertArgs& args, const DeviceInfo& device, char* 
   const int64_t average = args.assignments <= args.experts
                               ? 1
                               : (args.assignments + args.experts - 1) / args.experts;
-  // Decoded weights in tensor memory: needs the unit's block scales (128 rows x K/16 bytes)
-  // to fit one buffer and every tile's scale range to form a legal bulk copy.
+  // Decoded weights in tensor memory: every tile's block scales (128 rows x K/16 bytes) must
+  // form a legal bulk copy and two such buffers must fit beside the rings.
   const int rows_per_expert = args.gate_up ? 2 * args.outputs : args.outputs;
-  const bool tmem_weights =
-      get_kernel_policy() != 3 && args.inputs / 16 * kTileN <= kScaleBufferBytes &&
-      rows_per_expert % 4 == 0 && reinterpret_cast<uintptr_t>(args.block_scales) % 16 == 0;
+  const bool tmem_weights = get_kernel_policy() != 3 && rows_per_expert % 4 == 0 &&
+                            reinterpret_cast<uintptr_t>(args.block_scales) % 16 == 0;
   if (tmem_weights && average <= 160) {
+    int32_t rc;
     if (average <= 16) {
-      return launch_config<16, 4, 6, 8, 2, 2, 8, true, AFMT, T, MODE, XTMA>(args, device, message,
+      rc = launch_config<16, 4, 6, 4, 8, 2, 2, 8, true, AFMT, T, MODE, XTMA>(args, device, message,
                                                                             capacity);
-    }
-    if (average <= 32) {
-      return launch_config<32, 4, 5, 8, 2, 1, 4, true, AFMT, T, MODE, XTMA>(args, device, message,
+    } else if (average <= 32) {
+      rc = launch_config<32, 4, 5, 4, 8, 2, 1, 4, true, AFMT, T, MODE, XTMA>(args, device, message,
                                                                             capacity);
-    }
-    if (average <= 64) {
-      return launch_config<64, 4, 3, 8, 2, 1, 2, true, AFMT, T, MODE, XTMA>(args, device, message,
+    } else if (average <= 64) {
+      rc = launch_config<64, 4, 3, 3, 8, 2, 1, 2, true, AFMT, T, MODE, XTMA>(args, device, message,
                                                                             capacity);
+    } else {
+      rc = launch_config<128, 1, 8, 8, 8, 2, 1, 1, true, AFMT, T, MODE, XTMA>(args, device,
+                                                                             message, capacity);
     }
-    return launch_config<128, 1, 8, 8, 2, 1, 1, true, AFMT, T, MODE, XTMA>(args, device, message,
-                                                                           capacity);
+    if (rc != kDoesNotFit) return rc;
   }
   if (average <= 16) {
-    return launch_config<16, 4, 5, 4, 2, 2, 8, false, AFMT, T, MODE, XTMA>(args, device, message, capacity);
+    return launch_config<16, 4, 5, 4, 4, 2, 2, 8, false, AFMT, T, MODE, XTMA>(args, device, message,
+                                                                             capacity);
   }
   if (average <= 32) {
-    return launch_config<32, 4, 4, 4, 2, 2, 8, false, AFMT, T, MODE, XTMA>(args, device, message, capacity);
+    return launch_config<32, 4, 4, 3, 4, 2, 2, 8, false, AFMT, T, MODE, XTMA>(args, device, message,
+                                                                             capacity);
   }
   if (average <= 64) {
-    return launch_config<64, 4, 3, 4, 2, 1, 4, false, AFMT, T, MODE, XTMA>(args, device, message, capacity);
+    return launch_config<64, 4, 3, 3, 4, 2, 1, 4, false, AFMT, T, MODE, XTMA>(args, device, message,
+                                                                             capacity);
   }
   if (average <= 160) {
-    return launch_config<128, 1, 5, 5, 2, 1, 1, false, AFMT, T, MODE, XTMA>(args, device, message, capacity);
+    return launch_config<128, 1, 6, 5, 5, 2, 1, 1, false, AFMT, T, MODE, XTMA>(args, device,
+                                                                              message, capacity);
   }
-  return launch_config<256, 1, 4, 4, 2, 1, 1, false, AFMT, T, MODE, XTMA>(args, device, message, capacity);
+  return launch_config<256, 1, 4, 4, 4, 2, 1, 1, false, AFMT, T, MODE, XTMA>(args, device, message,
+                                                                            capacity);
 }
 
 template <int MODE>

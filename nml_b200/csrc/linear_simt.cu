@@ -94,7 +94,7 @@ int32_t launch_linear_simt(const LinearArgs& args, const DeviceInfo&, char* mess
         args.global_scale, static_cast<const __nv_bfloat16*>(args.bias),
         static_cast<__nv_bfloat16*>(args.output), args.rows, args.outputs, args.inputs);
   }
-  note_linear_kernel("simt");
+  note_linear_kernel("simt", 0);
   return launch_result(message, capacity);
 }
 

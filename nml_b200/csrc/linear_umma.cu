@@ -14,10 +14,17 @@ namespace {
 
 using namespace umma;
 
-template <int BM, int KS, int RAW, int WB, int DG, int MI, int PA, bool WT, int AFMT, typename T>
+
+constexpr int32_t kDoesNotFit = -1000;  // internal: the variant's shared memory exceeds the SM's
+
+template <int BM, int KS, int PS, int XS, int WB, int DG, int MI, int PA, bool WT, int AFMT,
+          typename T>
 int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* message,
                       size_t capacity) {
-  using L = Layout<BM, KS, RAW, WB, false, WT>;
+  using L = Layout<BM, KS, PS, XS, WB, false, WT>;
+  const int scale_buffer_bytes = WT ? ((args.inputs / 16 * kTileN + 127) / 128) * 128 : 0;
+  const int smem_bytes = L::kSmemBytes + 2 * scale_buffer_bytes;
+  if (smem_bytes > kSmemBudget) return kDoesNotFit;
   CUtensorMap tmap_payload, tmap_x;
   if (!encode_payload_map<KS>(&tmap_payload, args.payload, args.outputs, args.inputs) ||
       !encode_activation_map<T>(&tmap_x, args.activation, args.rows, args.inputs, BM, KS)) {
@@ -42,36 +49,43 @@ int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* me
   p.n_fastest = weight_bytes <= (32ll << 20) ? 1 : 0;
   p.output = args.output;
   p.status = device.status_word;
+  p.scale_buffer_bytes = scale_buffer_bytes;
+  fill_decode_constants(&p.decode);
 #ifdef NML_SM100_PROFILE
   p.knockout = std::getenv("NML_SM100_KNOCKOUT") ? std::atoi(std::getenv("NML_SM100_KNOCKOUT")) : 0;
 #endif
 
-  auto kernel = gemm_kernel<BM, KS, RAW, WB, DG, MI, PA, WT, AFMT, T, kDense, true>;
+  auto kernel = gemm_kernel<BM, KS, PS, XS, WB, DG, MI, PA, WT, AFMT, T, kDense, true>;
   static bool configured[64] = {};
-  if (!reserve_smem(kernel, L::kSmemBytes, device.device, configured)) {
+  if (!reserve_smem(kernel, WT ? kSmemBudget : L::kSmemBytes, device.device, configured)) {
     return fail(NML_SM100_LAUNCH_FAILURE, "cannot reserve shared memory for the tcgen05 linear",
                 message, capacity);
   }
   const int64_t tiles = static_cast<int64_t>(p.n_tiles) * p.m_tiles;
   const unsigned grid = static_cast<unsigned>(tiles < device.sm_count ? tiles : device.sm_count);
-  kernel<<<grid, launch_threads<DG, MI, true>(), L::kSmemBytes, args.stream>>>(tmap_payload, tmap_x, p);
+  kernel<<<grid, launch_threads<DG, MI, true>(), smem_bytes, args.stream>>>(tmap_payload, tmap_x,
+                                                                            p);
   note_linear_kernel(WT ? (AFMT == kAf16 ? "umma_tmem_weights_af16" : "umma_tmem_weights_abf16")
-                        : (AFMT == kAf16 ? "umma_swapab_af16" : "umma_swapab_abf16"));
+                        : (AFMT == kAf16 ? "umma_swapab_af16" : "umma_swapab_abf16"), BM);
   return launch_result(message, capacity);
 }
 
-int choose_tile_rows(int rows, int outputs, int sm_count) {
+// `wide` allows the 192-row tile (decoded weights in tensor memory leave room for two
+// 192-column accumulators, not for two of 256).
+int choose_tile_rows(int rows, int outputs, int sm_count, bool wide) {
   if (rows <= 16) return 16;
   if (rows <= 32) return 32;
   if (rows <= 64) return 64;
   const int n_tiles = (outputs + kTileN - 1) / kTileN;
-  // relative time of one K step of a tile: decode-bound below 256 rows, MMA-bound at 256
-  const int candidates[3] = {64, 128, 256};
-  const int step_cost[3] = {300, 350, 512};
+  // relative time of one K step of a tile: decode-bound for few rows, MMA-bound beyond
+  // measured time of one K step of a tile (2880 -> 5760 at M = 16384, relative units)
+  const int candidates[4] = {64, 128, 192, 256};
+  const int step_cost[4] = {137, wide ? 156 : 190, 180, 228};
   int best = 256;
   int64_t best_cost = -1;
-  for (int i = 0; i < 3; ++i) {
+  for (int i = 0; i < 4; ++i) {
     const int bm = candidates[i];
+    if (bm == 192 && !wide) continue;
     if (bm > 64 && rows <= bm / 2) continue;
     const int64_t tiles = static_cast<int64_t>(n_tiles) * ((rows + bm - 1) / bm);
     const int64_t waves = (tiles + sm_count - 1) / sm_count;
@@ -87,38 +101,58 @@ int choose_tile_rows(int rows, int outputs, int sm_count) {
 template <int AFMT, typename T>
 int32_t launch_for_rows(const LinearArgs& args, const DeviceInfo& device, char* message,
                         size_t capacity) {
-  const int tile_rows = choose_tile_rows(args.rows, args.outputs, device.sm_count);
-  // Decoded weights in tensor memory: needs the unit's block scales (128 rows x K/16 bytes)
-  // to fit one buffer and to form a legal bulk copy.
-  const bool tmem_weights =
-      get_kernel_policy() != 3 && args.inputs / 16 * kTileN <= kScaleBufferBytes &&
-      args.outputs % 4 == 0 && reinterpret_cast<uintptr_t>(args.block_scales) % 16 == 0;
+  // Decoded weights in tensor memory: the unit's block scales (128 rows x K/16 bytes) must
+  // form a legal bulk copy and two such buffers must fit beside the rings.
+  // Experiment hook: policy 100 + BM forces the tile height (tensor-memory variant), policy
+  // 1000 + BM forces it for the shared-memory ring.
+  const int policy = get_kernel_policy();
+  const int forced_rows = policy >= 1000 ? policy - 1000 : policy >= 100 ? policy - 100 : 0;
+  const bool tmem_weights = policy != 3 && policy < 1000 && args.outputs % 4 == 0 &&
+                            reinterpret_cast<uintptr_t>(args.block_scales) % 16 == 0;
   if (tmem_weights) {
-    switch (tile_rows) {
+    int32_t rc = kDoesNotFit;
+    switch (forced_rows ? forced_rows
+                        : choose_tile_rows(args.rows, args.outputs, device.sm_count, true)) {
       case 16:
-        return launch_config<16, 4, 6, 8, 3, 2, 8, true, AFMT, T>(args, device, message, capacity);
+        rc = launch_config<16, 4, 6, 4, 8, 3, 2, 8, true, AFMT, T>(args, device, message, capacity);
+        break;
       case 32:
-        return launch_config<32, 4, 5, 8, 3, 1, 4, true, AFMT, T>(args, device, message, capacity);
+        rc = launch_config<32, 4, 5, 4, 8, 3, 1, 4, true, AFMT, T>(args, device, message, capacity);
+        break;
       case 64:
-        return launch_config<64, 4, 3, 8, 3, 1, 2, true, AFMT, T>(args, device, message, capacity);
+        rc = launch_config<64, 4, 3, 3, 8, 3, 1, 2, true, AFMT, T>(args, device, message, capacity);
+        break;
       case 128:
-        return launch_config<128, 1, 8, 8, 3, 1, 1, true, AFMT, T>(args, device, message,
-                                                                   capacity);
+        rc = launch_config<128, 1, 8, 8, 8, 4, 1, 1, true, AFMT, T>(args, device, message,
+                                                                    capacity);
+        break;
+      case 192:
+        rc = launch_config<192, 1, 6, 6, 4, 3, 1, 1, true, AFMT, T>(args, device, message,
+                                                                    capacity);
+        break;
       default:
         break;
     }
+    if (rc != kDoesNotFit) return rc;
   }
-  switch (tile_rows) {
+  switch (forced_rows && forced_rows != 192
+              ? forced_rows
+              : choose_tile_rows(args.rows, args.outputs, device.sm_count, false)) {
     case 16:
-      return launch_config<16, 4, 5, 4, 3, 1, 8, false, AFMT, T>(args, device, message, capacity);
+      return launch_config<16, 4, 5, 4, 4, 3, 1, 8, false, AFMT, T>(args, device, message,
+                                                                    capacity);
     case 32:
-      return launch_config<32, 4, 4, 4, 3, 1, 8, false, AFMT, T>(args, device, message, capacity);
+      return launch_config<32, 4, 4, 3, 4, 3, 1, 8, false, AFMT, T>(args, device, message,
+                                                                    capacity);
     case 64:
-      return launch_config<64, 4, 3, 4, 3, 1, 4, false, AFMT, T>(args, device, message, capacity);
+      return launch_config<64, 4, 3, 3, 4, 3, 1, 4, false, AFMT, T>(args, device, message,
+                                                                    capacity);
     case 128:
-      return launch_config<128, 1, 6, 6, 3, 1, 1, false, AFMT, T>(args, device, message, capacity);
+      return launch_config<128, 1, 8, 5, 5, 3, 1, 1, false, AFMT, T>(args, device, message,
+                                                                     capacity);
     default:
-      return launch_config<256, 1, 4, 4, 3, 1, 1, false, AFMT, T>(args, device, message, capacity);
+      return launch_config<256, 1, 6, 4, 4, 3, 1, 1, false, AFMT, T>(args, device, message,
+                                                                     capacity);
   }
 }
 

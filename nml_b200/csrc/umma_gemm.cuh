@@ -7,16 +7,30 @@
 // or schedule slots (grouped) are the UMMA N dimension, so packed weights are decoded once
 // per K step whatever the number of rows.
 //
-// Two rings decouple bytes in flight from the 16 KB decoded-operand buffers:
-//   raw ring  (RAW stages, each KS K-steps of 64): payload tile [128 x 32*KS B] by TMA,
-//             block-scale bytes by 4-byte cp.async, X tiles [BM x 64] by TMA (dense) or by
-//             16-byte cp.async gathers of scheduled rows (grouped), 128B-swizzled
-//   W' ring   (WB buffers): decoded operand tile [128 x 64], UMMA K-major 128B swizzle
-// Warp roles: 0 producer, 1 MMA issuer + TMEM owner, 2-5 epilogue, then DG decode groups of
-// four warps, then four row-gather warps (grouped only).  Accumulators are double-buffered in TMEM; the kernel is persistent.
+// Three rings, each with its own producer and consumer, so that no stage waits for a
+// consumer it does not need:
+//   P ring   (PS stages of KS K-steps of 64): packed payload tile [128 x 32*KS B] by TMA, and,
+//            when the decoded tiles live in shared memory, the stage's block-scale bytes by
+//            4-byte cp.async.  Producer warp -> decode warps, which free a stage themselves.
+//   X ring   (XS stages of KS K-steps): activation tiles [BM x 64], 128B-swizzled, by TMA
+//            (dense, slot-ordered grouped) or by 16-byte cp.async gathers of scheduled rows.
+//            X warp(s) -> MMA, freed by tcgen05.commit.
+//   W' ring  (WB decoded operand tiles [128 x 64]): decode warps -> MMA, freed by commit.
+//            Either in tensor memory (the MMA reads its A operand there; block scales of a
+//            whole unit then arrive with one bulk copy into one of two buffers) or in shared
+//            memory as UMMA K-major 128B-swizzled tiles.
+// The packed weights are the only HBM stream; decoupling lets decode run WB tiles ahead of
+// the MMA while the X ring alone sets how far the MMA's operands are prefetched.
+// Warp roles: 0 payload producer, 1 MMA issuer + TMEM owner, 2-5 epilogue, then DG decode
+// groups of four warps, then the X side (one TMA warp, or four row-gather warps), then the
+// second MMA issuer if any.  Accumulators are double-buffered in TMEM; the kernel is persistent.
 //
 // Every mbarrier wait is bounded; a wait that runs out sets the barrier-timeout bit of the
 // device status word and all roles leave through the common teardown.
+//
+// Parity waits cannot tell "phase k done" from "phase k - 1 not yet done": every waiter below
+// either gates the reuse of what it waits on (its own arrival is needed before the barrier
+// can advance again) or has itself consumed the previous phase.
 #pragma once
 
 #include <type_traits>
@@ -45,8 +59,8 @@ constexpr int kGatherThreads = kGatherWarps * 32;
 // sequence number is congruent to g modulo DG, so DG K steps are in decode at once: the
 // decode of one K step is a long dependent instruction chain, and it is the number of
 // chains in flight, not the instruction count, that keeps the tensor pipe fed.
-// Threads of a launch: the roles above, the gather warps unless activations come by TMA, and
-// one more warp when a second MMA issuer is used.
+// Threads of a launch: the roles above, the X side (one warp issuing TMA loads, or the four
+// gather warps), and one more warp when a second MMA issuer is used.
 template <int DG, int MI, bool XTMA>
 constexpr int launch_threads();
 
@@ -54,7 +68,7 @@ template <int DG>
 struct Roles {
   static constexpr int kDecodeWarps = 4 * DG;
   static constexpr int kGatherWarp0 = kDecodeWarp0 + kDecodeWarps;
-  static constexpr int kThreadsDense = kGatherWarp0 * 32;
+  static constexpr int kThreadsDense = (kGatherWarp0 + 1) * 32;
   static constexpr int kThreadsGrouped = (kGatherWarp0 + kGatherWarps) * 32;
 };
 template <int DG, int MI, bool XTMA>
@@ -67,29 +81,38 @@ constexpr int kMaxGroups = 256;
 
 // WT: the decoded weight tiles live in tensor memory (the MMA reads its A operand there) and
 // the block scales of a whole unit arrive with one bulk copy into one of two buffers;
-// otherwise the decoded tiles form a shared-memory ring and every raw stage carries its own
+// otherwise the decoded tiles form a shared-memory ring and every P stage carries its own
 // scale bytes.
-constexpr int kScaleBufferBytes = 24 * 1024;  // 128 rows x K/16 bytes, so K <= 3072 with WT
-
-template <int BM, int KS, int RAW, int WB, bool GROUPED, bool WT = false>
+template <int BM, int KS, int PS, int XS, int WB, bool GROUPED, bool WT>
 struct Layout {
   static constexpr int kPayloadBytes = kTileN * 32 * KS;
   static constexpr int kScaleBytes = WT ? 0 : (kTileN * 4 * KS < 1024 ? 1024 : kTileN * 4 * KS);
-  static constexpr int kXBytes = BM * 128;                 // one K step
-  static constexpr int kRawBytes = kPayloadBytes + kScaleBytes + kXBytes * KS;
-  static constexpr int kRawOffset = WT ? 0 : WB * kWBytes;
-  static constexpr int kScaleBufferOffset = kRawOffset + RAW * kRawBytes;
-  static constexpr int kBarrierOffset = kScaleBufferOffset + (WT ? 2 * kScaleBufferBytes : 0);
+  static constexpr int kPBytes = kPayloadBytes + kScaleBytes;  // one P stage
+  static constexpr int kXBytes = BM * 128;                     // one K step of X
+  static constexpr int kXStageBytes = KS * kXBytes;
+  static constexpr int kXOffset = WT ? 0 : WB * kWBytes;       // the W' ring comes first
+  static constexpr int kPOffset = kXOffset + XS * kXStageBytes;
+  static constexpr int kBarrierOffset = kPOffset + PS * kPBytes;
   static constexpr int kBarrierBytes = 2048;
   // grouped: group table + one slot table (assignment id, routing weight) per epilogue warp
   static constexpr int kSlotTableBytes = GROUPED ? kEpilogueWarps * BM * 6 : 0;
-  static constexpr int kGroupBytes = GROUPED ? (kMaxGroups * 16 + 64) + kSlotTableBytes : 0;
-  static constexpr int kSmemBytes = kBarrierOffset + kBarrierBytes + kGroupBytes + 1024;
+  static constexpr int kGroupBytes =
+      GROUPED ? ((kMaxGroups * 16 + 64 + kSlotTableBytes + 127) / 128) * 128 : 0;
+  // WT: two scale buffers of Params::scale_buffer_bytes each follow (sized at launch)
+  static constexpr int kScaleBufferOffset = kBarrierOffset + kBarrierBytes + kGroupBytes;
+  static constexpr int kSmemBytes = kScaleBufferOffset + 1024;  // + alignment slack
   static constexpr int kTmemColumns = 2 * BM < 32 ? 32 : 2 * BM;
   static_assert(kSmemBytes <= kSmemBudget, "shared memory budget exceeded");
-  static_assert(kRawBytes % 1024 == 0, "raw stage must keep 1024-byte alignment");
-  static_assert((kTmemColumns & (kTmemColumns - 1)) == 0 && kTmemColumns <= 512, "TMEM");
-  static_assert(KS == 1 || KS == 2 || KS == 4, "K steps per raw stage");
+  static_assert(kPBytes % 1024 == 0 && kXBytes % 1024 == 0, "stages keep 1024-byte alignment");
+  static_assert(KS == 1 || KS == 2 || KS == 4, "K steps per stage");
+};
+
+// Shift amounts as multipliers that the compiler cannot see through.  The decode is bound by
+// the half-rate integer pipe (logic, shift, byte-permute); a multiply by a power of two held
+// in a register issues on the FMA pipe instead, which the decode otherwise barely uses.
+struct DecodeConstants {
+  uint32_t mul4, mul16, mul64, mul256, mul4096;  // left shifts by 2, 4, 6, 8, 12
+  uint32_t hi26, hi30;                           // mul.hi by 2^26, 2^30: right shifts by 6, 2
 };
 
 struct Params {
@@ -113,6 +136,8 @@ struct Params {
   const void* routing_weights;
   int assignments, schedule_blocks, experts, top_k;
   int* status;
+  int scale_buffer_bytes;  // WT: bytes of one scale buffer (128 rows x K / 16, 128-aligned)
+  DecodeConstants decode;  // see DecodeConstants; filled by fill_decode_constants()
   int knockout;  // tuning builds only: bit 0 skips the decode arithmetic, bit 1 the MMA issue
 };
 
@@ -177,15 +202,39 @@ __device__ __forceinline__ void scales2_f16(uint32_t two_bytes, uint32_t& first,
 
 // 8 codes -> 8 exact bf16 values code * scale * 2^-7, K order.  scale2 holds
 // bf16(scale * 2^119) in both halves.  The code's magnitude bits placed at bf16 bits 8:6
-// read as value * 2^-126 (0.5 is the bf16 subnormal); the sign stays at bit 15.
-__device__ __forceinline__ void decode8_bf16(uint32_t word, uint32_t scale2, uint32_t (&out)[4]) {
+// read as value * 2^-126 (0.5 is the bf16 subnormal); the sign goes to bit 15.  Nibble i of
+// each 16-bit half (codes i and i + 4) needs its own pair of shifts; all come from the one
+// payload word, so there is no dependent shift chain.
+__device__ __forceinline__ void decode8_bf16(uint32_t q, uint32_t scale2, uint32_t (&out)[4],
+                                             const DecodeConstants& c) {
+  constexpr uint32_t kSign = 0x80008000u, kMagnitude = 0x01c001c0u;
   uint32_t t[4];
-  uint32_t q = word;
+#ifndef NML_DECODE_VARIANT
+#define NML_DECODE_VARIANT 3
+#endif
+#if NML_DECODE_VARIANT == 0
+  uint32_t w = q;
 #pragma unroll
   for (int i = 3; i >= 0; --i) {
-    t[i] = (q & 0x80008000u) | ((q & 0x70007000u) >> 6);  // codes i and i + 4
-    q <<= 4;
+    t[i] = (w & kSign) | ((w & 0x70007000u) >> 6);
+    w <<= 4;
   }
+#elif NML_DECODE_VARIANT == 1
+  t[3] = (q & kSign) | (__umulhi(q, c.hi26) & kMagnitude);
+  t[2] = ((q * c.mul16) & kSign) | (__umulhi(q, c.hi30) & kMagnitude);
+  t[1] = ((q * c.mul256) & kSign) | ((q * c.mul4) & kMagnitude);
+  t[0] = ((q * c.mul4096) & kSign) | ((q * c.mul64) & kMagnitude);
+#elif NML_DECODE_VARIANT == 2
+  t[3] = (q & kSign) | ((q >> 6) & kMagnitude);
+  t[2] = ((q * c.mul16) & kSign) | ((q >> 2) & kMagnitude);
+  t[1] = ((q * c.mul256) & kSign) | ((q * c.mul4) & kMagnitude);
+  t[0] = ((q * c.mul4096) & kSign) | ((q * c.mul64) & kMagnitude);
+#else
+  t[3] = (q & kSign) | ((q >> 6) & kMagnitude);
+  t[2] = ((q << 4) & kSign) | ((q >> 2) & kMagnitude);
+  t[1] = ((q << 8) & kSign) | ((q << 2) & kMagnitude);
+  t[0] = ((q << 12) & kSign) | ((q << 6) & kMagnitude);
+#endif
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(t[i]) : "r"(scale2));
@@ -196,16 +245,23 @@ __device__ __forceinline__ void decode8_bf16(uint32_t word, uint32_t scale2, uin
   out[3] = __byte_perm(t[2], t[3], 0x7632);
 }
 
-// One E4M3 scale byte -> bf16(scale * 2^119) in both halves: the byte's value bits at bf16
-// bits 10:4 read as scale * 2^-120; two exact bf16 multiplies rescale.
-__device__ __forceinline__ uint32_t scale_bf16_dup(uint32_t byte) {
-  uint32_t s = (byte & 0x7fu) << 4;
-  s |= s << 16;
+// Four E4M3 scale bytes -> four words holding bf16(scale * 2^119) in both halves: a byte's
+// value bits at bf16 bits 10:4 read as scale * 2^-120; two exact bf16 multiplies rescale.
+__device__ __forceinline__ void scales4_bf16(uint32_t four_bytes, uint32_t (&scale)[4],
+                                             const DecodeConstants& c) {
   const uint32_t two_p120 = 0x7b807b80u;
   const uint32_t two_p119 = 0x7b007b00u;
-  asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(s) : "r"(two_p120));
-  asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(s) : "r"(two_p119));
-  return s;
+  uint32_t pair[2];
+  pair[0] = __byte_perm(four_bytes, 0u, 0x4140);  // byte 0 -> low half, byte 1 -> high half
+  pair[1] = __byte_perm(four_bytes, 0u, 0x4342);
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    pair[i] = (pair[i] & 0x007f007fu) * c.mul16;
+    asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(pair[i]) : "r"(two_p120));
+    asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(pair[i]) : "r"(two_p119));
+    scale[2 * i] = __byte_perm(pair[i], pair[i], 0x1010);
+    scale[2 * i + 1] = __byte_perm(pair[i], pair[i], 0x3232);
+  }
 }
 
 // ---- unit enumeration -------------------------------------------------------------------
@@ -367,19 +423,19 @@ struct RingState {
 // dependent chain whose per-instruction latency (not its throughput) bounds tiles with few
 // activation rows, so the K=16 slices rotate over PA accumulators (instruction i of a unit
 // goes to accumulator i % PA) and the epilogue adds them in index order.
-template <int BM, int KS, int RAW, int WB, int DG, int MI, int PA, bool WT, int AFMT,
+template <int BM, int KS, int PS, int XS, int WB, int DG, int MI, int PA, bool WT, int AFMT,
           typename T, int MODE, bool XTMA>
 __global__ void __launch_bounds__(launch_threads<DG, MI, XTMA>(), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
             const __grid_constant__ CUtensorMap tmap_x, const Params p) {
   constexpr bool GROUPED = MODE != kDense;
-  constexpr int kGatherWarp0 = Roles<DG>::kGatherWarp0;
-  constexpr int kMmaWarpB = XTMA ? kGatherWarp0 : kGatherWarp0 + kGatherWarps;
+  constexpr int kGatherWarp0 = Roles<DG>::kGatherWarp0;  // first warp of the X side
+  constexpr int kMmaWarpB = XTMA ? kGatherWarp0 + 1 : kGatherWarp0 + kGatherWarps;
   static_assert(2 * PA * BM <= 512, "partial accumulators exceed tensor memory");
   static_assert(MI == 1 || PA == 8, "two issuers need disjoint partial accumulators");
   static_assert(WB > DG, "the W' ring must hold one tile per decode group plus one");
   static_assert(GROUPED || XTMA, "the dense mode always loads activations by TMA");
-  using L = Layout<BM, KS, RAW, WB, GROUPED, WT>;
+  using L = Layout<BM, KS, PS, XS, WB, GROUPED, WT>;
   constexpr int kAccColumns = PA * L::kTmemColumns;   // two accumulator sets of PA partials
   constexpr int kWColumns = kTileK / 2;                // one decoded K step: 64 x 16 bit per row
   constexpr int kTmemNeeded = kAccColumns + (WT ? WB * kWColumns : 0);
@@ -389,19 +445,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
                                : kTmemNeeded <= 256 ? 256
                                                     : 512;
   static_assert(kTmemNeeded <= 512, "tensor memory budget exceeded");
+  // With one K step per stage and equally deep X and W' rings the two advance in lockstep, so
+  // the commit that frees a W' tile also frees the X stage of the same index.
+  constexpr bool kSharedEmpty = KS == 1 && XS == WB && MI == 1;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
 
   auto w_tile = [&](int w) { return smem + w * kWBytes; };
-  auto raw_base = [&](int r) { return smem + L::kRawOffset + r * L::kRawBytes; };
-  auto x_tile = [&](int r, int j) { return raw_base(r) + j * L::kXBytes; };
-  auto payload_tile = [&](int r) { return raw_base(r) + KS * L::kXBytes; };
-  auto scale_tile = [&](int r) { return raw_base(r) + KS * L::kXBytes + L::kPayloadBytes; };
-  auto scale_buffer = [&](int b) { return smem + L::kScaleBufferOffset + b * kScaleBufferBytes; };
+  auto x_tile = [&](int r, int j) { return smem + L::kXOffset + r * L::kXStageBytes + j * L::kXBytes; };
+  auto payload_tile = [&](int r) { return smem + L::kPOffset + r * L::kPBytes; };
+  auto scale_tile = [&](int r) { return payload_tile(r) + L::kPayloadBytes; };
+  auto scale_buffer = [&](int b) { return smem + L::kScaleBufferOffset + b * p.scale_buffer_bytes; };
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarrierOffset);
-  uint64_t* full_raw = bars;               // [RAW]
-  uint64_t* empty_raw = bars + RAW;        // [RAW]
-  uint64_t* full_w = bars + 2 * RAW;       // [WB]
+  uint64_t* full_p = bars;                 // [PS]
+  uint64_t* empty_p = full_p + PS;         // [PS]
+  uint64_t* full_x = empty_p + PS;         // [XS]
+  uint64_t* empty_x = full_x + XS;         // [XS]
+  uint64_t* full_w = empty_x + XS;         // [WB]
   uint64_t* empty_w = full_w + WB;         // [WB]
   uint64_t* tmem_full = empty_w + WB;      // [2]
   uint64_t* tmem_empty = tmem_full + 2;    // [2]
@@ -409,16 +469,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
   uint64_t* empty_scale = full_scale + 2;  // [2] (WT)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(empty_scale + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  static_assert((2 * RAW + 2 * WB + 8) * 8 + 8 <= L::kBarrierBytes, "barrier area");
+  static_assert((2 * PS + 2 * XS + 2 * WB + 8) * 8 + 8 <= L::kBarrierBytes, "barrier area");
   Groups* groups = reinterpret_cast<Groups*>(smem + L::kBarrierOffset + L::kBarrierBytes);
+  uint64_t* x_free = kSharedEmpty ? empty_w : empty_x;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int r = 0; r < RAW; ++r) {
-      mbar_init(&full_raw[r], 1 + (WT ? 0 : 32) + (XTMA ? 0 : kGatherWarps));
-      mbar_init(&empty_raw[r], MI);
+    for (int r = 0; r < PS; ++r) {
+      mbar_init(&full_p[r], 1 + (WT ? 0 : 32));  // expect_tx arrival (+ the lanes' scale copies)
+      mbar_init(&empty_p[r], 4 * DG);            // every decode warp
+    }
+    for (int r = 0; r < XS; ++r) {
+      mbar_init(&full_x[r], XTMA ? 1 : kGatherWarps);
+      mbar_init(&empty_x[r], MI);
     }
     for (int w = 0; w < WB; ++w) {
       mbar_init(&full_w[w], kGroupThreads / 32);
@@ -434,10 +499,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     mbar_fence_init();
   }
   if (warp == kProducerWarp) {
-    if (lane == 0) {
-      tma_prefetch_descriptor(&tmap_payload);
-      if constexpr (XTMA) tma_prefetch_descriptor(&tmap_x);
-    }
+    if (lane == 0) tma_prefetch_descriptor(&tmap_payload);
     if constexpr (GROUPED) build_groups(groups, p, BM, lane);
   }
   if (warp == kMmaWarp) {
@@ -449,7 +511,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const int units = total_units<BM, GROUPED>(p, groups);
-  const int raw_stages = (p.k_steps + KS - 1) / KS;
+  const int stages = (p.k_steps + KS - 1) / KS;  // per unit, of the P ring and of the X ring
 
   // `site` says which wait ran out (diagnostic bits 8.. of the status word).
   auto give_up = [&](int site) {
@@ -490,15 +552,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     give_up(site);
     return false;
   };
-  // With one K step per raw stage the two rings advance in lockstep, so the commit that
-  // frees a W' buffer also frees the raw stage of the same index: one commit per K step.
-  constexpr bool kSharedEmpty = KS == 1;
-  static_assert(!kSharedEmpty || WB == RAW, "lockstep rings need equal depth");
-  uint64_t* raw_free = kSharedEmpty ? empty_w : empty_raw;
-
   if (warp == kProducerWarp) {
-    // ------------------------------------------------------------------ producer
-    RingState raw;
+    // ---------------------------------------------------------- payload producer
+    RingState ps;
     int issued = 0;
     int local = 0;
     bool ok = true;
@@ -521,31 +577,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
                     &full_scale[b]);
         }
       }
-      for (int rs = 0; rs < raw_stages; ++rs) {
+      for (int rs = 0; rs < stages; ++rs) {
         NML_PROF_BEGIN();
 #ifdef NML_SM100_DEBUG_WAITS
         wait_position.stage = rs;
 #endif
-        if (!wait(&raw_free[raw.index], raw.phase ^ 1u, kSiteProducerRaw)) {
+        if (!wait(&empty_p[ps.index], ps.phase ^ 1u, kSiteProducerRaw)) {
           ok = false;
           break;
         }
         NML_PROF_END(0);
         if (lane == 0) {
-          mbar_arrive_expect_tx(&full_raw[raw.index],
-                                L::kPayloadBytes + (XTMA ? KS * L::kXBytes : 0));
-          tma_load_2d(payload_tile(raw.index), &tmap_payload, &full_raw[raw.index],
-                      rs * KS * 32, u.weight_row0);
-          if constexpr (XTMA) {
-            if constexpr (KS == 1) {
-              tma_load_2d(x_tile(raw.index, 0), &tmap_x, &full_raw[raw.index], rs * kTileK,
-                          u.m0);
-            } else {
-              // the activation map is a 3-D view [K/64][rows][64]: one box carries KS K steps
-              tma_load_3d(x_tile(raw.index, 0), &tmap_x, &full_raw[raw.index], 0, u.m0,
-                          rs * KS);
-            }
-          }
+          mbar_arrive_expect_tx(&full_p[ps.index], L::kPayloadBytes);
+          tma_load_2d(payload_tile(ps.index), &tmap_payload, &full_p[ps.index], rs * KS * 32,
+                      u.weight_row0);
         }
         if constexpr (!WT) {
           // block scales: 4 bytes per row and K step (scale rows are not TMA-legal)
@@ -557,25 +602,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
               for (int i = 0; i < kTileN / 32; ++i) {
                 const int row = lane + 32 * i;
                 const int n = min(u.weight_row0 + row, p.weight_rows_total - 1);
-                cp_async_4(scale_tile(raw.index) + row * (4 * KS) + j * 4,
+                cp_async_4(scale_tile(ps.index) + row * (4 * KS) + j * 4,
                            p.block_scales + static_cast<int64_t>(n) * p.scale_width + k_step * 4);
               }
             }
           }
-          cp_async_mbar_arrive_noinc(&full_raw[raw.index]);
+          cp_async_mbar_arrive_noinc(&full_p[ps.index]);
         } else {
           __syncwarp();
         }
         ++issued;
-        raw.advance<RAW>();
+        ps.advance<PS>();
       }
     }
     // Do not leave while copies this warp started may still be landing in shared memory.
-    const int pending = issued < RAW ? issued : RAW;
+    const int pending = issued < PS ? issued : PS;
     for (int i = 0; i < pending; ++i) {
-      raw.index = raw.index == 0 ? RAW - 1 : raw.index - 1;
-      if (raw.index == RAW - 1) raw.phase ^= 1u;
-      if (!mbar_wait(&full_raw[raw.index], raw.phase)) give_up(kSiteProducerDrain);
+      ps.index = ps.index == 0 ? PS - 1 : ps.index - 1;
+      if (ps.index == PS - 1) ps.phase ^= 1u;
+      if (!mbar_wait(&full_p[ps.index], ps.phase)) give_up(kSiteProducerDrain);
     }
     if constexpr (WT) {
       for (int back = 1; back <= 2 && back <= local; ++back) {
@@ -584,6 +629,42 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       }
     }
     NML_PROF_FLUSH(0, lane == 0)
+  } else if (XTMA && warp == kGatherWarp0) {
+    // ------------------------------------------------------- activation producer
+    if constexpr (XTMA) {
+      RingState xs;
+      int issued = 0;
+      bool ok = true;
+      if (lane == 0) tma_prefetch_descriptor(&tmap_x);
+      for (int index = blockIdx.x; index < units && ok; index += gridDim.x) {
+        const Unit u = get_unit<BM, GROUPED>(p, groups, index);
+        for (int rs = 0; rs < stages; ++rs) {
+          if (!wait(&x_free[xs.index], xs.phase ^ 1u, kSiteGather)) {
+            ok = false;
+            break;
+          }
+          if (lane == 0) {
+            // the box always covers KS K steps; columns past K read as zeros
+            mbar_arrive_expect_tx(&full_x[xs.index], L::kXStageBytes);
+            if constexpr (KS == 1) {
+              tma_load_2d(x_tile(xs.index, 0), &tmap_x, &full_x[xs.index], rs * kTileK, u.m0);
+            } else {
+              // the activation map is a 3-D view [K/64][rows][64]: one box carries KS K steps
+              tma_load_3d(x_tile(xs.index, 0), &tmap_x, &full_x[xs.index], 0, u.m0, rs * KS);
+            }
+          }
+          __syncwarp();
+          ++issued;
+          xs.advance<XS>();
+        }
+      }
+      const int pending = issued < XS ? issued : XS;
+      for (int i = 0; i < pending; ++i) {
+        xs.index = xs.index == 0 ? XS - 1 : xs.index - 1;
+        if (xs.index == XS - 1) xs.phase ^= 1u;
+        if (!mbar_wait(&full_x[xs.index], xs.phase)) give_up(kSiteProducerDrain);
+      }
+    }
   } else if (warp == kMmaWarp || (MI == 2 && warp == kMmaWarpB)) {
     // ----------------------------------------------------------------------- MMA
     // With MI == 2 two warps issue alternate K steps into disjoint partial accumulators that
@@ -610,7 +691,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       constexpr uint32_t b_format = std::is_same<T, __half>::value ? kUmmaF16 : kUmmaBF16;
       constexpr uint32_t idesc = umma_idesc_f16(a_format, b_format, kTileN, BM);
       constexpr uint64_t desc_hi = static_cast<uint64_t>(kUmmaDescHiSw128) << 32;
-      RingState raw, wb;
+      RingState xs, wb;
       int local = 0;
       int sequence = 0;  // K steps seen so far by this CTA, over all units
       const uint64_t w_desc = desc_hi | (WT ? 0u : umma_desc_lo(smem_u32(w_tile(0))));
@@ -636,16 +717,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         tcgen05_fence_after_sync();
         const uint32_t d_base = tmem_base + acc * PA * BM;
         int step = 0;  // K step inside the unit
-        for (int rs = 0; rs < raw_stages; ++rs) {
+        for (int rs = 0; rs < stages; ++rs) {
           NML_PROF_BEGIN();
 #ifdef NML_SM100_DEBUG_WAITS
           wait_position.stage = rs;
 #endif
-          mbar_wait_or_abort(&full_raw[raw.index], raw.phase, abort_flag, p.status,
+          mbar_wait_or_abort(&full_x[xs.index], xs.phase, abort_flag, p.status,
                              kSiteMmaRaw);
 #ifdef NML_SM100_DEBUG_WAITS
           if (*abort_flag && g_wait_debug[blockIdx.x & 127][kSiteMmaRaw + issuer * 0][0] == 0) {
-            record(&full_raw[raw.index], raw.phase, issuer == 0 ? kSiteMmaRaw : kSiteMmaAccumulator, 3);
+            record(&full_x[xs.index], xs.phase, issuer == 0 ? kSiteMmaRaw : kSiteMmaAccumulator, 3);
           }
 #endif
           NML_PROF_END(1);
@@ -673,7 +754,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
             const uint32_t a_tmem = tmem_base + kAccColumns + wb.index * kWColumns;
             const uint64_t a_desc = w_desc + wb.index * (kWBytes >> 4);
             const uint64_t b_desc =
-                x_desc + raw.index * (L::kRawBytes >> 4) + j * (L::kXBytes >> 4);
+                x_desc + xs.index * (L::kXStageBytes >> 4) + j * (L::kXBytes >> 4);
 #ifdef NML_SM100_PROFILE
             const long long issue_t0 = clock64();
             if (!(p.knockout & 2))
@@ -703,12 +784,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
 #ifdef NML_SM100_PROFILE
             const long long commit_t0 = clock64();
 #endif
-            umma_commit_elect(&empty_raw[raw.index]);
+            umma_commit_elect(&empty_x[xs.index]);
 #ifdef NML_SM100_PROFILE
             prof_fine[2] += static_cast<unsigned long long>(clock64() - commit_t0);
 #endif
           }
-          raw.advance<RAW>();
+          xs.advance<XS>();
         }
         umma_commit_elect(&tmem_full[acc]);
       }
@@ -876,10 +957,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     // Weight row of the tile this thread decodes.  A warp may only touch the tensor-memory
     // lanes 32 * (warp % 4) + lane, and with the weights in tensor memory row = lane.
     const int row = ((warp & 3) << 5) | lane;
-    RingState raw, wb;
+    RingState ps, wb;
     int sequence = 0;  // K steps seen so far by this CTA, over all units
     bool ok = true;
     int local = 0;
+    const DecodeConstants dc = p.decode;
     NML_PROF_DECL
     for (int index = blockIdx.x; index < units && ok; index += gridDim.x, ++local) {
       const uint8_t* unit_scales = nullptr;
@@ -887,13 +969,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         if (!wait(&full_scale[local & 1], (local >> 1) & 1, kSiteDecodeScale)) break;
         unit_scales = scale_buffer(local & 1) + row * p.scale_width;
       }
-      for (int rs = 0; rs < raw_stages && ok; ++rs) {
+      for (int rs = 0; rs < stages && ok; ++rs) {
         NML_PROF_BEGIN();
 #ifdef NML_SM100_DEBUG_WAITS
         wait_position.unit = local;
         wait_position.stage = rs;
 #endif
-        if (!wait(&full_raw[raw.index], raw.phase, kSiteDecodeRaw)) {
+        if (!wait(&full_p[ps.index], ps.phase, kSiteDecodeRaw)) {
           ok = false;
           break;
         }
@@ -901,73 +983,82 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         const int sub_steps = min(KS, p.k_steps - rs * KS);
         for (int j = 0; j < sub_steps; ++j, ++sequence, wb.advance<WB>()) {
           if (sequence % DG != group) continue;
-          NML_PROF_BEGIN();
 #ifdef NML_SM100_DEBUG_WAITS
           wait_position.step = sequence;
 #endif
-          if (!wait(&empty_w[wb.index], wb.phase ^ 1u, kSiteDecodeWeights)) {
-            ok = false;
-            break;
+          if constexpr (!WT) {
+            // the decoded tile is written as it is computed: the slot must be free first
+            NML_PROF_BEGIN();
+            if (!wait(&empty_w[wb.index], wb.phase ^ 1u, kSiteDecodeWeights)) {
+              ok = false;
+              break;
+            }
+            NML_PROF_END(1);
           }
-          NML_PROF_END(1);
           NML_PROF_BEGIN();
-#ifdef NML_SM100_PROFILE
-          if (p.knockout & 1) {
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&full_w[wb.index]);
-            continue;
-          }
-#endif
           uint4 codes[2];
           if constexpr (KS == 1) {
             const uint4* source =
-                reinterpret_cast<const uint4*>(payload_tile(raw.index) + row * 32);
+                reinterpret_cast<const uint4*>(payload_tile(ps.index) + row * 32);
             codes[0] = source[0];
             codes[1] = source[1];
           } else {
             // rows of 32*KS bytes, 128-byte swizzled by the TMA load
-            const uint8_t* source = payload_tile(raw.index) + row * (32 * KS);
+            const uint8_t* source = payload_tile(ps.index) + row * (32 * KS);
             codes[0] = *reinterpret_cast<const uint4*>(source + (((2 * j) ^ (row & 7)) * 16));
             codes[1] = *reinterpret_cast<const uint4*>(source + (((2 * j + 1) ^ (row & 7)) * 16));
           }
           const uint32_t four_scales =
               WT ? *reinterpret_cast<const uint32_t*>(unit_scales + (rs * KS + j) * 4)
-                 : *reinterpret_cast<const uint32_t*>(scale_tile(raw.index) + row * (4 * KS) +
+                 : *reinterpret_cast<const uint32_t*>(scale_tile(ps.index) + row * (4 * KS) +
                                                       j * 4);
           uint32_t scale[4];
           if constexpr (AFMT == kAf16) {
             scales2_f16(four_scales & 0xffffu, scale[0], scale[1]);
             scales2_f16(four_scales >> 16, scale[2], scale[3]);
           } else {
-#pragma unroll
-            for (int b = 0; b < 4; ++b) scale[b] = scale_bf16_dup((four_scales >> (8 * b)) & 0xffu);
+            scales4_bf16(four_scales, scale, dc);
           }
           const uint32_t words[8] = {codes[0].x, codes[0].y, codes[0].z, codes[0].w,
                                      codes[1].x, codes[1].y, codes[1].z, codes[1].w};
           if constexpr (WT) {
-            // 32-bit column c of this thread's lane holds elements 2c and 2c + 1 of the row
-            const uint32_t w_address = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
-                                       kAccColumns + wb.index * kWColumns;
-            __syncwarp();
+            // The row is decoded into registers before the warp waits for a free W' tile.
+            uint32_t o[4][8];
 #pragma unroll
             for (int pair = 0; pair < 4; ++pair) {
-              uint32_t o[8];
 #pragma unroll
               for (int half = 0; half < 2; ++half) {
                 uint32_t q4[4];
                 if constexpr (AFMT == kAf16) {
                   decode8_f16(words[2 * pair + half], scale[pair], q4);
                 } else {
-                  decode8_bf16(words[2 * pair + half], scale[pair], q4);
+                  decode8_bf16(words[2 * pair + half], scale[pair], q4, dc);
                 }
 #pragma unroll
-                for (int i = 0; i < 4; ++i) o[4 * half + i] = q4[i];
+                for (int i = 0; i < 4; ++i) o[pair][4 * half + i] = q4[i];
               }
-              tmem_store_32x8(w_address + pair * 8, o);
             }
+            NML_PROF_END(2);
+            NML_PROF_BEGIN();
+            if (!wait(&empty_w[wb.index], wb.phase ^ 1u, kSiteDecodeWeights)) {
+              ok = false;
+              break;
+            }
+            NML_PROF_END(1);
+            // 32-bit column c of this thread's lane holds elements 2c and 2c + 1 of the row
+            const uint32_t w_address = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
+                                       kAccColumns + wb.index * kWColumns;
+            __syncwarp();
+#pragma unroll
+            for (int pair = 0; pair < 4; ++pair) tmem_store_32x8(w_address + pair * 8, o[pair]);
+            // Announcing the tile one own K step later, so that the stores overlap the next
+            // row's arithmetic, was measured 1-3 % slower; so was freeing tiles in groups of
+            // KS with one commit per group.
             tmem_store_wait();
             tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full_w[wb.index]);
+            continue;
           } else {
             uint8_t* w_row = w_tile(wb.index) + row * 128;
 #pragma unroll
@@ -976,7 +1067,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
               if constexpr (AFMT == kAf16) {
                 decode8_f16(words[jj], scale[jj >> 1], o);
               } else {
-                decode8_bf16(words[jj], scale[jj >> 1], o);
+                decode8_bf16(words[jj], scale[jj >> 1], o, dc);
               }
               const int chunk = jj ^ (row & 7);
               *reinterpret_cast<uint4*>(w_row + chunk * 16) = make_uint4(o[0], o[1], o[2], o[3]);
@@ -988,7 +1079,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
           if (lane == 0) mbar_arrive(&full_w[wb.index]);
           NML_PROF_END(2);
         }
-        raw.advance<RAW>();
+        // this warp has read its last byte of the stage
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_p[ps.index]);
+        ps.advance<PS>();
       }
       if constexpr (WT) {
         // this warp has read its last scale of the unit: the buffer may be refilled
@@ -1009,8 +1103,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       const int row0 = t >> 3;
       const int position = (chunk ^ (row0 & 7)) * 16;
       const uint8_t* input = static_cast<const uint8_t*>(p.input);
-      constexpr int kLag = RAW > 2 ? 2 : RAW - 1;  // stages whose copies may still be landing
-      RingState raw, arrive;
+      constexpr int kLag = XS > 2 ? 2 : XS - 1;  // stages whose copies may still be landing
+      RingState xs, arrive;
       int in_flight = 0;
       bool ok = true;
       NML_PROF_DECL
@@ -1025,8 +1119,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
           }
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&full_raw[arrive.index]);
-          arrive.advance<RAW>();
+          if (lane == 0) mbar_arrive(&full_x[arrive.index]);
+          arrive.advance<XS>();
           --in_flight;
         }
       };
@@ -1045,13 +1139,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
           }
           source_offset[i] = offset;
         }
-        for (int rs = 0; rs < raw_stages; ++rs) {
+        for (int rs = 0; rs < stages; ++rs) {
           NML_PROF_BEGIN();
 #ifdef NML_SM100_DEBUG_WAITS
           wait_position.stage = rs;
           wait_position.step = in_flight;
 #endif
-          if (!wait(&raw_free[raw.index], raw.phase ^ 1u, kSiteGather)) {
+          if (!wait(&x_free[xs.index], xs.phase ^ 1u, kSiteGather)) {
             ok = false;
             break;
           }
@@ -1062,7 +1156,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
             const int k_step = rs * KS + j;
             if (k_step < p.k_steps) {
               const uint8_t* column = input + (static_cast<int64_t>(k_step) * kTileK + chunk * 8) * 2;
-              uint8_t* tile = x_tile(raw.index, j) + position + row0 * 128;
+              uint8_t* tile = x_tile(xs.index, j) + position + row0 * 128;
 #pragma unroll
               for (int i = 0; i < kRowsPerThread; ++i) {
                 const bool valid = source_offset[i] >= 0;
@@ -1073,7 +1167,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
           }
           asm volatile("cp.async.commit_group;" ::: "memory");
           ++in_flight;
-          raw.advance<RAW>();
+          xs.advance<XS>();
           NML_PROF_END(1);
           NML_PROF_BEGIN();
           retire(kLag);
@@ -1172,6 +1266,16 @@ inline bool encode_activation_map(CUtensorMap* map, const void* x, int64_t rows,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+inline void fill_decode_constants(DecodeConstants* c) {
+  c->mul4 = 4u;
+  c->mul16 = 16u;
+  c->mul64 = 64u;
+  c->mul256 = 256u;
+  c->mul4096 = 4096u;
+  c->hi26 = 1u << 26;
+  c->hi30 = 1u << 30;
 }
 
 // Opts a kernel into its dynamic shared memory once per device.  `configured` is the

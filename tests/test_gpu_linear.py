@@ -103,9 +103,10 @@ def test_tensor_core_kernel_shared_memory_weight_ring(M, K, N, dtype):
                expect_kernel="umma_swapab_a")
 
 
-@pytest.mark.parametrize("M,K,N", [(16, 4096, 2880), (64, 128, 130), (33, 3136, 512)])
+@pytest.mark.parametrize("M,K,N", [(200, 8192, 256), (64, 128, 130), (33, 16384, 512)])
 def test_tensor_core_kernel_falls_back_to_shared_memory_ring(M, K, N):
-    # K above the scale buffer, or an output count that breaks the bulk scale copy
+    # two scale buffers (128 rows x K/16 bytes each) that no longer fit beside the rings, or an
+    # output count that breaks the bulk scale copy
     from nml_b200 import _abi
     run_linear(M, K, N, oracle.BF16, _abi.POLICY_UMMA, seed=M + N + 2,
                expect_kernel="umma_swapab_abf16")
