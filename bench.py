@@ -46,13 +46,17 @@ def parse_args():
     parser = argparse.ArgumentParser(description=__doc__,
                                      formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=5)
+    parser.add_argument("--steps", type=int, default=20)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--no-e2e", action="store_true", help="skip the host-buffer pass")
     parser.add_argument("--no-detail", action="store_true", help="skip the per-shape table")
     parser.add_argument("--no-extras", action="store_true",
                         help="skip the sharded MoE / unembedding / embedding figures")
+    parser.add_argument("--kernel-policy", type=int, default=0,
+                        help="nml_nvfp4_sm100_set_kernel_policy value (profiling captures: "
+                             "100 + BM forces the tile height, 1000 + BM with the "
+                             "shared-memory weight ring)")
     parser.add_argument("--rows", type=str, default="",
                         help="comma-separated subset of M values (profiling captures)")
     parser.add_argument("--shapes", type=str, default="",
@@ -98,7 +102,7 @@ class ClockSampler:
         try:
             self.process = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.process = None
@@ -110,9 +114,11 @@ class ClockSampler:
         for line in self.process.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) >= 6 and parts[0].isdigit():
-                self.samples.append(parts)
+                self.samples.append(parts + [time.time()])
 
-    def stop(self) -> dict:
+    def stop(self, window_begin: float = 0.0, window_end: float = float("inf")) -> dict:
+        """Summary of the samples taken inside [window_begin, window_end]; when the window
+        is shorter than the sampling period, of those taken since the warm-up began."""
         if self.process is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         self.process.terminate()
@@ -122,14 +128,19 @@ class ClockSampler:
             self.process.kill()
         if self.thread is not None:
             self.thread.join(timeout=2)
-        if not self.samples:
+        inside = [s for s in self.samples if window_begin <= s[-1] <= window_end]
+        scope = "timed region"
+        if len(inside) < 3:
+            inside, scope = self.samples, "warm-up and timed region"
+        if not inside:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.samples = inside
         clocks = [int(s[0]) for s in self.samples]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [name for i, name in enumerate(names)
                    if any(s[2 + i].lower().startswith("active") for s in self.samples)]
         return {"sm_mhz": int(statistics.median(clocks)), "sm_max_mhz": int(self.samples[0][1]),
-                "reasons": reasons, "samples": len(self.samples)}
+                "reasons": reasons, "samples": len(self.samples), "scope": scope}
 
 
 # ------------------------------------------------------------------ CPU baseline
@@ -253,6 +264,8 @@ def run_ours(args) -> None:
         os.environ.pop("NCCL_DEBUG", None)
         dist.init_process_group("nccl", device_id=device)
     _abi.load()
+    if args.kernel_policy:
+        _abi.set_kernel_policy(args.kernel_policy)
     shapes, rows = select(args)
     full_sweep = shapes == SHAPES and rows == ROWS
 
@@ -274,7 +287,10 @@ def run_ours(args) -> None:
                                                   generator=generator).to(torch.bfloat16)
     outputs = {(name, m): torch.empty((m, n), dtype=torch.bfloat16, device=device)
                for name, _, n in shapes for m in rows}
-    cases = [(name, k, n, m) for name, k, n in shapes for m in rows]
+    # Largest first: the host then runs far ahead of the device, so no launch waits for the
+    # host, per-launch event times hold kernel time only and the clocks stay up.
+    cases = sorted(((name, k, n, m) for name, k, n in shapes for m in rows),
+                   key=lambda c: -(c[1] * c[2] * c[3]))
     torch.cuda.synchronize()
 
     selected = {}  # case -> (kernel family, activation rows per tile) the library chose
@@ -295,6 +311,9 @@ def run_ours(args) -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     for _ in range(max(args.warmup, 3)):
         one_pass()
     barrier()
@@ -304,16 +323,14 @@ def run_ours(args) -> None:
     step_events = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
                     for _ in cases] for _ in range(args.steps)]
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     barrier()
+    window_begin = time.time()
     begin.record()
     for step in range(args.steps):
         one_pass(step_events[step])
     end.record()
     barrier()
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(window_begin, time.time()) if rank == 0 else None
     elapsed_ms = begin.elapsed_time(end)
     if world > 1:
         t = torch.tensor([elapsed_ms], dtype=torch.float64, device=device)
