@@ -366,7 +366,10 @@ def run_ours(args) -> None:
                                    "bf16 decodes of the NVFP4 weights",
                     "launches_per_step": len(dominant),
                     "avg_launch_ms": d_time / len(dominant) * 1e3,
-                    "traffic": NCU_TRAFFIC["gemm_kernel_large_tiles"]}
+                    "traffic": NCU_TRAFFIC["gemm_kernel_large_tiles"],
+                    "traffic_case": "dram read+write bytes of one launch of 2880->5760 at "
+                                    "M=16384 (algorithmic 292e6); the other launches were "
+                                    "not captured"}
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -408,7 +411,7 @@ def run_ours(args) -> None:
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from ncu captures, filled in from
 # the summaries under profiles/ (None until a capture exists).
-NCU_TRAFFIC = {"gemm_kernel_large_tiles": None}
+NCU_TRAFFIC = {"gemm_kernel_large_tiles": 253.2e6}  # 2880->5760 at M=16384, BM=256 (292 MB algorithmic)
 
 
 def shape_table(cases, durations, weights, activations, outputs, peaks, selected):
