@@ -23,7 +23,7 @@ template <int BM, int KS, int PS, int XS, int WB, int DG, int MI, int PA, bool W
           typename T, int MODE, bool XTMA>
 int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* message,
                       size_t capacity) {
-  using L = Layout<BM, KS, PS, XS, WB, true, WT>;
+  using L = KernelLayout<BM, KS, PS, XS, WB, WT, AFMT, MODE, false>;
   const int scale_buffer_bytes = WT ? ((args.inputs / 16 * kTileN + 127) / 128) * 128 : 0;
   const int smem_bytes = L::kSmemBytes + 2 * scale_buffer_bytes;
   if (smem_bytes > kSmemBudget) return kDoesNotFit;

@@ -18,11 +18,11 @@ using namespace umma;
 constexpr int32_t kDoesNotFit = -1000;  // internal: the variant's shared memory exceeds the SM's
 
 template <int BM, int KS, int PS, int XS, int WB, int DG, int MI, int PA, bool WT, int AFMT,
-          typename T>
+          typename T, bool SB = false>
 int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* message,
                       size_t capacity) {
-  using L = Layout<BM, KS, PS, XS, WB, false, WT>;
-  const int scale_buffer_bytes = WT ? ((args.inputs / 16 * kTileN + 127) / 128) * 128 : 0;
+  using L = KernelLayout<BM, KS, PS, XS, WB, WT, AFMT, kDense, SB>;
+  const int scale_buffer_bytes = (WT || SB) ? ((args.inputs / 16 * kTileN + 127) / 128) * 128 : 0;
   const int smem_bytes = L::kSmemBytes + 2 * scale_buffer_bytes;
   if (smem_bytes > kSmemBudget) return kDoesNotFit;
   CUtensorMap tmap_payload, tmap_x;
@@ -55,9 +55,9 @@ int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* me
   p.knockout = std::getenv("NML_SM100_KNOCKOUT") ? std::atoi(std::getenv("NML_SM100_KNOCKOUT")) : 0;
 #endif
 
-  auto kernel = gemm_kernel<BM, KS, PS, XS, WB, DG, MI, PA, WT, AFMT, T, kDense, true>;
+  auto kernel = gemm_kernel<BM, KS, PS, XS, WB, DG, MI, PA, WT, AFMT, T, kDense, true, SB>;
   static bool configured[64] = {};
-  if (!reserve_smem(kernel, WT ? kSmemBudget : L::kSmemBytes, device.device, configured)) {
+  if (!reserve_smem(kernel, (WT || SB) ? kSmemBudget : L::kSmemBytes, device.device, configured)) {
     return fail(NML_SM100_LAUNCH_FAILURE, "cannot reserve shared memory for the tcgen05 linear",
                 message, capacity);
   }
@@ -65,7 +65,9 @@ int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* me
   const unsigned grid = static_cast<unsigned>(tiles < device.sm_count ? tiles : device.sm_count);
   kernel<<<grid, launch_threads<DG, MI, true>(), smem_bytes, args.stream>>>(tmap_payload, tmap_x,
                                                                             p);
-  note_linear_kernel(WT ? (AFMT == kAf16 ? "umma_tmem_weights_af16" : "umma_tmem_weights_abf16")
+  note_linear_kernel(WT ? (AFMT == kAf16      ? "umma_tmem_weights_af16"
+                           : AFMT == kAbf16Lut ? "umma_tmem_weights_abf16_lut"
+                                               : "umma_tmem_weights_abf16")
                         : (AFMT == kAf16 ? "umma_swapab_af16" : "umma_swapab_abf16"), BM);
   return launch_result(message, capacity);
 }
@@ -103,12 +105,48 @@ int32_t launch_for_rows(const LinearArgs& args, const DeviceInfo& device, char* 
                         size_t capacity) {
   // Decoded weights in tensor memory: the unit's block scales (128 rows x K/16 bytes) must
   // form a legal bulk copy and two such buffers must fit beside the rings.
-  // Experiment hook: policy 100 + BM forces the tile height (tensor-memory variant), policy
-  // 1000 + BM forces it for the shared-memory ring.
+  // Experiment hooks: policy 100 + BM forces the tile height (tensor-memory variant), 2000 +
+  // BM the same without the byte-table decode, 1000 + BM the shared-memory ring (1257: 256
+  // rows with per-stage scale copies); policy 4 turns the byte-table decode off.
   const int policy = get_kernel_policy();
-  const int forced_rows = policy >= 1000 ? policy - 1000 : policy >= 100 ? policy - 100 : 0;
-  const bool tmem_weights = policy != 3 && policy < 1000 && args.outputs % 4 == 0 &&
-                            reinterpret_cast<uintptr_t>(args.block_scales) % 16 == 0;
+  const int forced_rows = policy >= 2000   ? policy - 2000
+                          : policy >= 1000 ? policy - 1000
+                          : policy >= 100  ? policy - 100
+                                           : 0;
+  const bool table_decode = policy != 4 && policy < 2000;
+  const bool bulk_scales_legal = args.outputs % 4 == 0 &&
+                                 reinterpret_cast<uintptr_t>(args.block_scales) % 16 == 0;
+  const bool tmem_weights = policy != 3 && (policy < 1000 || policy >= 2000) && bulk_scales_legal;
+  if (tmem_weights && AFMT == kAbf16 && table_decode) {
+    // bf16 operands through the byte table (32 KB of shared memory; slightly shallower rings)
+    int32_t rc = kDoesNotFit;
+    switch (forced_rows ? forced_rows
+                        : choose_tile_rows(args.rows, args.outputs, device.sm_count, true)) {
+      case 16:
+        rc = launch_config<16, 4, 6, 4, 8, 3, 2, 8, true, kAbf16Lut, T>(args, device, message,
+                                                                        capacity);
+        break;
+      case 32:
+        rc = launch_config<32, 4, 5, 4, 8, 3, 1, 4, true, kAbf16Lut, T>(args, device, message,
+                                                                        capacity);
+        break;
+      case 64:
+        rc = launch_config<64, 4, 3, 2, 8, 3, 1, 2, true, kAbf16Lut, T>(args, device, message,
+                                                                        capacity);
+        break;
+      case 128:
+        rc = launch_config<128, 1, 8, 6, 6, 4, 1, 1, true, kAbf16Lut, T>(args, device, message,
+                                                                         capacity);
+        break;
+      case 192:
+        rc = launch_config<192, 1, 6, 4, 4, 3, 1, 1, true, kAbf16Lut, T>(args, device, message,
+                                                                         capacity);
+        break;
+      default:
+        break;
+    }
+    if (rc != kDoesNotFit) return rc;
+  }
   if (tmem_weights) {
     int32_t rc = kDoesNotFit;
     switch (forced_rows ? forced_rows
@@ -135,7 +173,7 @@ int32_t launch_for_rows(const LinearArgs& args, const DeviceInfo& device, char* 
     }
     if (rc != kDoesNotFit) return rc;
   }
-  switch (forced_rows && forced_rows != 192
+  switch (forced_rows && forced_rows != 192 && forced_rows != 257
               ? forced_rows
               : choose_tile_rows(args.rows, args.outputs, device.sm_count, false)) {
     case 16:
@@ -150,9 +188,17 @@ int32_t launch_for_rows(const LinearArgs& args, const DeviceInfo& device, char* 
     case 128:
       return launch_config<128, 1, 8, 5, 5, 3, 1, 1, false, AFMT, T>(args, device, message,
                                                                      capacity);
-    default:
+    default: {
+      // 256-row tiles: scales by bulk copy when the two buffers fit beside three activation
+      // stages (K <= ~2900) and the copy is legal; else per-stage 4-byte copies
+      if (bulk_scales_legal && policy != 1257) {
+        const int32_t rc = launch_config<256, 1, 4, 3, 4, 3, 1, 1, false, AFMT, T, true>(
+            args, device, message, capacity);
+        if (rc != kDoesNotFit) return rc;
+      }
       return launch_config<256, 1, 6, 4, 4, 3, 1, 1, false, AFMT, T>(args, device, message,
                                                                      capacity);
+    }
   }
 }
 

@@ -42,7 +42,10 @@ namespace nml_sm100 {
 namespace umma {
 
 enum Mode : int { kDense = 0, kGateUp = 1, kDown = 2 };
-enum AFormat : int { kAf16 = 0, kAbf16 = 1 };
+// kAbf16Lut: bf16 operands decoded through a byte -> two-bf16 table in shared memory instead
+// of integer bit placement (a third of the integer-pipe work; needs 32 KB for the table).
+enum AFormat : int { kAf16 = 0, kAbf16 = 1, kAbf16Lut = 2 };
+constexpr int kLutBytes = 256 * 32 * 4;  // 256 entries, one copy per lane (bank)
 
 constexpr int kTileN = 128;
 constexpr int kTileK = 64;
@@ -83,22 +86,26 @@ constexpr int kMaxGroups = 256;
 // the block scales of a whole unit arrive with one bulk copy into one of two buffers;
 // otherwise the decoded tiles form a shared-memory ring and every P stage carries its own
 // scale bytes.
-template <int BM, int KS, int PS, int XS, int WB, bool GROUPED, bool WT>
+// BULK (always with WT, optional without): block scales by one bulk copy per unit.
+template <int BM, int KS, int PS, int XS, int WB, bool GROUPED, bool WT, bool BULK = WT,
+          bool LUT = false>
 struct Layout {
+  static_assert(BULK || !WT, "tensor-memory weight tiles take their scales by bulk copy");
   static constexpr int kPayloadBytes = kTileN * 32 * KS;
-  static constexpr int kScaleBytes = WT ? 0 : (kTileN * 4 * KS < 1024 ? 1024 : kTileN * 4 * KS);
+  static constexpr int kScaleBytes = BULK ? 0 : (kTileN * 4 * KS < 1024 ? 1024 : kTileN * 4 * KS);
   static constexpr int kPBytes = kPayloadBytes + kScaleBytes;  // one P stage
   static constexpr int kXBytes = BM * 128;                     // one K step of X
   static constexpr int kXStageBytes = KS * kXBytes;
   static constexpr int kXOffset = WT ? 0 : WB * kWBytes;       // the W' ring comes first
   static constexpr int kPOffset = kXOffset + XS * kXStageBytes;
-  static constexpr int kBarrierOffset = kPOffset + PS * kPBytes;
+  static constexpr int kLutOffset = kPOffset + PS * kPBytes;
+  static constexpr int kBarrierOffset = kLutOffset + (LUT ? kLutBytes : 0);
   static constexpr int kBarrierBytes = 2048;
   // grouped: group table + one slot table (assignment id, routing weight) per epilogue warp
   static constexpr int kSlotTableBytes = GROUPED ? kEpilogueWarps * BM * 6 : 0;
   static constexpr int kGroupBytes =
       GROUPED ? ((kMaxGroups * 16 + 64 + kSlotTableBytes + 127) / 128) * 128 : 0;
-  // WT: two scale buffers of Params::scale_buffer_bytes each follow (sized at launch)
+  // BULK: two scale buffers of Params::scale_buffer_bytes each follow (sized at launch)
   static constexpr int kScaleBufferOffset = kBarrierOffset + kBarrierBytes + kGroupBytes;
   static constexpr int kSmemBytes = kScaleBufferOffset + 1024;  // + alignment slack
   static constexpr int kTmemColumns = 2 * BM < 32 ? 32 : 2 * BM;
@@ -114,6 +121,12 @@ struct DecodeConstants {
   uint32_t mul4, mul16, mul64, mul256, mul4096;  // left shifts by 2, 4, 6, 8, 12
   uint32_t hi26, hi30;                           // mul.hi by 2^26, 2^30: right shifts by 6, 2
 };
+
+// The one place that maps a kernel instantiation to its shared-memory layout; the kernel and
+// its launchers both use it, so the launch can never reserve less than the kernel addresses.
+template <int BM, int KS, int PS, int XS, int WB, bool WT, int AFMT, int MODE, bool SB>
+using KernelLayout =
+    Layout<BM, KS, PS, XS, WB, MODE != kDense, WT, WT || SB, AFMT == kAbf16Lut>;
 
 struct Params {
   // weights
@@ -243,6 +256,36 @@ __device__ __forceinline__ void decode8_bf16(uint32_t q, uint32_t scale2, uint32
   out[1] = __byte_perm(t[2], t[3], 0x5410);
   out[2] = __byte_perm(t[0], t[1], 0x7632);
   out[3] = __byte_perm(t[2], t[3], 0x7632);
+}
+
+// 8 codes -> 8 exact bf16 values code * scale through the byte table: entry stride 128 bytes,
+// this lane's copy at `lut_lane`.  Four shift+mask pairs, four loads, four multiplies; the
+// table already holds the two values of a byte in K order.
+__device__ __forceinline__ void decode8_bf16_lut(uint32_t q, uint32_t scale2, uint32_t (&out)[4],
+                                                 const uint8_t* lut_lane) {
+  const uint32_t offset[4] = {(q << 7) & 0x7f80u, (q >> 1) & 0x7f80u, (q >> 9) & 0x7f80u,
+                              (q >> 17) & 0x7f80u};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    out[i] = *reinterpret_cast<const uint32_t*>(lut_lane + offset[i]);
+    asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(out[i]) : "r"(scale2));
+  }
+}
+
+// Four E4M3 scale bytes -> four words holding the exact bf16 scale in both halves (a byte's
+// value bits at bf16 bits 10:4 read as scale * 2^-120).
+__device__ __forceinline__ void scales4_bf16_true(uint32_t four_bytes, uint32_t (&scale)[4]) {
+  const uint32_t two_p120 = 0x7b807b80u;
+  uint32_t pair[2];
+  pair[0] = __byte_perm(four_bytes, 0u, 0x4140);
+  pair[1] = __byte_perm(four_bytes, 0u, 0x4342);
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    pair[i] = (pair[i] & 0x007f007fu) << 4;
+    asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(pair[i]) : "r"(two_p120));
+    scale[2 * i] = __byte_perm(pair[i], pair[i], 0x1010);
+    scale[2 * i + 1] = __byte_perm(pair[i], pair[i], 0x3232);
+  }
 }
 
 // Four E4M3 scale bytes -> four words holding bf16(scale * 2^119) in both halves: a byte's
@@ -424,7 +467,7 @@ struct RingState {
 // activation rows, so the K=16 slices rotate over PA accumulators (instruction i of a unit
 // goes to accumulator i % PA) and the epilogue adds them in index order.
 template <int BM, int KS, int PS, int XS, int WB, int DG, int MI, int PA, bool WT, int AFMT,
-          typename T, int MODE, bool XTMA>
+          typename T, int MODE, bool XTMA, bool SB = false>
 __global__ void __launch_bounds__(launch_threads<DG, MI, XTMA>(), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
             const __grid_constant__ CUtensorMap tmap_x, const Params p) {
@@ -435,7 +478,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
   static_assert(MI == 1 || PA == 8, "two issuers need disjoint partial accumulators");
   static_assert(WB > DG, "the W' ring must hold one tile per decode group plus one");
   static_assert(GROUPED || XTMA, "the dense mode always loads activations by TMA");
-  using L = Layout<BM, KS, PS, XS, WB, GROUPED, WT>;
+  constexpr bool kBulk = WT || SB;  // block scales of a unit by one bulk copy
+  constexpr bool kLut = AFMT == kAbf16Lut;
+  using L = KernelLayout<BM, KS, PS, XS, WB, WT, AFMT, MODE, SB>;
   constexpr int kAccColumns = PA * L::kTmemColumns;   // two accumulator sets of PA partials
   constexpr int kWColumns = kTileK / 2;                // one decoded K step: 64 x 16 bit per row
   constexpr int kTmemNeeded = kAccColumns + (WT ? WB * kWColumns : 0);
@@ -478,7 +523,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
 
   if (threadIdx.x == 0) {
     for (int r = 0; r < PS; ++r) {
-      mbar_init(&full_p[r], 1 + (WT ? 0 : 32));  // expect_tx arrival (+ the lanes' scale copies)
+      mbar_init(&full_p[r], 1 + (kBulk ? 0 : 32));  // expect_tx arrival (+ the lanes' scale copies)
       mbar_init(&empty_p[r], 4 * DG);            // every decode warp
     }
     for (int r = 0; r < XS; ++r) {
@@ -505,6 +550,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
   if (warp == kMmaWarp) {
     tmem_alloc(tmem_slot, kTmemColumns);
     tmem_relinquish_alloc_permit();
+  }
+  if constexpr (kLut) {
+    // entry b = bf16 values of the two codes of byte b (low nibble in the low half); copy
+    // `lane` of an entry sits in bank `lane`, so a warp's 32 lookups never conflict
+    uint32_t* lut = reinterpret_cast<uint32_t*>(smem + L::kLutOffset);
+    for (int i = threadIdx.x; i < 256 * 32; i += blockDim.x) {
+      const uint32_t byte = static_cast<uint32_t>(i) >> 5;
+      uint32_t entry = 0;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const uint32_t code = (byte >> (4 * half)) & 0xfu;
+        const uint32_t m = code & 0x7u;
+        uint32_t bits = m == 0 ? 0u : m == 1 ? 0x3f00u : ((126u + (m >> 1)) << 7) | ((m & 1u) << 6);
+        bits |= (code & 0x8u) << 12;
+        entry |= bits << (16 * half);
+      }
+      lut[i] = entry;
+    }
   }
   tcgen05_fence_before_sync();
   __syncthreads();
@@ -564,7 +627,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
 #ifdef NML_SM100_DEBUG_WAITS
       wait_position.unit = local;
 #endif
-      if constexpr (WT) {
+      if constexpr (kBulk) {
         // all block scales of the unit's weight rows: one contiguous range of the tensor
         const int b = local & 1;
         if (!wait(&empty_scale[b], ((local >> 1) & 1) ^ 1u, kSiteProducerScale)) break;
@@ -592,7 +655,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
           tma_load_2d(payload_tile(ps.index), &tmap_payload, &full_p[ps.index], rs * KS * 32,
                       u.weight_row0);
         }
-        if constexpr (!WT) {
+        if constexpr (!kBulk) {
           // block scales: 4 bytes per row and K step (scale rows are not TMA-legal)
 #pragma unroll
           for (int j = 0; j < KS; ++j) {
@@ -622,7 +685,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       if (ps.index == PS - 1) ps.phase ^= 1u;
       if (!mbar_wait(&full_p[ps.index], ps.phase)) give_up(kSiteProducerDrain);
     }
-    if constexpr (WT) {
+    if constexpr (kBulk) {
       for (int back = 1; back <= 2 && back <= local; ++back) {
         const int unit = local - back;
         if (!mbar_wait(&full_scale[unit & 1], (unit >> 1) & 1)) give_up(kSiteProducerDrain);
@@ -962,10 +1025,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     bool ok = true;
     int local = 0;
     const DecodeConstants dc = p.decode;
+    const uint8_t* lut_lane = smem + L::kLutOffset + lane * 4;  // this lane's copy of the table
     NML_PROF_DECL
     for (int index = blockIdx.x; index < units && ok; index += gridDim.x, ++local) {
       const uint8_t* unit_scales = nullptr;
-      if constexpr (WT) {
+      if constexpr (kBulk) {
         if (!wait(&full_scale[local & 1], (local >> 1) & 1, kSiteDecodeScale)) break;
         unit_scales = scale_buffer(local & 1) + row * p.scale_width;
       }
@@ -1009,13 +1073,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
             codes[1] = *reinterpret_cast<const uint4*>(source + (((2 * j + 1) ^ (row & 7)) * 16));
           }
           const uint32_t four_scales =
-              WT ? *reinterpret_cast<const uint32_t*>(unit_scales + (rs * KS + j) * 4)
+              kBulk ? *reinterpret_cast<const uint32_t*>(unit_scales + (rs * KS + j) * 4)
                  : *reinterpret_cast<const uint32_t*>(scale_tile(ps.index) + row * (4 * KS) +
                                                       j * 4);
           uint32_t scale[4];
           if constexpr (AFMT == kAf16) {
             scales2_f16(four_scales & 0xffffu, scale[0], scale[1]);
             scales2_f16(four_scales >> 16, scale[2], scale[3]);
+          } else if constexpr (kLut) {
+            scales4_bf16_true(four_scales, scale);
           } else {
             scales4_bf16(four_scales, scale, dc);
           }
@@ -1031,6 +1097,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
                 uint32_t q4[4];
                 if constexpr (AFMT == kAf16) {
                   decode8_f16(words[2 * pair + half], scale[pair], q4);
+                } else if constexpr (kLut) {
+                  decode8_bf16_lut(words[2 * pair + half], scale[pair], q4, lut_lane);
                 } else {
                   decode8_bf16(words[2 * pair + half], scale[pair], q4, dc);
                 }
@@ -1066,6 +1134,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
               uint32_t o[4];
               if constexpr (AFMT == kAf16) {
                 decode8_f16(words[jj], scale[jj >> 1], o);
+              } else if constexpr (kLut) {
+                decode8_bf16_lut(words[jj], scale[jj >> 1], o, lut_lane);
               } else {
                 decode8_bf16(words[jj], scale[jj >> 1], o, dc);
               }
@@ -1084,7 +1154,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         if (lane == 0) mbar_arrive(&empty_p[ps.index]);
         ps.advance<PS>();
       }
-      if constexpr (WT) {
+      if constexpr (kBulk) {
         // this warp has read its last scale of the unit: the buffer may be refilled
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_scale[local & 1]);
