@@ -477,13 +477,39 @@ def end_to_end(args, cases, weights, activations, outputs, world, barrier, flops
     h2d = sum(host_x[(k, m)].numel() * 2 for _, k, _, m in cases)
     d2h = sum(outputs[(name, m)].numel() * 2 for name, _, _, m in cases)
 
+    # Three streams: uploads, kernels, downloads.  A case's kernel waits for its upload; its
+    # download waits for the kernel; an activation buffer is not overwritten while a kernel
+    # still reads it, an output buffer not while its previous download is in flight.
+    main = torch.cuda.current_stream()
+    upload, download = torch.cuda.Stream(), torch.cuda.Stream()
+    x_readers_done = {key: None for key in activations}
+    out_downloaded = {key: None for key in outputs}
+
     def one_pass():
         for name, k, n, m in cases:
             x = activations[(k, m)]
-            x.copy_(host_x[(k, m)], non_blocking=True)
+            with torch.cuda.stream(upload):
+                if x_readers_done[(k, m)] is not None:
+                    upload.wait_event(x_readers_done[(k, m)])
+                x.copy_(host_x[(k, m)], non_blocking=True)
+                uploaded = torch.cuda.Event()
+                uploaded.record(upload)
             out = outputs[(name, m)]
+            main.wait_event(uploaded)
+            if out_downloaded[(name, m)] is not None:
+                main.wait_event(out_downloaded[(name, m)])
             ops.linear(x, weights[name], out=out)
-            host_out[:out.numel()].view(m, n).copy_(out, non_blocking=True)
+            computed = torch.cuda.Event()
+            computed.record(main)
+            x_readers_done[(k, m)] = computed
+            with torch.cuda.stream(download):
+                download.wait_event(computed)
+                host_out[:out.numel()].view(m, n).copy_(out, non_blocking=True)
+                done = torch.cuda.Event()
+                done.record(download)
+            out_downloaded[(name, m)] = done
+        # the timed stream ends only when the last download has landed
+        main.wait_stream(download)
 
     steps = max(1, min(args.steps, 5))
     one_pass()
