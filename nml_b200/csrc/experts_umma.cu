@@ -103,6 +103,24 @@ int32_t launch_for_load(const ExpertArgs& args, const DeviceInfo& device, char* 
   const int rows_per_expert = args.gate_up ? 2 * args.outputs : args.outputs;
   const bool tmem_weights = get_kernel_policy() != 3 && rows_per_expert % 4 == 0 &&
                             reinterpret_cast<uintptr_t>(args.block_scales) % 16 == 0;
+  if (tmem_weights && average <= 160 && AFMT == kAbf16 && get_kernel_policy() != 4) {
+    // bf16 operands through the byte table (32 KB of shared memory; slightly shallower rings)
+    int32_t rc;
+    if (average <= 16) {
+      rc = launch_config<16, 4, 6, 4, 8, 2, 2, 8, true, kAbf16Lut, T, MODE, XTMA>(
+          args, device, message, capacity);
+    } else if (average <= 32) {
+      rc = launch_config<32, 4, 4, 4, 8, 2, 1, 4, true, kAbf16Lut, T, MODE, XTMA>(
+          args, device, message, capacity);
+    } else if (average <= 64) {
+      rc = launch_config<64, 4, 3, 2, 8, 2, 1, 2, true, kAbf16Lut, T, MODE, XTMA>(
+          args, device, message, capacity);
+    } else {
+      rc = launch_config<128, 1, 8, 6, 6, 2, 1, 1, true, kAbf16Lut, T, MODE, XTMA>(
+          args, device, message, capacity);
+    }
+    if (rc != kDoesNotFit) return rc;
+  }
   if (tmem_weights && average <= 160) {
     int32_t rc;
     if (average <= 16) {
