@@ -109,12 +109,13 @@ def test_nccl_ranks_match_single_device_evaluation():
     manager = mp.Manager()
     results = manager.dict()
     mp.spawn(nccl_worker, args=(world, free_port(), results), nprocs=world, join=True)
+    # A shard sees other batch sizes than the single device (rows per expert, output columns),
+    # so the tile variant and with it the f32 accumulation order may differ: the results agree
+    # to GEMM tolerance, bit for bit only when both sides select the same variant.
     for rank in range(world):
         outcome = results[rank]
-        out, expected = outcome["alltoall"]
-        assert np.array_equal(out, expected), f"alltoall rank {rank}"
-        out, expected = outcome["unembed"]
-        assert np.array_equal(out, expected), f"unembed rank {rank}"
-        out, expected = outcome["allreduce"]
-        a, e = oracle.to_f32(out, oracle.BF16), oracle.to_f32(expected, oracle.BF16)
-        assert np.linalg.norm(a - e) <= 1e-2 * np.linalg.norm(e), f"allreduce rank {rank}"
+        for schedule in ("alltoall", "allreduce", "unembed"):
+            out, expected = outcome[schedule]
+            a, e = oracle.to_f32(out, oracle.BF16), oracle.to_f32(expected, oracle.BF16)
+            assert np.isfinite(a).all(), f"{schedule} rank {rank}"
+            assert np.linalg.norm(a - e) <= 1e-2 * np.linalg.norm(e), f"{schedule} rank {rank}"
