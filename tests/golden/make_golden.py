@@ -57,7 +57,10 @@ CASES = {
 
 
 def main() -> int:
-    reference = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        print("usage: make_golden.py <path of a checkout of the reference project>")
+        return 2
+    reference = Path(sys.argv[1])
     convert = load(reference / "tools/nvfp4/convert.py", "nml_ref_convert")
     extract = load(reference / "tools/nvfp4/extract_fixture.py", "nml_ref_extract")
     rng = np.random.Generator(np.random.PCG64(20250101))
