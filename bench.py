@@ -401,6 +401,7 @@ def run_ours(args) -> None:
         extras = sharded_extras(args, rank, world, device, barrier, head, peaks)
         if rank == 0:
             line.update(extras)
+            line["qkv_fused"] = qkv_fusion_figures(device)
     if rank == 0:
         if world == 1 and full_sweep:
             line["cpu_baseline"] = time_cpu_baseline()
@@ -549,6 +550,43 @@ def timed(fn, warmup, steps, barrier, world):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         elapsed = float(t.item())
     return elapsed
+
+
+def qkv_fusion_figures(device) -> list:
+    """The Q/K/V projections of one GPT-OSS-20B layer (2880 -> 4096 + 512 + 512) at decode
+    batch sizes: one fused launch against three linear launches (device time per layer,
+    weights L2-resident; not part of `value`)."""
+    import torch
+    from nml_b200 import ops, quantize
+    generator = torch.Generator(device=device).manual_seed(7)
+    weights = [quantize.quantize_parameter(
+        name, (torch.randn((n, 2880), device=device, generator=generator) * 0.02)
+        .to(torch.bfloat16)) for name, n in (("q", 4096), ("k", 512), ("v", 512))]
+    rows = []
+    for m in (1, 16, 64):
+        x = torch.randn((m, 2880), device=device, generator=generator).to(torch.bfloat16)
+
+        def fused():
+            ops.linear_qkv(x, weights[0], None, weights[1], None, weights[2], None)
+
+        def separate():
+            for w in weights:
+                ops.linear(x, w)
+
+        times = {}
+        for label, fn in (("fused_us", fused), ("three_launches_us", separate)):
+            for _ in range(5):
+                fn()
+            torch.cuda.synchronize()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            for _ in range(50):
+                fn()
+            end.record()
+            torch.cuda.synchronize()
+            times[label] = begin.elapsed_time(end) * 1e3 / 50
+        rows.append({"M": m, **times})
+    return rows
 
 
 def sharded_extras(args, rank, world, device, barrier, head, peaks) -> dict:

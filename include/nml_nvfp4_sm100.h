@@ -60,6 +60,28 @@ typedef struct NmlSm100Linear {
   int32_t dtype; /* NmlSm100DType */
 } NmlSm100Linear;
 
+/* Three linears that share one activation (the Q, K and V projections), in one launch:
+ * output[i][rows, outputs[i]] = X * W_i^T (+ bias[i]).  The reference fuses them only for
+ * rows <= 8 on its Triton path (crates/nml-ir/src/nvfp4_backend.rs:221-380, config
+ * NvFp4QkvConfig) and lowers three custom calls otherwise; here one launch serves every row
+ * count the tcgen05 kernel takes (inputs a multiple of 64), else the call is answered by three
+ * linear launches.  Same dtype and inputs for all three; each weight has its own global scale
+ * and optional bias.  Results equal those of three nml_nvfp4_sm100_linear calls bit for bit. */
+typedef struct NmlSm100LinearQkv {
+  size_t struct_size;
+  const void *activation;         /* [rows, inputs] dtype */
+  const uint8_t *payload[3];      /* [outputs[i], ceil(inputs/2)] */
+  const uint8_t *block_scales[3]; /* [outputs[i], ceil(inputs/16)] */
+  const float *global_scale[3];   /* device scalars */
+  const void *bias[3];            /* [outputs[i]] dtype, each may be NULL */
+  void *output[3];                /* [rows, outputs[i]] dtype */
+  void *stream;
+  int64_t rows;
+  int64_t outputs[3];
+  int64_t inputs;
+  int32_t dtype;
+} NmlSm100LinearQkv;
+
 /* out[r, :] = decode(W[indices[r], :]); an index outside [0, vocabulary) yields a row of
  * zeros and raises the device status bit NML_SM100_STATUS_INDEX_RANGE.
  * Field-for-field NmlNvFp4Embedding (nml_nvfp4.h:33-46). */
@@ -289,6 +311,8 @@ int32_t nml_nvfp4_sm100_linear(const NmlSm100Linear *request, char *error_messag
                                size_t error_message_capacity);
 
 /* Replaces nml_nvfp4_turing_embedding (nml_nvfp4.h:98-100, turing_adapter.cu:735-783). */
+int32_t nml_nvfp4_sm100_linear_qkv(const NmlSm100LinearQkv *request, char *error_message,
+                                   size_t error_message_capacity);
 int32_t nml_nvfp4_sm100_embedding(const NmlSm100Embedding *request, char *error_message,
                                   size_t error_message_capacity);
 

@@ -42,6 +42,13 @@ class Linear(ctypes.Structure):
                 ("dtype", _i32)]
 
 
+class LinearQkv(ctypes.Structure):
+    _fields_ = [("struct_size", _sz), ("activation", _vp), ("payload", _vp * 3),
+                ("block_scales", _vp * 3), ("global_scale", _vp * 3), ("bias", _vp * 3),
+                ("output", _vp * 3), ("stream", _vp), ("rows", _i64), ("outputs", _i64 * 3),
+                ("inputs", _i64), ("dtype", _i32)]
+
+
 class Embedding(ctypes.Structure):
     _fields_ = [("struct_size", _sz), ("indices", _vp), ("payload", _vp), ("block_scales", _vp),
                 ("global_scale", _vp), ("output", _vp), ("stream", _vp), ("rows", _i64),
@@ -123,6 +130,7 @@ class CombineRows(ctypes.Structure):
 # name -> request structure, for the entry points of the form fn(const Request*, char*, size_t)
 REQUEST_ENTRY_POINTS = {
     "nml_nvfp4_sm100_linear": Linear,
+    "nml_nvfp4_sm100_linear_qkv": LinearQkv,
     "nml_nvfp4_sm100_embedding": Embedding,
     "nml_nvfp4_sm100_expert_gate_up": ExpertGateUp,
     "nml_nvfp4_sm100_expert_down": ExpertDown,

@@ -266,6 +266,83 @@ extern "C" int32_t nml_nvfp4_sm100_linear(const NmlSm100Linear* request, char* e
   return launch_linear_simt(args, *device, error_message, error_message_capacity);
 }
 
+extern "C" int32_t nml_nvfp4_sm100_linear_qkv(const NmlSm100LinearQkv* request,
+                                              char* error_message,
+                                              size_t error_message_capacity) {
+  if (request == nullptr || request->struct_size < sizeof(NmlSm100LinearQkv)) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "truncated NVFP4 QKV request", error_message,
+                error_message_capacity);
+  }
+  bool valid = request->activation != nullptr && request->stream != nullptr &&
+               fits_i32(request->rows) && fits_i32(request->inputs);
+  int64_t total_outputs = 0;
+  for (int i = 0; i < 3; ++i) {
+    valid = valid && request->payload[i] != nullptr && request->block_scales[i] != nullptr &&
+            request->global_scale[i] != nullptr && request->output[i] != nullptr &&
+            fits_i32(request->outputs[i]);
+    total_outputs += request->outputs[i];
+  }
+  if (!valid || !fits_i32(total_outputs)) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "invalid NVFP4 QKV request", error_message,
+                error_message_capacity);
+  }
+  if (!valid_dtype(request->dtype)) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "NVFP4 QKV supports F16 and BF16 only", error_message,
+                error_message_capacity);
+  }
+  const DeviceInfo* device = current_device(error_message, error_message_capacity);
+  if (device == nullptr) return NML_SM100_LAUNCH_FAILURE;
+  LinearArgs args;
+  args.activation = request->activation;
+  args.payload = request->payload[0];
+  args.block_scales = request->block_scales[0];
+  args.global_scale = request->global_scale[0];
+  args.bias = request->bias[0];
+  args.output = request->output[0];
+  args.stream = static_cast<cudaStream_t>(request->stream);
+  args.rows = static_cast<int>(request->rows);
+  args.outputs = static_cast<int>(request->outputs[0]);
+  args.inputs = static_cast<int>(request->inputs);
+  args.dtype = request->dtype;
+  args.extra_projections = 2;
+  for (int i = 0; i < 2; ++i) {
+    args.extra[i] = {request->payload[i + 1], request->block_scales[i + 1],
+                     request->global_scale[i + 1], request->bias[i + 1], request->output[i + 1],
+                     static_cast<int>(request->outputs[i + 1])};
+  }
+  const int policy = get_kernel_policy();
+  if (policy != 1 && linear_umma_supported(args)) {
+    return launch_linear_umma(args, *device, error_message, error_message_capacity);
+  }
+  // one launch per projection
+  for (int i = 0; i < 3; ++i) {
+    LinearArgs one;
+    one.activation = request->activation;
+    one.payload = request->payload[i];
+    one.block_scales = request->block_scales[i];
+    one.global_scale = request->global_scale[i];
+    one.bias = request->bias[i];
+    one.output = request->output[i];
+    one.stream = args.stream;
+    one.rows = args.rows;
+    one.outputs = static_cast<int>(request->outputs[i]);
+    one.inputs = args.inputs;
+    one.dtype = args.dtype;
+    int32_t rc;
+    if (policy != 1 && linear_umma_supported(one)) {
+      rc = launch_linear_umma(one, *device, error_message, error_message_capacity);
+    } else if (policy >= 2) {
+      return fail(NML_SM100_INVALID_ARGUMENT,
+                  "the tcgen05 linear kernel was forced but does not support this shape",
+                  error_message, error_message_capacity);
+    } else {
+      rc = launch_linear_simt(one, *device, error_message, error_message_capacity);
+    }
+    if (rc != NML_SM100_OK) return rc;
+  }
+  return NML_SM100_OK;
+}
+
 extern "C" int32_t nml_nvfp4_sm100_embedding(const NmlSm100Embedding* request,
                                              char* error_message,
                                              size_t error_message_capacity) {

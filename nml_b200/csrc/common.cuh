@@ -115,6 +115,17 @@ struct LinearArgs {
   cudaStream_t stream;
   int rows, outputs, inputs;
   int dtype;
+  // Fused projections that share the activation (Q/K/V): further weights after the first.
+  struct Projection {
+    const uint8_t* payload;
+    const uint8_t* block_scales;
+    const float* global_scale;
+    const void* bias;
+    void* output;
+    int outputs;
+  };
+  int extra_projections = 0;  // 0..2
+  Projection extra[2] = {};
 };
 
 int32_t launch_linear_simt(const LinearArgs& args, const DeviceInfo& device, char* message,

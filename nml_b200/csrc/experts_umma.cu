@@ -86,8 +86,8 @@ int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* me
   const int64_t max_units = slot_tiles * p.n_tiles;
   const unsigned grid =
       static_cast<unsigned>(max_units < device.sm_count ? max_units : device.sm_count);
-  kernel<<<grid, launch_threads<DG, MI, XTMA>(), smem_bytes, args.stream>>>(tmap_payload, tmap_x,
-                                                                            p);
+  kernel<<<grid, launch_threads<DG, MI, XTMA>(), smem_bytes, args.stream>>>(
+      tmap_payload, tmap_x, p, tmap_payload, tmap_payload);
   return launch_result(message, capacity);
 }
 

@@ -25,10 +25,17 @@ int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* me
   const int scale_buffer_bytes = (WT || SB) ? ((args.inputs / 16 * kTileN + 127) / 128) * 128 : 0;
   const int smem_bytes = L::kSmemBytes + 2 * scale_buffer_bytes;
   if (smem_bytes > kSmemBudget) return kDoesNotFit;
-  CUtensorMap tmap_payload, tmap_x;
+  CUtensorMap tmap_payload, tmap_x, tmap_extra[2];
   if (!encode_payload_map<KS>(&tmap_payload, args.payload, args.outputs, args.inputs) ||
       !encode_activation_map<T>(&tmap_x, args.activation, args.rows, args.inputs, BM, KS)) {
     return fail(NML_SM100_LAUNCH_FAILURE, "tensor map encoding failed", message, capacity);
+  }
+  tmap_extra[0] = tmap_extra[1] = tmap_payload;
+  for (int i = 0; i < args.extra_projections; ++i) {
+    if (!encode_payload_map<KS>(&tmap_extra[i], args.extra[i].payload, args.extra[i].outputs,
+                                args.inputs)) {
+      return fail(NML_SM100_LAUNCH_FAILURE, "tensor map encoding failed", message, capacity);
+    }
   }
   Params p = {};
   p.block_scales = args.block_scales;
@@ -40,12 +47,20 @@ int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* me
   p.M = args.rows;
   p.N = args.outputs;
   p.K = args.inputs;
+  p.segments = 1 + args.extra_projections;
+  p.segment[0] = {args.block_scales, args.global_scale, args.bias, args.output, args.outputs, 0};
   p.n_tiles = (args.outputs + kTileN - 1) / kTileN;
+  int64_t weight_bytes = static_cast<int64_t>(args.outputs) * (args.inputs / 2);
+  for (int i = 0; i < args.extra_projections; ++i) {
+    const LinearArgs::Projection& e = args.extra[i];
+    p.segment[1 + i] = {e.block_scales, e.global_scale, e.bias, e.output, e.outputs, p.n_tiles};
+    p.n_tiles += (e.outputs + kTileN - 1) / kTileN;
+    weight_bytes += static_cast<int64_t>(e.outputs) * (args.inputs / 2);
+  }
   p.m_tiles = (args.rows + BM - 1) / BM;
   p.k_steps = args.inputs / kTileK;
   // Walk n fastest when the packed weights stay L2-resident (activations stream once);
   // otherwise walk m fastest so the large weight tensor streams once.
-  const int64_t weight_bytes = static_cast<int64_t>(args.outputs) * (args.inputs / 2);
   p.n_fastest = weight_bytes <= (32ll << 20) ? 1 : 0;
   p.output = args.output;
   p.status = device.status_word;
@@ -63,8 +78,8 @@ int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* me
   }
   const int64_t tiles = static_cast<int64_t>(p.n_tiles) * p.m_tiles;
   const unsigned grid = static_cast<unsigned>(tiles < device.sm_count ? tiles : device.sm_count);
-  kernel<<<grid, launch_threads<DG, MI, true>(), smem_bytes, args.stream>>>(tmap_payload, tmap_x,
-                                                                            p);
+  kernel<<<grid, launch_threads<DG, MI, true>(), smem_bytes, args.stream>>>(
+      tmap_payload, tmap_x, p, tmap_extra[0], tmap_extra[1]);
   note_linear_kernel(WT ? (AFMT == kAf16      ? "umma_tmem_weights_af16"
                            : AFMT == kAbf16Lut ? "umma_tmem_weights_abf16_lut"
                                                : "umma_tmem_weights_abf16")
@@ -114,14 +129,20 @@ int32_t launch_for_rows(const LinearArgs& args, const DeviceInfo& device, char* 
                           : policy >= 100  ? policy - 100
                                            : 0;
   const bool table_decode = policy != 4 && policy < 2000;
-  const bool bulk_scales_legal = args.outputs % 4 == 0 &&
-                                 reinterpret_cast<uintptr_t>(args.block_scales) % 16 == 0;
+  bool bulk_scales_legal = args.outputs % 4 == 0 &&
+                           reinterpret_cast<uintptr_t>(args.block_scales) % 16 == 0;
+  int total_outputs = args.outputs;
+  for (int i = 0; i < args.extra_projections; ++i) {
+    bulk_scales_legal = bulk_scales_legal && args.extra[i].outputs % 4 == 0 &&
+                        reinterpret_cast<uintptr_t>(args.extra[i].block_scales) % 16 == 0;
+    total_outputs += args.extra[i].outputs;
+  }
   const bool tmem_weights = policy != 3 && (policy < 1000 || policy >= 2000) && bulk_scales_legal;
   if (tmem_weights && AFMT == kAbf16 && table_decode) {
     // bf16 operands through the byte table (32 KB of shared memory; slightly shallower rings)
     int32_t rc = kDoesNotFit;
     switch (forced_rows ? forced_rows
-                        : choose_tile_rows(args.rows, args.outputs, device.sm_count, true)) {
+                        : choose_tile_rows(args.rows, total_outputs, device.sm_count, true)) {
       case 16:
         rc = launch_config<16, 4, 6, 4, 8, 3, 2, 8, true, kAbf16Lut, T>(args, device, message,
                                                                         capacity);
@@ -150,7 +171,7 @@ int32_t launch_for_rows(const LinearArgs& args, const DeviceInfo& device, char* 
   if (tmem_weights) {
     int32_t rc = kDoesNotFit;
     switch (forced_rows ? forced_rows
-                        : choose_tile_rows(args.rows, args.outputs, device.sm_count, true)) {
+                        : choose_tile_rows(args.rows, total_outputs, device.sm_count, true)) {
       case 16:
         rc = launch_config<16, 4, 6, 4, 8, 3, 2, 8, true, AFMT, T>(args, device, message, capacity);
         break;
@@ -175,7 +196,7 @@ int32_t launch_for_rows(const LinearArgs& args, const DeviceInfo& device, char* 
   }
   switch (forced_rows && forced_rows != 192 && forced_rows != 257
               ? forced_rows
-              : choose_tile_rows(args.rows, args.outputs, device.sm_count, false)) {
+              : choose_tile_rows(args.rows, total_outputs, device.sm_count, false)) {
     case 16:
       return launch_config<16, 4, 5, 4, 4, 3, 1, 8, false, AFMT, T>(args, device, message,
                                                                     capacity);
@@ -205,9 +226,14 @@ int32_t launch_for_rows(const LinearArgs& args, const DeviceInfo& device, char* 
 }  // namespace
 
 bool linear_umma_supported(const LinearArgs& args) {
-  return args.inputs % kTileK == 0 && reinterpret_cast<uintptr_t>(args.payload) % 16 == 0 &&
-         reinterpret_cast<uintptr_t>(args.activation) % 16 == 0 &&
-         reinterpret_cast<uintptr_t>(args.block_scales) % 4 == 0;
+  bool ok = args.inputs % kTileK == 0 && reinterpret_cast<uintptr_t>(args.payload) % 16 == 0 &&
+            reinterpret_cast<uintptr_t>(args.activation) % 16 == 0 &&
+            reinterpret_cast<uintptr_t>(args.block_scales) % 4 == 0;
+  for (int i = 0; i < args.extra_projections; ++i) {
+    ok = ok && reinterpret_cast<uintptr_t>(args.extra[i].payload) % 16 == 0 &&
+         reinterpret_cast<uintptr_t>(args.extra[i].block_scales) % 4 == 0;
+  }
+  return ok;
 }
 
 int32_t launch_linear_umma(const LinearArgs& args, const DeviceInfo& device, char* message,

@@ -148,6 +148,18 @@ struct Params {
   const int32_t* expert_offset;
   const void* routing_weights;
   int assignments, schedule_blocks, experts, top_k;
+  // dense: up to three weights that share the activation operand (fused Q/K/V); a plain
+  // linear is one segment.  Weight tile t belongs to the last segment with tile_begin <= t.
+  struct Segment {
+    const uint8_t* block_scales;
+    const float* global_scale;
+    const void* bias;
+    void* output;
+    int outputs;     // rows of this weight = output columns
+    int tile_begin;  // first weight tile of the segment
+  };
+  Segment segment[3];
+  int segments;
   int* status;
   int scale_buffer_bytes;  // WT: bytes of one scale buffer (128 rows x K / 16, 128-aligned)
   DecodeConstants decode;  // see DecodeConstants; filled by fill_decode_constants()
@@ -395,8 +407,11 @@ __device__ __forceinline__ Unit get_unit(const Params& p, const Groups* groups, 
       n_tile = index / p.m_tiles;
       m_tile = index - n_tile * p.m_tiles;
     }
-    u.expert = 0;
-    u.n0 = n_tile * kTileN;
+    int segment = 0;
+    if (p.segments > 1 && n_tile >= p.segment[1].tile_begin) segment = 1;
+    if (p.segments > 2 && n_tile >= p.segment[2].tile_begin) segment = 2;
+    u.expert = segment;  // dense: index of the weight the tile belongs to
+    u.n0 = (n_tile - p.segment[segment].tile_begin) * kTileN;
     u.weight_row0 = u.n0;
     u.m0 = m_tile * BM;
     u.rows = min(BM, p.M - u.m0);
@@ -470,7 +485,9 @@ template <int BM, int KS, int PS, int XS, int WB, int DG, int MI, int PA, bool W
           typename T, int MODE, bool XTMA, bool SB = false>
 __global__ void __launch_bounds__(launch_threads<DG, MI, XTMA>(), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
-            const __grid_constant__ CUtensorMap tmap_x, const Params p) {
+            const __grid_constant__ CUtensorMap tmap_x, const Params p,
+            const __grid_constant__ CUtensorMap tmap_payload1,
+            const __grid_constant__ CUtensorMap tmap_payload2) {
   constexpr bool GROUPED = MODE != kDense;
   constexpr int kGatherWarp0 = Roles<DG>::kGatherWarp0;  // first warp of the X side
   constexpr int kMmaWarpB = XTMA ? kGatherWarp0 + 1 : kGatherWarp0 + kGatherWarps;
@@ -517,6 +534,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
   static_assert((2 * PS + 2 * XS + 2 * WB + 8) * 8 + 8 <= L::kBarrierBytes, "barrier area");
   Groups* groups = reinterpret_cast<Groups*>(smem + L::kBarrierOffset + L::kBarrierBytes);
   uint64_t* x_free = kSharedEmpty ? empty_w : empty_x;
+  // Per-unit weight operands: in dense mode they come from the unit's segment.
+  auto scale_base = [&](const Unit& u) -> const uint8_t* {
+    return GROUPED ? p.block_scales : p.segment[u.expert].block_scales;
+  };
+  auto weight_rows = [&](const Unit& u) -> int {
+    return GROUPED ? p.weight_rows_total : p.segment[u.expert].outputs;
+  };
+  auto payload_map = [&](const Unit& u) -> const CUtensorMap* {
+    if constexpr (!GROUPED) {
+      if (u.expert == 1) return &tmap_payload1;
+      if (u.expert == 2) return &tmap_payload2;
+    }
+    return &tmap_payload;
+  };
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -544,7 +575,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     mbar_fence_init();
   }
   if (warp == kProducerWarp) {
-    if (lane == 0) tma_prefetch_descriptor(&tmap_payload);
+    if (lane == 0) {
+      tma_prefetch_descriptor(&tmap_payload);
+      if (!GROUPED && p.segments > 1) tma_prefetch_descriptor(&tmap_payload1);
+      if (!GROUPED && p.segments > 2) tma_prefetch_descriptor(&tmap_payload2);
+    }
     if constexpr (GROUPED) build_groups(groups, p, BM, lane);
   }
   if (warp == kMmaWarp) {
@@ -632,11 +667,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         const int b = local & 1;
         if (!wait(&empty_scale[b], ((local >> 1) & 1) ^ 1u, kSiteProducerScale)) break;
         if (lane == 0) {
-          const int rows = min(kTileN, p.weight_rows_total - u.weight_row0);
+          const int rows = min(kTileN, weight_rows(u) - u.weight_row0);
           const uint32_t bytes = static_cast<uint32_t>(rows * p.scale_width);
           mbar_arrive_expect_tx(&full_scale[b], bytes);
           bulk_load(scale_buffer(b),
-                    p.block_scales + static_cast<int64_t>(u.weight_row0) * p.scale_width, bytes,
+                    scale_base(u) + static_cast<int64_t>(u.weight_row0) * p.scale_width, bytes,
                     &full_scale[b]);
         }
       }
@@ -652,7 +687,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         NML_PROF_END(0);
         if (lane == 0) {
           mbar_arrive_expect_tx(&full_p[ps.index], L::kPayloadBytes);
-          tma_load_2d(payload_tile(ps.index), &tmap_payload, &full_p[ps.index], rs * KS * 32,
+          tma_load_2d(payload_tile(ps.index), payload_map(u), &full_p[ps.index], rs * KS * 32,
                       u.weight_row0);
         }
         if constexpr (!kBulk) {
@@ -664,9 +699,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
 #pragma unroll
               for (int i = 0; i < kTileN / 32; ++i) {
                 const int row = lane + 32 * i;
-                const int n = min(u.weight_row0 + row, p.weight_rows_total - 1);
+                const int n = min(u.weight_row0 + row, weight_rows(u) - 1);
                 cp_async_4(scale_tile(ps.index) + row * (4 * KS) + j * 4,
-                           p.block_scales + static_cast<int64_t>(n) * p.scale_width + k_step * 4);
+                           scale_base(u) + static_cast<int64_t>(n) * p.scale_width + k_step * 4);
               }
             }
           }
@@ -870,9 +905,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
   } else if (warp < kDecodeWarp0) {
     // ------------------------------------------------------------------ epilogue
     const int quarter = warp & 3;  // TMEM lanes a warp may read: 32 * (warp % 4)
-    const float g = __ldg(p.global_scale) * (AFMT == kAbf16 ? 128.0f : 1.0f);
+    constexpr float kDecodeFactor = AFMT == kAbf16 ? 128.0f : 1.0f;
+    float g = GROUPED ? __ldg(p.global_scale) * kDecodeFactor : 0.0f;
     T* out = static_cast<T*>(p.output);
     const T* bias = static_cast<const T*>(p.bias);
+    int out_columns = p.N;
     const int row = quarter * 32 + lane;  // row of the weight tile this thread reads
     int local = 0;
     NML_PROF_DECL
@@ -917,8 +954,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         }
         __syncwarp();
       }
+      if constexpr (!GROUPED) {
+        const Params::Segment& segment = p.segment[u.expert];
+        g = __ldg(segment.global_scale) * kDecodeFactor;
+        out = static_cast<T*>(segment.output);
+        bias = static_cast<const T*>(segment.bias);
+        out_columns = segment.outputs;
+      }
       const int n = u.n0 + row;  // output column (dense, down) or weight row in the expert
-      const bool n_ok = n < (MODE == kGateUp ? p.rows_per_expert : p.N);
+      const bool n_ok = n < (MODE == kGateUp ? p.rows_per_expert : out_columns);
       float bias_value = 0.0f;
       if (bias != nullptr && n_ok) {
         bias_value = Elem<T>::load(
@@ -962,7 +1006,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
             for (int j = 0; j < kChunk; ++j) {
               const int m = u.m0 + c + j;
               if (c + j < u.rows) {
-                out[static_cast<int64_t>(m) * p.N + n] =
+                out[static_cast<int64_t>(m) * out_columns + n] =
                     Elem<T>::store(fmaf(__uint_as_float(v[j]), g, bias_value));
               }
             }

@@ -134,9 +134,42 @@ def linear(input: torch.Tensor, weight: NvFp4Parameter, bias: torch.Tensor | Non
 
 def linear_qkv(input: torch.Tensor, query_weight: NvFp4Parameter, query_bias,
                key_weight: NvFp4Parameter, key_bias, value_weight: NvFp4Parameter, value_bias):
-    """Three projections over one activation (crates/nml-ir/src/lib.rs:4884-4928)."""
-    return (linear(input, query_weight, query_bias), linear(input, key_weight, key_bias),
-            linear(input, value_weight, value_bias))
+    """Three projections over one activation (crates/nml-ir/src/lib.rs:4884-4928), one launch
+    (``nml_nvfp4_sm100_linear_qkv``).  Projections of different dtype or width cannot share a
+    launch and are evaluated one by one, as the reference does (nvfp4_backend.rs:243-268)."""
+    weights = (query_weight, key_weight, value_weight)
+    biases = (query_bias, key_bias, value_bias)
+    if input.dim() == 0:
+        raise ValueError("linear input requires at least one dimension")
+    same = all(len(w.shape) == 2 and w.shape[1] == query_weight.shape[1] and
+               w.dtype == input.dtype for w in weights)
+    if not same:
+        return tuple(linear(input, w, b) for w, b in zip(weights, biases))
+    inputs = query_weight.shape[1]
+    if input.shape[-1] != inputs:
+        raise ValueError(
+            f"linear input extent {input.shape[-1]} does not match rows of {inputs} values")
+    for w, b in zip(weights, biases):
+        if b is not None and (tuple(b.shape) != (w.shape[0],) or b.dtype != input.dtype):
+            raise ValueError("NVFP4 linear bias must be a length-N activation vector")
+        _require_cuda(w.payload, w.block_scales, w.global_scale, b)
+    _require_cuda(input)
+    rows = input.numel() // inputs
+    if rows <= 0:
+        raise ValueError("NVFP4 linear row extent must be positive")
+    outs = tuple(torch.empty(tuple(input.shape[:-1]) + (w.shape[0],), dtype=input.dtype,
+                             device=input.device) for w in weights)
+    three = _abi._vp * 3
+    request = _abi.LinearQkv(
+        activation=_ptr(input), payload=three(*[_ptr(w.payload) for w in weights]),
+        block_scales=three(*[_ptr(w.block_scales) for w in weights]),
+        global_scale=three(*[_ptr(w.global_scale) for w in weights]),
+        bias=three(*[_ptr(b) for b in biases]), output=three(*[_ptr(o) for o in outs]),
+        stream=_stream(input), rows=rows,
+        outputs=(_abi._i64 * 3)(*[w.shape[0] for w in weights]), inputs=inputs,
+        dtype=_code(input.dtype))
+    _abi.call("nml_nvfp4_sm100_linear_qkv", request)
+    return outs
 
 
 def token_embedding(weight: NvFp4Parameter, indices: torch.Tensor,

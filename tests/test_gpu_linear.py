@@ -141,3 +141,43 @@ def test_config0_single_linear():
     # BASELINE config 0: X bf16 [16, 2880], W [5760, 2880]
     from nml_b200 import _abi
     run_linear(16, 2880, 5760, oracle.BF16, _abi.POLICY_AUTO, seed=7)
+
+
+QKV_CASES = [(1, 2880, (4096, 512, 512), True), (8, 2880, (4096, 512, 512), False),
+             (64, 2880, (4096, 512, 512), True), (300, 2880, (4096, 512, 512), True),
+             (16, 256, (130, 64, 200), True),     # odd output counts: shared-memory weight ring
+             (5, 80, (33, 16, 7), True)]          # K not a multiple of 64: three SIMT launches
+
+
+@pytest.mark.parametrize("dtype", [oracle.BF16, oracle.F16])
+@pytest.mark.parametrize("M,K,outputs,with_bias", QKV_CASES)
+def test_fused_qkv_matches_three_linears_and_oracle(M, K, outputs, with_bias, dtype):
+    # crates/nml-ir/src/nvfp4_backend.rs:221-380: Q, K and V share the activation; every
+    # projection has its own weight triple, global scale and bias
+    from nml_b200 import ops, _abi
+    import gpu_util as gu
+    x_bits, x32 = make_activation(900 + M, (M, K), dtype=dtype)
+    x = gu.to_device_bits(x_bits, dtype)
+    weights, biases, triples, biases32 = [], [], [], []
+    for i, n in enumerate(outputs):
+        triple = make_weight(910 + i + n, (n, K))
+        triples.append(triple)
+        weights.append(gu.parameter(f"w{i}", triple, K, dtype))
+        if with_bias and i != 1:  # the key projection goes without a bias
+            bits, b32 = make_activation(920 + i, (n,), std=0.5, dtype=dtype)
+            biases.append(gu.to_device_bits(bits, dtype))
+            biases32.append(b32)
+        else:
+            biases.append(None)
+            biases32.append(None)
+    fused = ops.linear_qkv(x, weights[0], biases[0], weights[1], biases[1], weights[2], biases[2])
+    torch.cuda.synchronize()
+    assert _abi.device_status(0x1) == 0
+    for i in range(3):
+        single = ops.linear(x, weights[i], biases[i])
+        torch.cuda.synchronize()
+        if M <= 64:  # same tile height either way: the same instruction stream per row
+            assert torch.equal(fused[i].view(torch.int16), single.view(torch.int16)), i
+        expected = oracle.linear(x32, *triples[i], biases32[i])
+        gu.assert_gemm_close(gu.device_f32(fused[i]), expected, f"qkv projection {i} M={M}")
+    assert _abi.device_status(0x1) == 0
