@@ -402,7 +402,9 @@ int32_t nml_nvfp4_sm100_device_status(void *stream, int32_t clear, int32_t *stat
 
 /* Kernel selection override for experiments and tests: 0 = automatic, 1 = force the
  * portable SIMT kernels, 2 = force the tcgen05 kernels where the shape allows, 3 = as 2 but
- * keep the decoded weight tiles in a shared-memory ring instead of tensor memory.
+ * keep the decoded weight tiles in a shared-memory ring instead of tensor memory, 4 = bf16
+ * operands by bit placement instead of the byte table, 5 = never cut K over a cluster
+ * (values from 100 up force tile heights, see linear_umma.cu).
  * Process-wide; returns the previous value. */
 int32_t nml_nvfp4_sm100_set_kernel_policy(int32_t policy);
 

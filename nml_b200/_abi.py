@@ -28,6 +28,8 @@ POLICY_AUTO = 0
 POLICY_SIMT = 1
 POLICY_UMMA = 2
 POLICY_UMMA_SMEM = 3  # tcgen05 with the decoded-weight ring in shared memory
+POLICY_NO_TABLE_DECODE = 4  # bf16 operands by bit placement instead of the byte table
+POLICY_NO_SPLIT_K = 5  # never cut K over a cluster
 
 _vp = ctypes.c_void_p
 _i64 = ctypes.c_int64

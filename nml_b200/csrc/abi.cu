@@ -27,6 +27,11 @@ std::atomic<int> g_device_ready[kMaxDevices];
 }  // namespace
 
 int get_kernel_policy() { return g_kernel_policy.load(std::memory_order_relaxed); }
+// 2 and 3 (and the tile-forcing values from 100 up) demand the tcgen05 kernels; 4 and 5 only
+// switch options of those kernels off.
+static bool policy_forces_tensor_cores(int policy) {
+  return policy == 2 || policy == 3 || policy >= 100;
+}
 void note_linear_kernel(const char* name, int tile_rows) {
   t_last_linear_kernel = name;
   t_last_linear_tile_rows = tile_rows;
@@ -124,7 +129,7 @@ int32_t dispatch_experts(const ExpertArgs& args, const DeviceInfo& device, char*
   if (policy != 1 && experts_umma_supported(args)) {
     return launch_experts_umma(args, device, message, capacity);
   }
-  if (policy >= 2) {
+  if (policy_forces_tensor_cores(policy)) {
     return fail(NML_SM100_INVALID_ARGUMENT,
                 "the tcgen05 expert kernel was forced but does not support this shape", message,
                 capacity);
@@ -258,7 +263,7 @@ extern "C" int32_t nml_nvfp4_sm100_linear(const NmlSm100Linear* request, char* e
   if (policy != 1 && linear_umma_supported(args)) {
     return launch_linear_umma(args, *device, error_message, error_message_capacity);
   }
-  if (policy >= 2) {
+  if (policy_forces_tensor_cores(policy)) {
     return fail(NML_SM100_INVALID_ARGUMENT,
                 "the tcgen05 linear kernel was forced but does not support this shape",
                 error_message, error_message_capacity);
@@ -331,7 +336,7 @@ extern "C" int32_t nml_nvfp4_sm100_linear_qkv(const NmlSm100LinearQkv* request,
     int32_t rc;
     if (policy != 1 && linear_umma_supported(one)) {
       rc = launch_linear_umma(one, *device, error_message, error_message_capacity);
-    } else if (policy >= 2) {
+    } else if (policy_forces_tensor_cores(policy)) {
       return fail(NML_SM100_INVALID_ARGUMENT,
                   "the tcgen05 linear kernel was forced but does not support this shape",
                   error_message, error_message_capacity);

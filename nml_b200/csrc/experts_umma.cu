@@ -70,6 +70,7 @@ int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* me
   p.top_k = args.experts_per_token;
   p.status = device.status_word;
   p.scale_buffer_bytes = scale_buffer_bytes;
+  p.split_k = 1;
   fill_decode_constants(&p.decode);
 #ifdef NML_SM100_PROFILE
   p.knockout = std::getenv("NML_SM100_KNOCKOUT") ? std::atoi(std::getenv("NML_SM100_KNOCKOUT")) : 0;

@@ -23,7 +23,29 @@ int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* me
                       size_t capacity) {
   using L = KernelLayout<BM, KS, PS, XS, WB, WT, AFMT, kDense, SB>;
   const int scale_buffer_bytes = (WT || SB) ? ((args.inputs / 16 * kTileN + 127) / 128) * 128 : 0;
-  const int smem_bytes = L::kSmemBytes + 2 * scale_buffer_bytes;
+  // Few tiles and few rows (decode shapes of the 2880-class weights): cut K over a cluster so
+  // that more SMs stream the weights.  One unit per cluster, at least 8 K steps per CTA.
+  int total_tiles = (args.outputs + kTileN - 1) / kTileN;
+  for (int i = 0; i < args.extra_projections; ++i) {
+    total_tiles += (args.extra[i].outputs + kTileN - 1) / kTileN;
+  }
+  int split_k = 1;
+  if (BM <= 32 && args.rows <= BM && get_kernel_policy() != 5) {
+    const int k_steps = args.inputs / kTileK;
+    while (split_k < 4 && total_tiles * (split_k + 1) <= device.sm_count &&
+           k_steps / (split_k + 1) >= 8) {
+      ++split_k;
+    }
+  }
+  int smem_bytes = L::kSmemBytes + 2 * scale_buffer_bytes;
+  if (split_k > 1) {
+    const int with_partials = smem_bytes + (split_k - 1) * kTileN * BM * 4;
+    if (with_partials <= kSmemBudget) {
+      smem_bytes = with_partials;
+    } else {
+      split_k = 1;
+    }
+  }
   if (smem_bytes > kSmemBudget) return kDoesNotFit;
   CUtensorMap tmap_payload, tmap_x, tmap_extra[2];
   if (!encode_payload_map<KS>(&tmap_payload, args.payload, args.outputs, args.inputs) ||
@@ -47,6 +69,7 @@ int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* me
   p.M = args.rows;
   p.N = args.outputs;
   p.K = args.inputs;
+  p.split_k = split_k;
   p.segments = 1 + args.extra_projections;
   p.segment[0] = {args.block_scales, args.global_scale, args.bias, args.output, args.outputs, 0};
   p.n_tiles = (args.outputs + kTileN - 1) / kTileN;
@@ -72,14 +95,33 @@ int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* me
 
   auto kernel = gemm_kernel<BM, KS, PS, XS, WB, DG, MI, PA, WT, AFMT, T, kDense, true, SB>;
   static bool configured[64] = {};
-  if (!reserve_smem(kernel, (WT || SB) ? kSmemBudget : L::kSmemBytes, device.device, configured)) {
+  if (!reserve_smem(kernel, kSmemBudget, device.device, configured)) {
     return fail(NML_SM100_LAUNCH_FAILURE, "cannot reserve shared memory for the tcgen05 linear",
                 message, capacity);
   }
   const int64_t tiles = static_cast<int64_t>(p.n_tiles) * p.m_tiles;
   const unsigned grid = static_cast<unsigned>(tiles < device.sm_count ? tiles : device.sm_count);
-  kernel<<<grid, launch_threads<DG, MI, true>(), smem_bytes, args.stream>>>(
-      tmap_payload, tmap_x, p, tmap_extra[0], tmap_extra[1]);
+  if (split_k > 1) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(static_cast<unsigned>(tiles) * split_k);
+    config.blockDim = dim3(launch_threads<DG, MI, true>());
+    config.dynamicSmemBytes = smem_bytes;
+    config.stream = args.stream;
+    cudaLaunchAttribute cluster;
+    cluster.id = cudaLaunchAttributeClusterDimension;
+    cluster.val.clusterDim.x = split_k;
+    cluster.val.clusterDim.y = 1;
+    cluster.val.clusterDim.z = 1;
+    config.attrs = &cluster;
+    config.numAttrs = 1;
+    if (cudaLaunchKernelEx(&config, kernel, tmap_payload, tmap_x, p, tmap_extra[0],
+                           tmap_extra[1]) != cudaSuccess) {
+      return launch_result(message, capacity);
+    }
+  } else {
+    kernel<<<grid, launch_threads<DG, MI, true>(), smem_bytes, args.stream>>>(
+        tmap_payload, tmap_x, p, tmap_extra[0], tmap_extra[1]);
+  }
   note_linear_kernel(WT ? (AFMT == kAf16      ? "umma_tmem_weights_af16"
                            : AFMT == kAbf16Lut ? "umma_tmem_weights_abf16_lut"
                                                : "umma_tmem_weights_abf16")

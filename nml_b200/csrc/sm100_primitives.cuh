@@ -195,6 +195,55 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                : "memory");
 }
 
+// ---- thread-block clusters ---------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  return rank;
+}
+
+// Every thread of every CTA of the cluster; orders earlier writes before later reads.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Address of `local` (a shared-memory address of this CTA) in the CTA of rank `rank`.
+__device__ __forceinline__ uint32_t cluster_map_shared(uint32_t local, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+  return remote;
+}
+
+__device__ __forceinline__ void cluster_store_f32x4(uint32_t remote, float a, float b, float c,
+                                                    float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(remote), "f"(a), "f"(b),
+               "f"(c), "f"(d)
+               : "memory");
+}
+
+// Arrival on an mbarrier of another CTA of the cluster; releases this thread's earlier
+// (remote) stores at cluster scope.
+__device__ __forceinline__ void cluster_mbar_arrive(uint32_t remote_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar)
+               : "memory");
+}
+
+// try_wait that acquires at cluster scope (pairs with cluster_mbar_arrive).
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
 // ---- warp-uniform issue -------------------------------------------------------
 // The forms below are executed by every lane of a converged warp; one elected lane issues
 // the instruction.  Code that reaches a tcgen05.mma under `if (lane == 0)` is divergent to

@@ -160,6 +160,10 @@ struct Params {
   };
   Segment segment[3];
   int segments;
+  // dense, few tiles: the K range of a unit is cut over the `split_k` CTAs of a cluster (one
+  // unit per cluster); ranks > 0 hand their f32 partial tile to rank 0 through distributed
+  // shared memory, rank 0 adds them in rank order (ascending K) and finishes the unit.
+  int split_k;  // 1: no split
   int* status;
   int scale_buffer_bytes;  // WT: bytes of one scale buffer (128 rows x K / 16, 128-aligned)
   DecodeConstants decode;  // see DecodeConstants; filled by fill_decode_constants()
@@ -518,6 +522,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
   auto payload_tile = [&](int r) { return smem + L::kPOffset + r * L::kPBytes; };
   auto scale_tile = [&](int r) { return payload_tile(r) + L::kPayloadBytes; };
   auto scale_buffer = [&](int b) { return smem + L::kScaleBufferOffset + b * p.scale_buffer_bytes; };
+  // split K, rank 0: f32 partial tiles [128 x BM] of ranks 1.. behind the scale buffers
+  auto partial_tile = [&](int i) {
+    return reinterpret_cast<float*>(smem + L::kScaleBufferOffset + 2 * p.scale_buffer_bytes +
+                                    i * (kTileN * BM * 4));
+  };
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarrierOffset);
   uint64_t* full_p = bars;                 // [PS]
   uint64_t* empty_p = full_p + PS;         // [PS]
@@ -529,9 +538,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
   uint64_t* tmem_empty = tmem_full + 2;    // [2]
   uint64_t* full_scale = tmem_empty + 2;   // [2] (WT)
   uint64_t* empty_scale = full_scale + 2;  // [2] (WT)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(empty_scale + 2);
+  uint64_t* partial_full = empty_scale + 2;  // [1] (split K, rank 0: partial tiles have landed)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(partial_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  static_assert((2 * PS + 2 * XS + 2 * WB + 8) * 8 + 8 <= L::kBarrierBytes, "barrier area");
+  static_assert((2 * PS + 2 * XS + 2 * WB + 9) * 8 + 8 <= L::kBarrierBytes, "barrier area");
   Groups* groups = reinterpret_cast<Groups*>(smem + L::kBarrierOffset + L::kBarrierBytes);
   uint64_t* x_free = kSharedEmpty ? empty_w : empty_x;
   // Per-unit weight operands: in dense mode they come from the unit's segment.
@@ -571,6 +581,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       mbar_init(&full_scale[a], 1);
       mbar_init(&empty_scale[a], 4 * DG);
     }
+    mbar_init(partial_full, p.split_k > 1 ? (p.split_k - 1) * kEpilogueWarps : 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -609,7 +620,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const int units = total_units<BM, GROUPED>(p, groups);
-  const int stages = (p.k_steps + KS - 1) / KS;  // per unit, of the P ring and of the X ring
+  // K range of this CTA and the units it walks (split K: one unit per cluster, a K slice per
+  // CTA; otherwise every K step and a persistent walk over the units)
+  int k_begin = 0, k_count = p.k_steps;
+  int first_unit = blockIdx.x, unit_stride = gridDim.x;
+  uint32_t split_rank = 0;
+  const bool split = !GROUPED && p.split_k > 1;
+  if (split) {
+    split_rank = cluster_cta_rank();
+    const int share = p.k_steps / p.split_k, extra = p.k_steps % p.split_k;
+    k_count = share + (static_cast<int>(split_rank) < extra ? 1 : 0);
+    k_begin = static_cast<int>(split_rank) * share + min(static_cast<int>(split_rank), extra);
+    first_unit = blockIdx.x / p.split_k;
+    unit_stride = gridDim.x / p.split_k;
+    // remote arrivals must find initialised barriers
+    cluster_sync_all();
+  }
+  const int stages = (k_count + KS - 1) / KS;  // per unit, of the P ring and of the X ring
 
   // `site` says which wait ran out (diagnostic bits 8.. of the status word).
   auto give_up = [&](int site) {
@@ -657,7 +684,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     int local = 0;
     bool ok = true;
     NML_PROF_DECL
-    for (int index = blockIdx.x; index < units && ok; index += gridDim.x, ++local) {
+    for (int index = first_unit; index < units && ok; index += unit_stride, ++local) {
       const Unit u = get_unit<BM, GROUPED>(p, groups, index);
 #ifdef NML_SM100_DEBUG_WAITS
       wait_position.unit = local;
@@ -687,15 +714,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         NML_PROF_END(0);
         if (lane == 0) {
           mbar_arrive_expect_tx(&full_p[ps.index], L::kPayloadBytes);
-          tma_load_2d(payload_tile(ps.index), payload_map(u), &full_p[ps.index], rs * KS * 32,
-                      u.weight_row0);
+          tma_load_2d(payload_tile(ps.index), payload_map(u), &full_p[ps.index],
+                      (k_begin + rs * KS) * 32, u.weight_row0);
         }
         if constexpr (!kBulk) {
           // block scales: 4 bytes per row and K step (scale rows are not TMA-legal)
 #pragma unroll
           for (int j = 0; j < KS; ++j) {
-            const int k_step = rs * KS + j;
-            if (k_step < p.k_steps) {
+            const int k_step = k_begin + rs * KS + j;
+            if (rs * KS + j < k_count) {
 #pragma unroll
               for (int i = 0; i < kTileN / 32; ++i) {
                 const int row = lane + 32 * i;
@@ -734,7 +761,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       int issued = 0;
       bool ok = true;
       if (lane == 0) tma_prefetch_descriptor(&tmap_x);
-      for (int index = blockIdx.x; index < units && ok; index += gridDim.x) {
+      for (int index = first_unit; index < units && ok; index += unit_stride) {
         const Unit u = get_unit<BM, GROUPED>(p, groups, index);
         for (int rs = 0; rs < stages; ++rs) {
           if (!wait(&x_free[xs.index], xs.phase ^ 1u, kSiteGather)) {
@@ -745,10 +772,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
             // the box always covers KS K steps; columns past K read as zeros
             mbar_arrive_expect_tx(&full_x[xs.index], L::kXStageBytes);
             if constexpr (KS == 1) {
-              tma_load_2d(x_tile(xs.index, 0), &tmap_x, &full_x[xs.index], rs * kTileK, u.m0);
+              tma_load_2d(x_tile(xs.index, 0), &tmap_x, &full_x[xs.index],
+                          (k_begin + rs) * kTileK, u.m0);
             } else {
               // the activation map is a 3-D view [K/64][rows][64]: one box carries KS K steps
-              tma_load_3d(x_tile(xs.index, 0), &tmap_x, &full_x[xs.index], 0, u.m0, rs * KS);
+              tma_load_3d(x_tile(xs.index, 0), &tmap_x, &full_x[xs.index], 0, u.m0,
+                          k_begin + rs * KS);
             }
           }
           __syncwarp();
@@ -799,7 +828,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       const long long prof_start = clock64();
       unsigned long long prof_fine[4] = {0, 0, 0, 0};
 #endif
-      for (int index = blockIdx.x; index < units; index += gridDim.x, ++local) {
+      for (int index = first_unit; index < units; index += unit_stride, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
         NML_PROF_BEGIN();
@@ -828,7 +857,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
           }
 #endif
           NML_PROF_END(1);
-          const int sub_steps = min(KS, p.k_steps - rs * KS);
+          const int sub_steps = min(KS, k_count - rs * KS);
           for (int j = 0; j < sub_steps; ++j, ++step, ++sequence, wb.advance<WB>()) {
             if (MI == 2 && (sequence & 1) != issuer) continue;
             NML_PROF_BEGIN();
@@ -913,7 +942,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     const int row = quarter * 32 + lane;  // row of the weight tile this thread reads
     int local = 0;
     NML_PROF_DECL
-    for (int index = blockIdx.x; index < units; index += gridDim.x, ++local) {
+    for (int index = first_unit; index < units; index += unit_stride, ++local) {
       const Unit u = get_unit<BM, GROUPED>(p, groups, index);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
@@ -983,7 +1012,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         if constexpr (PA > 1) {
           // add the other partial accumulators in index order; a unit with few K steps has
           // touched only the first 4 * k_steps of them
-          const int used = min(PA, p.k_steps * (kTileK / kUmmaK));
+          const int used = min(PA, k_count * (kTileK / kUmmaK));
 #pragma unroll 1
           for (int partial = 1; partial < used; ++partial) {
             uint32_t extra[kChunk];
@@ -1001,6 +1030,39 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         }
         if (c >= u.rows) continue;  // uniform: nothing valid left in this chunk
         if constexpr (MODE == kDense) {
+          if (split) {
+            if (split_rank != 0) {
+              // hand this K slice's partial sums to rank 0 and skip the store
+              const uint32_t local = smem_u32(partial_tile(static_cast<int>(split_rank) - 1)) +
+                                     static_cast<uint32_t>(row * BM + c) * 4u;
+              const uint32_t remote = cluster_map_shared(local, 0);
+#pragma unroll
+              for (int j = 0; j < kChunk; j += 4) {
+                cluster_store_f32x4(remote + j * 4, __uint_as_float(v[j]),
+                                    __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
+                                    __uint_as_float(v[j + 3]));
+              }
+              continue;
+            }
+            if (c == 0) {
+              bool landed = false;
+              for (uint32_t poll = 0; poll < kWaitPolls && !landed; ++poll) {
+                landed = mbar_try_wait_cluster(partial_full, 0);
+              }
+              if (!landed) give_up(kSiteEpilogue);
+            }
+            for (int other = 1; other < p.split_k; ++other) {  // ascending K
+              const float* partial = partial_tile(other - 1) + row * BM + c;
+#pragma unroll
+              for (int j = 0; j < kChunk; j += 4) {
+                const float4 add = *reinterpret_cast<const float4*>(partial + j);
+                v[j] = __float_as_uint(__fadd_rn(__uint_as_float(v[j]), add.x));
+                v[j + 1] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 1]), add.y));
+                v[j + 2] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 2]), add.z));
+                v[j + 3] = __float_as_uint(__fadd_rn(__uint_as_float(v[j + 3]), add.w));
+              }
+            }
+          }
           if (n_ok) {
 #pragma unroll
             for (int j = 0; j < kChunk; ++j) {
@@ -1054,6 +1116,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       tcgen05_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if constexpr (MODE == kDense) {
+        if (split && split_rank != 0 && lane == 0) {
+          // this warp's share of the partial tile is written: tell rank 0
+          cluster_mbar_arrive(cluster_map_shared(smem_u32(partial_full), 0));
+        }
+      }
       NML_PROF_END(1);
     }
     NML_PROF_FLUSH(8, threadIdx.x == 64)
@@ -1071,7 +1139,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     const DecodeConstants dc = p.decode;
     const uint8_t* lut_lane = smem + L::kLutOffset + lane * 4;  // this lane's copy of the table
     NML_PROF_DECL
-    for (int index = blockIdx.x; index < units && ok; index += gridDim.x, ++local) {
+    for (int index = first_unit; index < units && ok; index += unit_stride, ++local) {
       const uint8_t* unit_scales = nullptr;
       if constexpr (kBulk) {
         if (!wait(&full_scale[local & 1], (local >> 1) & 1, kSiteDecodeScale)) break;
@@ -1088,7 +1156,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
           break;
         }
         NML_PROF_END(0);
-        const int sub_steps = min(KS, p.k_steps - rs * KS);
+        const int sub_steps = min(KS, k_count - rs * KS);
         for (int j = 0; j < sub_steps; ++j, ++sequence, wb.advance<WB>()) {
           if (sequence % DG != group) continue;
 #ifdef NML_SM100_DEBUG_WAITS
@@ -1117,7 +1185,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
             codes[1] = *reinterpret_cast<const uint4*>(source + (((2 * j + 1) ^ (row & 7)) * 16));
           }
           const uint32_t four_scales =
-              kBulk ? *reinterpret_cast<const uint32_t*>(unit_scales + (rs * KS + j) * 4)
+              kBulk ? *reinterpret_cast<const uint32_t*>(unit_scales + (k_begin + rs * KS + j) * 4)
                  : *reinterpret_cast<const uint32_t*>(scale_tile(ps.index) + row * (4 * KS) +
                                                       j * 4);
           uint32_t scale[4];
@@ -1238,7 +1306,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
           --in_flight;
         }
       };
-      for (int index = blockIdx.x; index < units && ok; index += gridDim.x) {
+      for (int index = first_unit; index < units && ok; index += unit_stride) {
         const Unit u = get_unit<BM, GROUPED>(p, groups, index);
         int64_t source_offset[kRowsPerThread];  // byte offset of the source row, -1 = zero row
 #pragma unroll
@@ -1299,6 +1367,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     tcgen05_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemColumns);
   }
+  // No CTA of a cluster leaves while another may still write into its shared memory.
+  if (split) cluster_sync_all();
 }
 
 }  // namespace umma

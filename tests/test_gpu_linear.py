@@ -174,10 +174,46 @@ def test_fused_qkv_matches_three_linears_and_oracle(M, K, outputs, with_bias, dt
     torch.cuda.synchronize()
     assert _abi.device_status(0x1) == 0
     for i in range(3):
-        single = ops.linear(x, weights[i], biases[i])
-        torch.cuda.synchronize()
-        if M <= 64:  # same tile height either way: the same instruction stream per row
-            assert torch.equal(fused[i].view(torch.int16), single.view(torch.int16)), i
         expected = oracle.linear(x32, *triples[i], biases32[i])
         gu.assert_gemm_close(gu.device_f32(fused[i]), expected, f"qkv projection {i} M={M}")
+    if M <= 64:
+        # Same tile height either way, so the same instruction stream per row -- once the
+        # K split over a cluster (whose width follows the tile count of the launch) is off.
+        previous = _abi.set_kernel_policy(_abi.POLICY_NO_SPLIT_K)
+        try:
+            fused = ops.linear_qkv(x, weights[0], biases[0], weights[1], biases[1], weights[2],
+                                   biases[2])
+            for i in range(3):
+                single = ops.linear(x, weights[i], biases[i])
+                torch.cuda.synchronize()
+                assert torch.equal(fused[i].view(torch.int16), single.view(torch.int16)), i
+        finally:
+            _abi.set_kernel_policy(previous)
     assert _abi.device_status(0x1) == 0
+
+
+@pytest.mark.parametrize("dtype", [oracle.BF16, oracle.F16])
+@pytest.mark.parametrize("M,K,N", [(1, 2880, 5760), (16, 2880, 2880), (32, 4096, 2880),
+                                   (16, 1024, 640), (8, 2880, 128)])
+def test_split_k_over_a_cluster_matches_oracle_and_unsplit_kernel(M, K, N, dtype):
+    # few weight tiles and few rows: the K range is cut over the CTAs of a cluster and the
+    # partial tiles meet in rank 0's shared memory
+    from nml_b200 import ops, _abi
+    import gpu_util as gu
+    triple = make_weight(1000 + N, (N, K))
+    weight = gu.parameter("w", triple, K, dtype)
+    x_bits, x32 = make_activation(1001 + M, (M, K), dtype=dtype)
+    x = gu.to_device_bits(x_bits, dtype)
+    split = ops.linear(x, weight)
+    again = ops.linear(x, weight)
+    previous = _abi.set_kernel_policy(_abi.POLICY_NO_SPLIT_K)
+    try:
+        unsplit = ops.linear(x, weight)
+    finally:
+        _abi.set_kernel_policy(previous)
+    torch.cuda.synchronize()
+    assert _abi.device_status(0x1) == 0
+    assert torch.equal(split.view(torch.int16), again.view(torch.int16))  # deterministic
+    expected = oracle.linear(x32, *triple, None)
+    gu.assert_gemm_close(gu.device_f32(split), expected, f"split M={M} K={K} N={N}")
+    gu.assert_gemm_close(gu.device_f32(unsplit), expected, f"unsplit M={M} K={K} N={N}")
