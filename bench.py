@@ -616,7 +616,7 @@ def sharded_extras(args, rank, world, device, barrier, head, peaks) -> dict:
     torch.cuda.empty_cache()
     x_local, logits_local = x[lo:hi].contiguous(), logits[lo:hi].contiguous()
     moe_flops = 2.0 * tokens * top_k * (2 * inter * hidden_size + hidden_size * inter)
-    for schedule in ("alltoall", "allreduce"):
+    for schedule in ("alltoall", "push", "allreduce"):
         moe = ep.ExpertParallelMoE(layer, top_k, schedule=schedule)
         ms = timed(lambda: moe(x_local, logits_local), 3, max(args.steps, 5), barrier, world)
         out[f"moe_{schedule}"] = {

@@ -344,6 +344,71 @@ int32_t nml_nvfp4_sm100_routed_swiglu(const NmlSm100RoutedSwiglu *request, char 
 
 /* Expert-parallel token exchange support; together they replace lower_expert_parallel's
  * replicate-and-all-reduce scheme (crates/nml-ir/src/lib.rs:9596-9728). */
+/* Token exchange by direct stores into peer memory (NVLink), for ranks that have mapped each
+ * other's receive buffers into their own address space (symmetric memory).  No counterpart in the reference.  Stage order per layer,
+ * all on the caller's stream: ep_dispatch_plan; all-gather of send_counts into count_matrix
+ * [ranks, ranks] (row = sender); ep_push_rows; a stream-ordered collective over the ranks (all
+ * pushes have landed); ep_receive_meta; the routed layer over the received rows (k = 1);
+ * ep_return_rows; the same collective again; combine_rows over the return buffer.  Rank r's
+ * rows for rank d occupy [sum_{r' < r} C[r'][d], ...) of d's buffer in r's send order.  A row
+ * that would fall outside `capacity` is dropped and NML_SM100_STATUS_INDEX_RANGE is raised. */
+#define NML_SM100_EP_MAX_RANKS 16
+typedef struct NmlSm100EpPushRows {
+  size_t struct_size;
+  const void *source;              /* [source_rows, width] dtype: this rank's tokens */
+  const int32_t *send_order;       /* [assignments] from ep_dispatch_plan (-1 in the tail) */
+  const int32_t *local_expert;     /* [assignments] from ep_dispatch_plan */
+  const void *routing_weights;     /* [assignments] dtype */
+  const int32_t *send_counts;      /* [ranks] from ep_dispatch_plan */
+  const int32_t *count_matrix;     /* [ranks, ranks] all-gathered send_counts */
+  void *peer_rows[NML_SM100_EP_MAX_RANKS];    /* receive rows [capacity, width] of every rank */
+  int32_t *peer_meta[NML_SM100_EP_MAX_RANKS]; /* receive meta [capacity, 4] i32 of every rank */
+  void *stream;
+  int64_t assignments;
+  int64_t source_rows;
+  int64_t experts_per_token;
+  int64_t width;                   /* multiple of 8 */
+  int64_t ranks;
+  int64_t rank;
+  int64_t capacity;
+  int32_t dtype;
+} NmlSm100EpPushRows;
+
+typedef struct NmlSm100EpReceiveMeta {
+  size_t struct_size;
+  const int32_t *meta;             /* this rank's receive meta [capacity, 4] */
+  const int32_t *count_matrix;
+  int32_t *expert_ids;             /* [capacity] local expert or -1 past the received rows */
+  void *routing_weights;           /* [capacity] dtype */
+  int32_t *received;               /* device scalar: rows received */
+  void *stream;
+  int64_t ranks;
+  int64_t rank;
+  int64_t capacity;
+  int32_t dtype;
+} NmlSm100EpReceiveMeta;
+
+typedef struct NmlSm100EpReturnRows {
+  size_t struct_size;
+  const void *computed;            /* [capacity, width] dtype: result rows in receive order */
+  const int32_t *meta;             /* this rank's receive meta */
+  const int32_t *count_matrix;
+  void *peer_return[NML_SM100_EP_MAX_RANKS];  /* return rows [return_capacity, width] */
+  void *stream;
+  int64_t width;
+  int64_t ranks;
+  int64_t rank;
+  int64_t capacity;
+  int64_t return_capacity;
+  int32_t dtype;
+} NmlSm100EpReturnRows;
+
+int32_t nml_nvfp4_sm100_ep_push_rows(const NmlSm100EpPushRows *request, char *error_message,
+                                     size_t error_message_capacity);
+int32_t nml_nvfp4_sm100_ep_receive_meta(const NmlSm100EpReceiveMeta *request,
+                                        char *error_message, size_t error_message_capacity);
+int32_t nml_nvfp4_sm100_ep_return_rows(const NmlSm100EpReturnRows *request, char *error_message,
+                                       size_t error_message_capacity);
 int32_t nml_nvfp4_sm100_ep_dispatch_plan(const NmlSm100EpDispatchPlan *request,
                                          char *error_message, size_t error_message_capacity);
 int32_t nml_nvfp4_sm100_gather_rows(const NmlSm100GatherRows *request, char *error_message,

@@ -130,7 +130,35 @@ class CombineRows(ctypes.Structure):
 
 
 # name -> request structure, for the entry points of the form fn(const Request*, char*, size_t)
+EP_MAX_RANKS = 16
+
+
+class EpPushRows(ctypes.Structure):
+    _fields_ = [("struct_size", _sz), ("source", _vp), ("send_order", _vp),
+                ("local_expert", _vp), ("routing_weights", _vp), ("send_counts", _vp),
+                ("count_matrix", _vp), ("peer_rows", _vp * EP_MAX_RANKS),
+                ("peer_meta", _vp * EP_MAX_RANKS), ("stream", _vp), ("assignments", _i64),
+                ("source_rows", _i64), ("experts_per_token", _i64), ("width", _i64),
+                ("ranks", _i64), ("rank", _i64), ("capacity", _i64), ("dtype", _i32)]
+
+
+class EpReceiveMeta(ctypes.Structure):
+    _fields_ = [("struct_size", _sz), ("meta", _vp), ("count_matrix", _vp), ("expert_ids", _vp),
+                ("routing_weights", _vp), ("received", _vp), ("stream", _vp), ("ranks", _i64),
+                ("rank", _i64), ("capacity", _i64), ("dtype", _i32)]
+
+
+class EpReturnRows(ctypes.Structure):
+    _fields_ = [("struct_size", _sz), ("computed", _vp), ("meta", _vp), ("count_matrix", _vp),
+                ("peer_return", _vp * EP_MAX_RANKS), ("stream", _vp), ("width", _i64),
+                ("ranks", _i64), ("rank", _i64), ("capacity", _i64), ("return_capacity", _i64),
+                ("dtype", _i32)]
+
+
 REQUEST_ENTRY_POINTS = {
+    "nml_nvfp4_sm100_ep_push_rows": EpPushRows,
+    "nml_nvfp4_sm100_ep_receive_meta": EpReceiveMeta,
+    "nml_nvfp4_sm100_ep_return_rows": EpReturnRows,
     "nml_nvfp4_sm100_linear": Linear,
     "nml_nvfp4_sm100_linear_qkv": LinearQkv,
     "nml_nvfp4_sm100_embedding": Embedding,

@@ -915,6 +915,89 @@ extern "C" int32_t nml_nvfp4_sm100_gather_rows(const NmlSm100GatherRows* request
                             error_message_capacity);
 }
 
+namespace {
+bool valid_ranks(int64_t ranks, int64_t rank) {
+  return ranks >= 1 && ranks <= NML_SM100_EP_MAX_RANKS && rank >= 0 && rank < ranks;
+}
+}  // namespace
+
+extern "C" int32_t nml_nvfp4_sm100_ep_push_rows(const NmlSm100EpPushRows* request,
+                                                char* error_message,
+                                                size_t error_message_capacity) {
+  if (request == nullptr || request->struct_size < sizeof(NmlSm100EpPushRows)) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "truncated NVFP4 row push request", error_message,
+                error_message_capacity);
+  }
+  bool valid = request->source != nullptr && request->send_order != nullptr &&
+               request->local_expert != nullptr && request->routing_weights != nullptr &&
+               request->send_counts != nullptr && request->count_matrix != nullptr &&
+               request->stream != nullptr && fits_i32(request->assignments) &&
+               fits_i32(request->source_rows) && fits_i32(request->width) &&
+               request->width % 8 == 0 && request->experts_per_token > 0 &&
+               fits_i32(request->capacity) && valid_ranks(request->ranks, request->rank) &&
+               reinterpret_cast<uintptr_t>(request->source) % 16 == 0;
+  for (int r = 0; valid && r < request->ranks; ++r) {
+    valid = request->peer_rows[r] != nullptr && request->peer_meta[r] != nullptr &&
+            reinterpret_cast<uintptr_t>(request->peer_rows[r]) % 16 == 0 &&
+            reinterpret_cast<uintptr_t>(request->peer_meta[r]) % 16 == 0;
+  }
+  if (!valid || !valid_dtype(request->dtype)) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "invalid NVFP4 row push request", error_message,
+                error_message_capacity);
+  }
+  const DeviceInfo* device = current_device(error_message, error_message_capacity);
+  if (device == nullptr) return NML_SM100_LAUNCH_FAILURE;
+  return launch_ep_push_rows(*request, *device, error_message, error_message_capacity);
+}
+
+extern "C" int32_t nml_nvfp4_sm100_ep_receive_meta(const NmlSm100EpReceiveMeta* request,
+                                                   char* error_message,
+                                                   size_t error_message_capacity) {
+  if (request == nullptr || request->struct_size < sizeof(NmlSm100EpReceiveMeta)) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "truncated NVFP4 receive meta request", error_message,
+                error_message_capacity);
+  }
+  if (request->meta == nullptr || request->count_matrix == nullptr ||
+      request->expert_ids == nullptr || request->routing_weights == nullptr ||
+      request->received == nullptr || request->stream == nullptr ||
+      !fits_i32(request->capacity) || !valid_ranks(request->ranks, request->rank) ||
+      reinterpret_cast<uintptr_t>(request->meta) % 16 != 0 || !valid_dtype(request->dtype)) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "invalid NVFP4 receive meta request", error_message,
+                error_message_capacity);
+  }
+  if (current_device(error_message, error_message_capacity) == nullptr) {
+    return NML_SM100_LAUNCH_FAILURE;
+  }
+  return launch_ep_receive_meta(*request, error_message, error_message_capacity);
+}
+
+extern "C" int32_t nml_nvfp4_sm100_ep_return_rows(const NmlSm100EpReturnRows* request,
+                                                  char* error_message,
+                                                  size_t error_message_capacity) {
+  if (request == nullptr || request->struct_size < sizeof(NmlSm100EpReturnRows)) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "truncated NVFP4 row return request", error_message,
+                error_message_capacity);
+  }
+  bool valid = request->computed != nullptr && request->meta != nullptr &&
+               request->count_matrix != nullptr && request->stream != nullptr &&
+               fits_i32(request->width) && request->width % 8 == 0 &&
+               fits_i32(request->capacity) && fits_i32(request->return_capacity) &&
+               valid_ranks(request->ranks, request->rank) &&
+               reinterpret_cast<uintptr_t>(request->computed) % 16 == 0 &&
+               reinterpret_cast<uintptr_t>(request->meta) % 16 == 0;
+  for (int r = 0; valid && r < request->ranks; ++r) {
+    valid = request->peer_return[r] != nullptr &&
+            reinterpret_cast<uintptr_t>(request->peer_return[r]) % 16 == 0;
+  }
+  if (!valid || !valid_dtype(request->dtype)) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "invalid NVFP4 row return request", error_message,
+                error_message_capacity);
+  }
+  const DeviceInfo* device = current_device(error_message, error_message_capacity);
+  if (device == nullptr) return NML_SM100_LAUNCH_FAILURE;
+  return launch_ep_return_rows(*request, *device, error_message, error_message_capacity);
+}
+
 extern "C" int32_t nml_nvfp4_sm100_combine_rows(const NmlSm100CombineRows* request,
                                                 char* error_message,
                                                 size_t error_message_capacity) {

@@ -181,6 +181,13 @@ bool experts_umma_supported(const ExpertArgs& args);
 int32_t launch_experts_umma(const ExpertArgs& args, const DeviceInfo& device, char* message,
                             size_t capacity);
 
+int32_t launch_ep_push_rows(const NmlSm100EpPushRows& request, const DeviceInfo& device,
+                            char* message, size_t capacity);
+int32_t launch_ep_receive_meta(const NmlSm100EpReceiveMeta& request, char* message,
+                               size_t capacity);
+int32_t launch_ep_return_rows(const NmlSm100EpReturnRows& request, const DeviceInfo& device,
+                              char* message, size_t capacity);
+
 int get_kernel_policy();
 void note_linear_kernel(const char* name, int tile_rows);
 

@@ -11,6 +11,12 @@ tokens on every device and all-reducing the partial outputs
               routed to it, and the token's home rank sums its k returned rows in route order.
               Every per-assignment row is produced by the same kernels as on one GPU, so the
               result equals the single-GPU result bit for bit.
+``push``      the same exchange without NCCL on the data path and without any host
+              synchronisation: every rank maps the others' receive buffers (torch symmetric
+              memory) and the
+              dispatch kernel stores each routed row straight into its owner's buffer over
+              NVLink; results come back the same way.  Row placement follows from the
+              all-gathered count matrix, so the layout is deterministic.  CUDA only.
 ``allreduce`` the reference's scheme: hidden states are all-gathered, every rank runs its local
               experts over all tokens and partial outputs are summed with an all-reduce.  No
               host synchronisation; meant for decode-size batches.
@@ -84,6 +90,41 @@ class CudaBackend:
         _abi.call("nml_nvfp4_sm100_combine_rows", request)
         return out
 
+    def push_rows(self, hidden, order, local_expert, weights, counts, count_matrix, peers, rank,
+                  top_k, capacity):
+        request = _abi.EpPushRows(
+            source=hidden.data_ptr(), send_order=order.data_ptr(),
+            local_expert=local_expert.data_ptr(), routing_weights=weights.data_ptr(),
+            send_counts=counts.data_ptr(), count_matrix=count_matrix.data_ptr(),
+            peer_rows=(_abi._vp * _abi.EP_MAX_RANKS)(*[p.rows_ptr for p in peers]),
+            peer_meta=(_abi._vp * _abi.EP_MAX_RANKS)(*[p.meta_ptr for p in peers]),
+            stream=ops._stream(hidden), assignments=order.numel(), source_rows=hidden.shape[0],
+            experts_per_token=top_k, width=hidden.shape[1], ranks=len(peers), rank=rank,
+            capacity=capacity, dtype=ops._code(hidden.dtype))
+        _abi.call("nml_nvfp4_sm100_ep_push_rows", request)
+
+    def receive_meta(self, meta, count_matrix, dtype, ranks, rank, capacity):
+        device = meta.device
+        ids = torch.empty((capacity, 1), dtype=torch.int32, device=device)
+        weights = torch.empty((capacity, 1), dtype=dtype, device=device)
+        received = torch.empty(1, dtype=torch.int32, device=device)
+        request = _abi.EpReceiveMeta(
+            meta=meta.data_ptr(), count_matrix=count_matrix.data_ptr(), expert_ids=ids.data_ptr(),
+            routing_weights=weights.data_ptr(), received=received.data_ptr(),
+            stream=ops._stream(meta), ranks=ranks, rank=rank, capacity=capacity,
+            dtype=ops._code(dtype))
+        _abi.call("nml_nvfp4_sm100_ep_receive_meta", request)
+        return ids, weights, received
+
+    def return_rows(self, computed, meta, count_matrix, peers, rank, capacity, return_capacity):
+        request = _abi.EpReturnRows(
+            computed=computed.data_ptr(), meta=meta.data_ptr(),
+            count_matrix=count_matrix.data_ptr(),
+            peer_return=(_abi._vp * _abi.EP_MAX_RANKS)(*[p.back_ptr for p in peers]),
+            stream=ops._stream(computed), width=computed.shape[1], ranks=len(peers), rank=rank,
+            capacity=capacity, return_capacity=return_capacity, dtype=ops._code(computed.dtype))
+        _abi.call("nml_nvfp4_sm100_ep_return_rows", request)
+
     def routed_experts(self, hidden, expert_ids, routing_weights, layer, expert_offset=0):
         return ops.routed_experts(hidden, expert_ids, routing_weights, layer.gate_up,
                                   layer.gate_up_bias, layer.down, layer.down_bias,
@@ -118,6 +159,55 @@ class LocalExperts:
                             experts, start)
 
 
+@dataclass
+class PeerBuffers:
+    """Device addresses of one rank's receive rows / receive meta / return rows, valid for
+    kernels of this process; `rows`, `meta` and `back` are tensors for this rank's own."""
+
+    rows_ptr: int
+    meta_ptr: int
+    back_ptr: int
+    rows: torch.Tensor | None = None  # [capacity, H]
+    meta: torch.Tensor | None = None  # [capacity, 4] i32: expert, weight bits, origin rank, slot
+    back: torch.Tensor | None = None  # [return_capacity, H]
+
+
+def exchange_peer_buffers(capacity: int, return_capacity: int, width: int, dtype, device,
+                          group=None) -> list:
+    """Allocates this rank's buffers in symmetric memory and maps every other rank's (a
+    collective over `group`): one allocation per rank, the same layout everywhere, peer
+    addresses from the rendezvous handle."""
+    element = torch.empty((), dtype=dtype).element_size()
+    rows_bytes = -(-capacity * width * element // 256) * 256
+    meta_bytes = -(-capacity * 16 // 256) * 256
+    back_bytes = -(-return_capacity * width * element // 256) * 256
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    total = rows_bytes + meta_bytes + back_bytes
+    if world == 1:
+        block = torch.empty(total, dtype=torch.uint8, device=device)
+        bases = [block.data_ptr()]
+    else:
+        import os
+        # plain peer mappings only: this path never uses multicast (multimem) accesses
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symmetric
+        block = symmetric.empty(total, dtype=torch.uint8, device=device)
+        handle = symmetric.rendezvous(block, group if group is not None else dist.group.WORLD)
+        bases = [int(p) for p in handle.buffer_ptrs]
+        if bases[rank] != block.data_ptr():
+            raise RuntimeError("symmetric memory handle does not describe the local buffer")
+    peers = [PeerBuffers(b, b + rows_bytes, b + rows_bytes + meta_bytes) for b in bases]
+    own = peers[rank]
+    own.rows = block[:capacity * width * element].view(dtype).view(capacity, width)
+    own.meta = block[rows_bytes:rows_bytes + capacity * 16].view(torch.int32).view(capacity, 4)
+    own.back = block[rows_bytes + meta_bytes:
+                     rows_bytes + meta_bytes + return_capacity * width * element] \
+        .view(dtype).view(return_capacity, width)
+    own.block = block  # keeps the allocation (and the mapping) alive
+    return peers
+
+
 class ExpertParallelMoE:
     """Routed clamped-SwiGLU layer with experts sharded over the ranks of ``group``.
 
@@ -127,9 +217,15 @@ class ExpertParallelMoE:
     """
 
     def __init__(self, layer: LocalExperts, experts_per_token: int, group=None,
-                 schedule: str = "alltoall", backend=None):
-        if schedule not in ("alltoall", "allreduce"):
-            raise ValueError("schedule must be 'alltoall' or 'allreduce'")
+                 schedule: str = "alltoall", backend=None, capacity_factor: float = 2.0):
+        if schedule not in ("alltoall", "allreduce", "push"):
+            raise ValueError("schedule must be 'alltoall', 'push' or 'allreduce'")
+        if capacity_factor < 1.0:
+            raise ValueError("capacity_factor must be at least 1")
+        self.capacity_factor = capacity_factor
+        self._peers = None       # push schedule: mapped buffers, allocated on first use
+        self._peer_key = None
+        self._fence_word = None
         self.layer = layer
         self.top_k = experts_per_token
         self.group = group
@@ -189,6 +285,49 @@ class ExpertParallelMoE:
             returned = computed
         return backend.combine_rows(returned, slot_of, tokens, k)  # unpermute + k-way sum
 
+    # ------------------------------------------------------------------ peer push
+    def _fence(self, device):
+        """Stream-ordered meeting point of the ranks: every rank's earlier kernels (and their
+        stores into peer memory) have completed when it returns on the stream."""
+        if self.world > 1:
+            if self._fence_word is None:
+                self._fence_word = torch.zeros(1, dtype=torch.int32, device=device)
+            dist.all_reduce(self._fence_word, group=self.group)
+
+    def _forward_push(self, hidden, router_logits, active_tokens):
+        backend, k = self.backend, self.top_k
+        tokens, width = hidden.shape
+        assignments = tokens * k
+        # rows one rank may receive: `capacity_factor` times its fair share, at most everything
+        capacity = min(self.world * assignments,
+                       -(-int(self.capacity_factor * assignments) // 16) * 16)
+        key = (tokens, width, hidden.dtype, hidden.device, capacity)
+        if self._peer_key != key:
+            self._peers = exchange_peer_buffers(capacity, assignments, width, hidden.dtype,
+                                                hidden.device, self.group)
+            self._peer_key = key
+        peers = self._peers
+        ids, weights = backend.route(router_logits, k, hidden.dtype, active_tokens)
+        order, local_expert, slot_of, counts = backend.dispatch_plan(
+            ids.reshape(-1), self.world, self.layer.experts_local)
+        count_matrix = torch.empty((self.world, self.world), dtype=torch.int32,
+                                   device=hidden.device)
+        if self.world > 1:
+            dist.all_gather_into_tensor(count_matrix, counts, group=self.group)
+        else:
+            count_matrix.copy_(counts.reshape(1, 1))
+        backend.push_rows(hidden, order, local_expert, weights.reshape(-1), counts, count_matrix,
+                          peers, self.rank, k, capacity)
+        self._fence(hidden.device)  # every row routed to this rank has landed
+        mine = peers[self.rank]
+        recv_ids, recv_weights, _ = backend.receive_meta(mine.meta, count_matrix, hidden.dtype,
+                                                         self.world, self.rank, capacity)
+        computed = backend.routed_experts(mine.rows, recv_ids, recv_weights, self.layer)
+        backend.return_rows(computed, mine.meta, count_matrix, peers, self.rank, capacity,
+                            assignments)
+        self._fence(hidden.device)  # every row of this rank's tokens is back
+        return backend.combine_rows(mine.back, slot_of, tokens, k)
+
     # ------------------------------------------------------------------ all-reduce
     def _forward_allreduce(self, hidden, router_logits, active_tokens):
         backend, group, k = self.backend, self.group, self.top_k
@@ -220,6 +359,8 @@ class ExpertParallelMoE:
             raise ValueError("routing tensors do not match the token and hidden extents")
         if self.schedule == "alltoall":
             return self._forward_alltoall(hidden, router_logits, active_tokens)
+        if self.schedule == "push":
+            return self._forward_push(hidden, router_logits, active_tokens)
         return self._forward_allreduce(hidden, router_logits, active_tokens)
 
     __call__ = forward
