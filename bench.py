@@ -53,6 +53,9 @@ def parse_args():
     parser.add_argument("--no-detail", action="store_true", help="skip the per-shape table")
     parser.add_argument("--no-extras", action="store_true",
                         help="skip the sharded MoE / unembedding / embedding figures")
+    parser.add_argument("--graph-extras", action="store_true",
+                        help="also time the expert-parallel layer replayed from a CUDA graph "
+                             "(push and all-reduce schedules; removes the host time per call)")
     parser.add_argument("--kernel-policy", type=int, default=0,
                         help="nml_nvfp4_sm100_set_kernel_policy value (profiling captures: "
                              "100 + BM forces the tile height, 1000 + BM with the "
@@ -552,6 +555,42 @@ def timed(fn, warmup, steps, barrier, world):
     return elapsed
 
 
+def timed_from_graph(fn, steps, barrier, world):
+    """Device time per replay of `fn` captured once in a CUDA graph (collectives included), in
+    ms, max over ranks; None when the capture fails."""
+    import torch
+    import torch.distributed as dist
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                fn()
+        torch.cuda.current_stream().wait_stream(side)
+        barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        for _ in range(3):
+            graph.replay()
+        barrier()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(steps):
+            graph.replay()
+        end.record()
+        barrier()
+        elapsed = begin.elapsed_time(end) / steps
+    except Exception as error:  # noqa: BLE001 -- report and carry on with the eager figure
+        print(f"cuda graph capture failed: {error}", file=sys.stderr)
+        return None
+    if world > 1:
+        t = torch.tensor([elapsed], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed = float(t.item())
+    return elapsed
+
+
 def qkv_fusion_figures(device) -> list:
     """The Q/K/V projections of one GPT-OSS-20B layer (2880 -> 4096 + 512 + 512) at decode
     batch sizes: one fused launch against three linear launches (device time per layer,
@@ -619,7 +658,12 @@ def sharded_extras(args, rank, world, device, barrier, head, peaks) -> dict:
     for schedule in ("alltoall", "push", "allreduce"):
         moe = ep.ExpertParallelMoE(layer, top_k, schedule=schedule)
         ms = timed(lambda: moe(x_local, logits_local), 3, max(args.steps, 5), barrier, world)
+        graph_ms = None
+        if args.graph_extras and schedule != "alltoall":  # all-to-all-v synchronises the host
+            graph_ms = timed_from_graph(lambda: moe(x_local, logits_local), max(args.steps, 5),
+                                        barrier, world)
         out[f"moe_{schedule}"] = {
+            "ms_per_layer_from_cuda_graph": graph_ms,
             "metric": "moe_layer_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
             "ms_per_layer": ms, "tflops": moe_flops / (ms * 1e-3) / 1e12, "tokens": tokens,
             "experts": experts, "top_k": top_k, "n_gpus": world, "scaling": "strong",
