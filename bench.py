@@ -415,7 +415,7 @@ def run_ours(args) -> None:
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from ncu captures, filled in from
 # the summaries under profiles/ (None until a capture exists).
-NCU_TRAFFIC = {"gemm_kernel_large_tiles": 253.2e6}  # 2880->5760 at M=16384, BM=256 (292 MB algorithmic)
+NCU_TRAFFIC = {"gemm_kernel_large_tiles": 251.7e6}  # 2880->5760 at M=16384, BM=256 (292 MB algorithmic)
 
 
 def shape_table(cases, durations, weights, activations, outputs, peaks, selected):
