@@ -1174,10 +1174,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
           NML_PROF_BEGIN();
           uint4 codes[2];
           if constexpr (KS == 1) {
-            const uint4* source =
-                reinterpret_cast<const uint4*>(payload_tile(ps.index) + row * 32);
-            codes[0] = source[0];
-            codes[1] = source[1];
+            // rows of 32 bytes, 32-byte swizzled by the TMA load (16-byte halves of rows 4..7
+            // of every 8 swapped), which spreads a quarter-warp's 16-byte reads over all banks
+            const uint8_t* source = payload_tile(ps.index) + row * 32;
+            const int swap = (row >> 2) & 1;
+            codes[0] = *reinterpret_cast<const uint4*>(source + (swap * 16));
+            codes[1] = *reinterpret_cast<const uint4*>(source + ((swap ^ 1) * 16));
           } else {
             // rows of 32*KS bytes, 128-byte swizzled by the TMA load
             const uint8_t* source = payload_tile(ps.index) + row * (32 * KS);
@@ -1412,7 +1414,9 @@ inline bool encode_payload_map(CUtensorMap* map, const uint8_t* payload, int64_t
   const cuuint32_t elem[2] = {1, 1};
   return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(payload), dims,
                 strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                KS == 4 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                KS == 4   ? CU_TENSOR_MAP_SWIZZLE_128B
+                : KS == 1 ? CU_TENSOR_MAP_SWIZZLE_32B
+                          : CU_TENSOR_MAP_SWIZZLE_NONE,
                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
