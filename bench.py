@@ -657,6 +657,15 @@ def sharded_extras(args, rank, world, device, barrier, head, peaks) -> dict:
     moe_flops = 2.0 * tokens * top_k * (2 * inter * hidden_size + hidden_size * inter)
     for schedule in ("alltoall", "push", "allreduce"):
         moe = ep.ExpertParallelMoE(layer, top_k, schedule=schedule)
+        if schedule == "push":
+            # needs every rank's buffers mapped into this process (symmetric memory); a box
+            # that cannot do that gets a note instead of a number
+            try:
+                moe(x_local, logits_local)
+                torch.cuda.synchronize()
+            except Exception as error:  # noqa: BLE001
+                out["moe_push"] = {"unavailable": f"{type(error).__name__}: {error}"[:200]}
+                continue
         ms = timed(lambda: moe(x_local, logits_local), 3, max(args.steps, 5), barrier, world)
         graph_ms = None
         if args.graph_extras and schedule != "alltoall":  # all-to-all-v synchronises the host
