@@ -474,8 +474,9 @@ int32_t nml_nvfp4_sm100_device_status(void *stream, int32_t clear, int32_t *stat
 int32_t nml_nvfp4_sm100_set_kernel_policy(int32_t policy);
 
 /* Name of the kernel family the last nml_nvfp4_sm100_linear call on this thread selected
- * ("umma_tmem_weights_af16", "umma_tmem_weights_abf16", "umma_swapab_af16",
- * "umma_swapab_abf16", "simt"), for tests and benchmark records. */
+ * ("umma_tmem_weights_af16", "umma_tmem_weights_abf16", "umma_tmem_weights_abf16_lut",
+ * "umma_swapab_af16", "umma_swapab_abf16", "simt"), for tests and benchmark records; the
+ * fused Q/K/V call records its one launch the same way. */
 const char *nml_nvfp4_sm100_last_linear_kernel(void);
 /* Activation rows per tile of that launch (0 for the SIMT kernel). */
 int32_t nml_nvfp4_sm100_last_linear_tile_rows(void);
