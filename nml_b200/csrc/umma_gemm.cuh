@@ -1134,6 +1134,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     const int row = ((warp & 3) << 5) | lane;
     RingState ps, wb;
     int sequence = 0;  // K steps seen so far by this CTA, over all units
+    int turn = 0;      // the decode group whose K step `sequence` is
     bool ok = true;
     int local = 0;
     const DecodeConstants dc = p.decode;
@@ -1157,8 +1158,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         }
         NML_PROF_END(0);
         const int sub_steps = min(KS, k_count - rs * KS);
-        for (int j = 0; j < sub_steps; ++j, ++sequence, wb.advance<WB>()) {
-          if (sequence % DG != group) continue;
+        for (int j = 0; j < sub_steps;
+             ++j, ++sequence, turn = turn + 1 == DG ? 0 : turn + 1, wb.advance<WB>()) {
+          if (turn != group) continue;  // turn == sequence % DG
 #ifdef NML_SM100_DEBUG_WAITS
           wait_position.step = sequence;
 #endif
