@@ -190,11 +190,11 @@ int32_t launch_for_rows(const LinearArgs& args, const DeviceInfo& device, char* 
                                                                         capacity);
         break;
       case 32:
-        rc = launch_config<32, 4, 5, 4, 8, 3, 1, 4, true, kAbf16Lut, T>(args, device, message,
+        rc = launch_config<32, 4, 5, 4, 8, 3, 2, 4, true, kAbf16Lut, T>(args, device, message,
                                                                         capacity);
         break;
       case 64:
-        rc = launch_config<64, 4, 3, 2, 8, 3, 1, 2, true, kAbf16Lut, T>(args, device, message,
+        rc = launch_config<64, 4, 3, 2, 8, 3, 2, 2, true, kAbf16Lut, T>(args, device, message,
                                                                         capacity);
         break;
       case 128:

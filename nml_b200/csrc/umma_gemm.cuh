@@ -496,7 +496,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
   constexpr int kGatherWarp0 = Roles<DG>::kGatherWarp0;  // first warp of the X side
   constexpr int kMmaWarpB = XTMA ? kGatherWarp0 + 1 : kGatherWarp0 + kGatherWarps;
   static_assert(2 * PA * BM <= 512, "partial accumulators exceed tensor memory");
-  static_assert(MI == 1 || PA == 8, "two issuers need disjoint partial accumulators");
+  static_assert(MI == 1 || (PA >= 2 && PA % 2 == 0),
+                "two issuers need disjoint sets of partial accumulators");
   static_assert(WB > DG, "the W' ring must hold one tile per decode group plus one");
   static_assert(GROUPED || XTMA, "the dense mode always loads activations by TMA");
   constexpr bool kBulk = WT || SB;  // block scales of a unit by one bulk copy
@@ -889,8 +890,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
 #pragma unroll
             for (int q = 0; q < kTileK / kUmmaK; ++q) {
               const int instruction = step * (kTileK / kUmmaK) + q;
-              const uint32_t d = d_base + (instruction % PA) * BM;
-              const uint32_t accumulate = instruction >= PA ? 1u : 0u;
+              // One issuer: slice i of the unit goes to partial accumulator i % PA.  Two
+              // issuers: the K step's parity picks a half of the accumulators (a K step has
+              // one issuer, so the halves never share a writer), q walks inside the half.
+              constexpr int kHalf = PA / 2;
+              const int partial = MI == 2 ? (step & 1) * kHalf + q % (kHalf > 0 ? kHalf : 1)
+                                          : instruction % PA;
+              const bool first = MI == 2 ? (step < 2 && q < kHalf) : instruction < PA;
+              const uint32_t d = d_base + partial * BM;
+              const uint32_t accumulate = first ? 0u : 1u;
               if constexpr (WT) {
                 umma_f16_tmem_a_elect(d, a_tmem + q * (kUmmaK / 2), b_desc + 2 * q, idesc,
                                       accumulate);
@@ -1012,7 +1020,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         if constexpr (PA > 1) {
           // add the other partial accumulators in index order; a unit with few K steps has
           // touched only the first 4 * k_steps of them
-          const int used = min(PA, k_count * (kTileK / kUmmaK));
+          const int used = MI == 2 ? (k_count > 1 ? PA : min(PA / 2, kTileK / kUmmaK))
+                                   : min(PA, k_count * (kTileK / kUmmaK));
 #pragma unroll 1
           for (int partial = 1; partial < used; ++partial) {
             uint32_t extra[kChunk];
