@@ -66,7 +66,10 @@ typedef struct NmlSm100Linear {
  * NvFp4QkvConfig) and lowers three custom calls otherwise; here one launch serves every row
  * count the tcgen05 kernel takes (inputs a multiple of 64), else the call is answered by three
  * linear launches.  Same dtype and inputs for all three; each weight has its own global scale
- * and optional bias.  Results equal those of three nml_nvfp4_sm100_linear calls bit for bit. */
+ * and optional bias.  Results equal those of three nml_nvfp4_sm100_linear calls bit for bit
+ * when both select the same kernel variant and K split (always for at most 16 rows), and to
+ * GEMM tolerance otherwise: the tile height and the split follow the launch's total tile
+ * count, so the f32 summation order can differ. */
 typedef struct NmlSm100LinearQkv {
   size_t struct_size;
   const void *activation;         /* [rows, inputs] dtype */
@@ -310,9 +313,12 @@ typedef struct NmlSm100CombineRows {
 int32_t nml_nvfp4_sm100_linear(const NmlSm100Linear *request, char *error_message,
                                size_t error_message_capacity);
 
-/* Replaces nml_nvfp4_turing_embedding (nml_nvfp4.h:98-100, turing_adapter.cu:735-783). */
+/* Replaces the three linears of lower_qkv and its fused small-batch kernel
+ * (crates/nml-ir/src/nvfp4_backend.rs:221-380). */
 int32_t nml_nvfp4_sm100_linear_qkv(const NmlSm100LinearQkv *request, char *error_message,
                                    size_t error_message_capacity);
+
+/* Replaces nml_nvfp4_turing_embedding (nml_nvfp4.h:98-100, turing_adapter.cu:735-783). */
 int32_t nml_nvfp4_sm100_embedding(const NmlSm100Embedding *request, char *error_message,
                                   size_t error_message_capacity);
 
@@ -450,6 +456,31 @@ size_t nml_nvfp4_sm100_routed_swiglu_workspace_bytes(int64_t tokens, int64_t hid
                                                      int64_t intermediate_size, int64_t experts,
                                                      int64_t experts_per_token);
 
+/* Where nml_nvfp4_sm100_routed_swiglu keeps its intermediates inside the caller's workspace
+ * (byte offsets), so that a test or a diagnostic tool can read the schedule and the
+ * per-stage results of a call after it has run.  `slot_ordered` is 1 when a batch of this
+ * size takes the large-batch path (rows permuted into schedule-slot order once, gate/up
+ * result kept in slot order in `slot_activated`, `activated` unused) given a workspace of
+ * nml_nvfp4_sm100_routed_swiglu_workspace_bytes(...) bytes.  Returns 1 on extents the layer
+ * rejects.  No counterpart in the reference (its intermediates are XLA-owned buffers). */
+typedef struct NmlSm100RoutedWorkspaceLayout {
+  size_t sorted_assignments; /* i32 [schedule_positions] */
+  size_t block_experts;      /* i32 [schedule_blocks] */
+  size_t active_blocks;      /* i32 scalar */
+  size_t activated;          /* dtype [assignments, intermediate] */
+  size_t weighted;           /* dtype [assignments, hidden] */
+  size_t permuted_hidden;    /* dtype [schedule_positions, hidden], slot-ordered path only */
+  size_t slot_activated;     /* dtype [schedule_positions, intermediate], slot-ordered path only */
+  int64_t schedule_blocks;
+  int64_t schedule_positions;
+  int32_t slot_ordered;
+} NmlSm100RoutedWorkspaceLayout;
+int32_t nml_nvfp4_sm100_routed_swiglu_workspace_layout(int64_t tokens, int64_t hidden_size,
+                                                       int64_t intermediate_size,
+                                                       int64_t experts,
+                                                       int64_t experts_per_token,
+                                                       NmlSm100RoutedWorkspaceLayout *layout);
+
 /* Schedule capacity of the assignment plan: writes blocks and positions, returns 0,
  * or 1 when the schedule would not be addressable by int32
  * (crates/nml-ir/src/lib.rs:5662-5688). */
@@ -465,18 +496,23 @@ int32_t nml_nvfp4_sm100_plan_capacity(int64_t assignments, int64_t experts, int6
 #define NML_SM100_STATUS_INDEX_RANGE 4
 int32_t nml_nvfp4_sm100_device_status(void *stream, int32_t clear, int32_t *status);
 
-/* Kernel selection override for experiments and tests: 0 = automatic, 1 = force the
- * portable SIMT kernels, 2 = force the tcgen05 kernels where the shape allows, 3 = as 2 but
- * keep the decoded weight tiles in a shared-memory ring instead of tensor memory, 4 = bf16
- * operands by bit placement instead of the byte table, 5 = never cut K over a cluster
- * (values from 100 up force tile heights, see linear_umma.cu).
- * Process-wide; returns the previous value. */
+/* Kernel selection override for tests: every shape has one automatic choice, and each kernel
+ * family must also be testable on shapes where it is not that choice.  The value belongs to
+ * the calling thread (calls on other threads are not affected); returns the previous value.
+ * A forced family that does not support the shape makes the call fail with
+ * NML_SM100_INVALID_ARGUMENT. */
+#define NML_SM100_POLICY_AUTO 0
+#define NML_SM100_POLICY_SIMT 1        /* the portable any-shape kernels */
+#define NML_SM100_POLICY_UMMA 2        /* the tcgen05 kernels */
+#define NML_SM100_POLICY_UMMA_SMEM 3   /* tcgen05 with the decoded weight tiles in shared memory */
+#define NML_SM100_POLICY_NO_SPLIT_K 5  /* tcgen05, never cut K over a cluster */
+#define NML_SM100_POLICY_STREAM 6      /* the weight-streaming kernels for few rows */
 int32_t nml_nvfp4_sm100_set_kernel_policy(int32_t policy);
 
 /* Name of the kernel family the last nml_nvfp4_sm100_linear call on this thread selected
- * ("umma_tmem_weights_af16", "umma_tmem_weights_abf16", "umma_tmem_weights_abf16_lut",
- * "umma_swapab_af16", "umma_swapab_abf16", "simt"), for tests and benchmark records; the
- * fused Q/K/V call records its one launch the same way. */
+ * ("stream", "umma_tmem_weights_af16", "umma_tmem_weights_abf16",
+ * "umma_tmem_weights_abf16_lut", "umma_swapab_af16", "umma_swapab_abf16", "simt"), for tests
+ * and benchmark records; the fused Q/K/V call records its one launch the same way. */
 const char *nml_nvfp4_sm100_last_linear_kernel(void);
 /* Activation rows per tile of that launch (0 for the SIMT kernel). */
 int32_t nml_nvfp4_sm100_last_linear_tile_rows(void);

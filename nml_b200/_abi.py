@@ -28,8 +28,8 @@ POLICY_AUTO = 0
 POLICY_SIMT = 1
 POLICY_UMMA = 2
 POLICY_UMMA_SMEM = 3  # tcgen05 with the decoded-weight ring in shared memory
-POLICY_NO_TABLE_DECODE = 4  # bf16 operands by bit placement instead of the byte table
-POLICY_NO_SPLIT_K = 5  # never cut K over a cluster
+POLICY_NO_SPLIT_K = 5  # tcgen05, never cut K over a cluster
+POLICY_STREAM = 6  # the weight-streaming kernels for few rows
 
 _vp = ctypes.c_void_p
 _i64 = ctypes.c_int64
@@ -129,7 +129,13 @@ class CombineRows(ctypes.Structure):
                 ("hidden_size", _i64), ("row_count", _i64), ("dtype", _i32)]
 
 
-# name -> request structure, for the entry points of the form fn(const Request*, char*, size_t)
+class RoutedWorkspaceLayout(ctypes.Structure):
+    _fields_ = [("sorted_assignments", _sz), ("block_experts", _sz), ("active_blocks", _sz),
+                ("activated", _sz), ("weighted", _sz), ("permuted_hidden", _sz),
+                ("slot_activated", _sz), ("schedule_blocks", _i64), ("schedule_positions", _i64),
+                ("slot_ordered", _i32)]
+
+
 EP_MAX_RANKS = 16
 
 
@@ -155,6 +161,7 @@ class EpReturnRows(ctypes.Structure):
                 ("dtype", _i32)]
 
 
+# name -> request structure, for the entry points of the form fn(const Request*, char*, size_t)
 REQUEST_ENTRY_POINTS = {
     "nml_nvfp4_sm100_ep_push_rows": EpPushRows,
     "nml_nvfp4_sm100_ep_receive_meta": EpReceiveMeta,
@@ -176,6 +183,7 @@ REQUEST_ENTRY_POINTS = {
 
 OTHER_ENTRY_POINTS = [
     "nml_nvfp4_sm100_routed_swiglu_workspace_bytes",
+    "nml_nvfp4_sm100_routed_swiglu_workspace_layout",
     "nml_nvfp4_sm100_plan_capacity",
     "nml_nvfp4_sm100_device_status",
     "nml_nvfp4_sm100_set_kernel_policy",
@@ -213,6 +221,9 @@ def load() -> ctypes.CDLL:
         fn.argtypes = [ctypes.POINTER(struct), ctypes.c_char_p, _sz]
     lib.nml_nvfp4_sm100_routed_swiglu_workspace_bytes.restype = _sz
     lib.nml_nvfp4_sm100_routed_swiglu_workspace_bytes.argtypes = [_i64] * 5
+    lib.nml_nvfp4_sm100_routed_swiglu_workspace_layout.restype = _i32
+    lib.nml_nvfp4_sm100_routed_swiglu_workspace_layout.argtypes = [_i64] * 5 + [
+        ctypes.POINTER(RoutedWorkspaceLayout)]
     lib.nml_nvfp4_sm100_plan_capacity.restype = _i32
     lib.nml_nvfp4_sm100_plan_capacity.argtypes = [_i64, _i64, ctypes.POINTER(_i64),
                                                   ctypes.POINTER(_i64)]

@@ -19,7 +19,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB_DIR = HERE / "lib"
 LIB_PATH = LIB_DIR / "libnml_nvfp4_sm100.so"
-SOURCES = ["abi.cu", "embedding.cu", "linear_simt.cu", "linear_umma.cu", "moe.cu",
+SOURCES = ["abi.cu", "embedding.cu", "linear_simt.cu", "linear_umma.cu", "stream.cu", "moe.cu",
            "experts_umma.cu", "ep.cu", "ep_push.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 

@@ -18,7 +18,7 @@ __device__ int g_status_word = 0;
 static __device__ __align__(256) unsigned char g_static_scratch[NML_SM100_STATIC_SCRATCH_BYTES];
 
 namespace {
-std::atomic<int> g_kernel_policy{0};
+thread_local int t_kernel_policy = NML_SM100_POLICY_AUTO;
 thread_local const char* t_last_linear_kernel = "none";
 thread_local int t_last_linear_tile_rows = 0;
 constexpr int kMaxDevices = 64;
@@ -26,11 +26,12 @@ DeviceInfo g_devices[kMaxDevices];
 std::atomic<int> g_device_ready[kMaxDevices];
 }  // namespace
 
-int get_kernel_policy() { return g_kernel_policy.load(std::memory_order_relaxed); }
-// 2 and 3 (and the tile-forcing values from 100 up) demand the tcgen05 kernels; 4 and 5 only
-// switch options of those kernels off.
+int get_kernel_policy() { return t_kernel_policy; }
 static bool policy_forces_tensor_cores(int policy) {
-  return policy == 2 || policy == 3 || policy >= 100;
+  return policy == NML_SM100_POLICY_UMMA || policy == NML_SM100_POLICY_UMMA_SMEM;
+}
+static bool policy_allows_stream(int policy) {
+  return policy == NML_SM100_POLICY_AUTO || policy == NML_SM100_POLICY_STREAM;
 }
 void note_linear_kernel(const char* name, int tile_rows) {
   t_last_linear_kernel = name;
@@ -87,7 +88,7 @@ int32_t launch_route(const NmlSm100Route& r, char* message, size_t capacity);
 int32_t launch_assignment_plan(const int32_t* expert_ids, int32_t* sorted_assignments,
                                int32_t* block_experts, int32_t* active_blocks, int assignments,
                                int experts, int expert_offset, int positions, int blocks,
-                               cudaStream_t stream, char* message, size_t capacity);
+                               int device, cudaStream_t stream, char* message, size_t capacity);
 int32_t launch_combine(const void* weighted, const int32_t* expert_ids, void* output, int tokens,
                        int top_k, int hidden, int experts, int expert_offset, int dtype,
                        cudaStream_t stream, char* message, size_t capacity);
@@ -123,10 +124,46 @@ bool plan_capacity(int64_t assignments, int64_t experts, int64_t* blocks, int64_
   return true;
 }
 
+// One linear launch (one to three projections over one activation) on the kernel family the
+// shape and the thread's policy select.  Returns kNoSingleLaunch when no family takes the
+// projections in one launch.
+constexpr int32_t kNoSingleLaunch = -1001;
+
+int32_t dispatch_linear(const LinearArgs& args, const DeviceInfo& device, char* message,
+                        size_t capacity) {
+  const int policy = get_kernel_policy();
+  if (policy_allows_stream(policy) && linear_stream_supported(args)) {
+    return launch_linear_stream(args, device, message, capacity);
+  }
+  if (policy == NML_SM100_POLICY_STREAM) {
+    return fail(NML_SM100_INVALID_ARGUMENT,
+                "the weight-streaming kernel was forced but does not support this shape", message,
+                capacity);
+  }
+  if (policy != NML_SM100_POLICY_SIMT && linear_umma_supported(args)) {
+    return launch_linear_umma(args, device, message, capacity);
+  }
+  if (policy_forces_tensor_cores(policy)) {
+    return fail(NML_SM100_INVALID_ARGUMENT,
+                "the tcgen05 linear kernel was forced but does not support this shape", message,
+                capacity);
+  }
+  if (args.extra_projections != 0) return kNoSingleLaunch;
+  return launch_linear_simt(args, device, message, capacity);
+}
+
 int32_t dispatch_experts(const ExpertArgs& args, const DeviceInfo& device, char* message,
                          size_t capacity) {
   const int policy = get_kernel_policy();
-  if (policy != 1 && experts_umma_supported(args)) {
+  if (policy_allows_stream(policy) && experts_stream_supported(args)) {
+    return launch_experts_stream(args, device, message, capacity);
+  }
+  if (policy == NML_SM100_POLICY_STREAM) {
+    return fail(NML_SM100_INVALID_ARGUMENT,
+                "the weight-streaming kernel was forced but does not support this shape", message,
+                capacity);
+  }
+  if (policy != NML_SM100_POLICY_SIMT && experts_umma_supported(args)) {
     return launch_experts_umma(args, device, message, capacity);
   }
   if (policy_forces_tensor_cores(policy)) {
@@ -194,7 +231,9 @@ using namespace nml_sm100;
 extern "C" int32_t nml_nvfp4_sm100_abi_version(void) { return NML_NVFP4_SM100_ABI_VERSION; }
 
 extern "C" int32_t nml_nvfp4_sm100_set_kernel_policy(int32_t policy) {
-  return g_kernel_policy.exchange(policy);
+  const int previous = t_kernel_policy;
+  t_kernel_policy = policy;
+  return previous;
 }
 
 extern "C" const char* nml_nvfp4_sm100_last_linear_kernel(void) { return t_last_linear_kernel; }
@@ -259,16 +298,7 @@ extern "C" int32_t nml_nvfp4_sm100_linear(const NmlSm100Linear* request, char* e
   args.outputs = static_cast<int>(request->outputs);
   args.inputs = static_cast<int>(request->inputs);
   args.dtype = request->dtype;
-  const int policy = get_kernel_policy();
-  if (policy != 1 && linear_umma_supported(args)) {
-    return launch_linear_umma(args, *device, error_message, error_message_capacity);
-  }
-  if (policy_forces_tensor_cores(policy)) {
-    return fail(NML_SM100_INVALID_ARGUMENT,
-                "the tcgen05 linear kernel was forced but does not support this shape",
-                error_message, error_message_capacity);
-  }
-  return launch_linear_simt(args, *device, error_message, error_message_capacity);
+  return dispatch_linear(args, *device, error_message, error_message_capacity);
 }
 
 extern "C" int32_t nml_nvfp4_sm100_linear_qkv(const NmlSm100LinearQkv* request,
@@ -315,10 +345,8 @@ extern "C" int32_t nml_nvfp4_sm100_linear_qkv(const NmlSm100LinearQkv* request,
                      request->global_scale[i + 1], request->bias[i + 1], request->output[i + 1],
                      static_cast<int>(request->outputs[i + 1])};
   }
-  const int policy = get_kernel_policy();
-  if (policy != 1 && linear_umma_supported(args)) {
-    return launch_linear_umma(args, *device, error_message, error_message_capacity);
-  }
+  const int32_t fused = dispatch_linear(args, *device, error_message, error_message_capacity);
+  if (fused != kNoSingleLaunch) return fused;
   // one launch per projection
   for (int i = 0; i < 3; ++i) {
     LinearArgs one;
@@ -333,16 +361,7 @@ extern "C" int32_t nml_nvfp4_sm100_linear_qkv(const NmlSm100LinearQkv* request,
     one.outputs = static_cast<int>(request->outputs[i]);
     one.inputs = args.inputs;
     one.dtype = args.dtype;
-    int32_t rc;
-    if (policy != 1 && linear_umma_supported(one)) {
-      rc = launch_linear_umma(one, *device, error_message, error_message_capacity);
-    } else if (policy_forces_tensor_cores(policy)) {
-      return fail(NML_SM100_INVALID_ARGUMENT,
-                  "the tcgen05 linear kernel was forced but does not support this shape",
-                  error_message, error_message_capacity);
-    } else {
-      rc = launch_linear_simt(one, *device, error_message, error_message_capacity);
-    }
+    const int32_t rc = dispatch_linear(one, *device, error_message, error_message_capacity);
     if (rc != NML_SM100_OK) return rc;
   }
   return NML_SM100_OK;
@@ -537,16 +556,15 @@ extern "C" int32_t nml_nvfp4_sm100_assignment_plan(const NmlSm100AssignmentPlan*
     return fail(NML_SM100_INVALID_ARGUMENT, "invalid NVFP4 assignment plan request",
                 error_message, error_message_capacity);
   }
-  if (current_device(error_message, error_message_capacity) == nullptr) {
-    return NML_SM100_LAUNCH_FAILURE;
-  }
+  const DeviceInfo* device = current_device(error_message, error_message_capacity);
+  if (device == nullptr) return NML_SM100_LAUNCH_FAILURE;
   return launch_assignment_plan(request->expert_ids, request->sorted_assignments,
                                 request->block_experts, request->active_blocks,
                                 static_cast<int>(request->assignments),
                                 static_cast<int>(request->experts), request->expert_offset,
                                 static_cast<int>(positions), static_cast<int>(blocks),
-                                static_cast<cudaStream_t>(request->stream), error_message,
-                                error_message_capacity);
+                                device->device, static_cast<cudaStream_t>(request->stream),
+                                error_message, error_message_capacity);
 }
 
 extern "C" int32_t nml_nvfp4_sm100_combine(const NmlSm100Combine* request, char* error_message,
@@ -590,6 +608,27 @@ extern "C" size_t nml_nvfp4_sm100_routed_swiglu_workspace_bytes(int64_t tokens,
     return 0;
   }
   return tokens * experts_per_token > kPermuteThreshold * experts ? w.total_permuted : w.total;
+}
+
+extern "C" int32_t nml_nvfp4_sm100_routed_swiglu_workspace_layout(
+    int64_t tokens, int64_t hidden_size, int64_t intermediate_size, int64_t experts,
+    int64_t experts_per_token, NmlSm100RoutedWorkspaceLayout* layout) {
+  RoutedWorkspace w;
+  if (layout == nullptr || !routed_workspace(tokens, hidden_size, intermediate_size, experts,
+                                             experts_per_token, &w)) {
+    return NML_SM100_INVALID_ARGUMENT;
+  }
+  layout->sorted_assignments = w.sorted_offset;
+  layout->block_experts = w.block_experts_offset;
+  layout->active_blocks = w.active_offset;
+  layout->activated = w.activated_offset;
+  layout->weighted = w.weighted_offset;
+  layout->permuted_hidden = w.permuted_offset;
+  layout->slot_activated = w.slot_activated_offset;
+  layout->schedule_blocks = w.blocks;
+  layout->schedule_positions = w.positions;
+  layout->slot_ordered = tokens * experts_per_token > kPermuteThreshold * experts ? 1 : 0;
+  return NML_SM100_OK;
 }
 
 extern "C" int32_t nml_nvfp4_sm100_routed_swiglu(const NmlSm100RoutedSwiglu* request,
@@ -641,7 +680,7 @@ extern "C" int32_t nml_nvfp4_sm100_routed_swiglu(const NmlSm100RoutedSwiglu* req
   int32_t status = launch_assignment_plan(
       request->expert_ids, sorted, block_experts, active, assignments,
       static_cast<int>(request->experts), request->expert_offset, static_cast<int>(w.positions),
-      static_cast<int>(w.blocks), stream, error_message, error_message_capacity);
+      static_cast<int>(w.blocks), device->device, stream, error_message, error_message_capacity);
   if (status != NML_SM100_OK) return status;
 
   ExpertArgs args;
@@ -671,7 +710,8 @@ extern "C" int32_t nml_nvfp4_sm100_routed_swiglu(const NmlSm100RoutedSwiglu* req
   // unit; the result rows go back to assignment order in the down epilogue (unpermute).
   const bool slot_ordered =
       static_cast<int64_t>(assignments) > kPermuteThreshold * request->experts &&
-      request->workspace_bytes >= w.total_permuted && get_kernel_policy() != 1 &&
+      request->workspace_bytes >= w.total_permuted &&
+      get_kernel_policy() != NML_SM100_POLICY_SIMT &&
       experts_umma_supported(args) && request->hidden_size % 8 == 0 &&
       request->intermediate_size % 64 == 0 &&
       reinterpret_cast<uintptr_t>(request->hidden) % 16 == 0;
@@ -809,7 +849,7 @@ extern "C" int32_t nml_nvfp4_sm100_routed_swiglu_static(const NmlSm100RoutedSwig
   int32_t status = launch_assignment_plan(
       request->expert_ids, sorted, block_experts, active, assignments,
       static_cast<int>(request->experts), request->expert_offset, static_cast<int>(w.positions),
-      static_cast<int>(w.blocks), stream, error_message, error_message_capacity);
+      static_cast<int>(w.blocks), device->device, stream, error_message, error_message_capacity);
   if (status != NML_SM100_OK) return status;
 
   ExpertArgs args;

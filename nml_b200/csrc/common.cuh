@@ -134,6 +134,10 @@ int32_t launch_linear_simt(const LinearArgs& args, const DeviceInfo& device, cha
 bool linear_umma_supported(const LinearArgs& args);
 int32_t launch_linear_umma(const LinearArgs& args, const DeviceInfo& device, char* message,
                            size_t capacity);
+// The weight-streaming kernel: few activation rows, K a multiple of 64 up to 4096.
+bool linear_stream_supported(const LinearArgs& args);
+int32_t launch_linear_stream(const LinearArgs& args, const DeviceInfo& device, char* message,
+                             size_t capacity);
 
 struct EmbeddingArgs {
   const void* indices;
@@ -180,6 +184,10 @@ int32_t launch_experts_simt(const ExpertArgs& args, const DeviceInfo& device, ch
 bool experts_umma_supported(const ExpertArgs& args);
 int32_t launch_experts_umma(const ExpertArgs& args, const DeviceInfo& device, char* message,
                             size_t capacity);
+// The weight-streaming kernel for decode-size batches (at most 16 slots per expert on average).
+bool experts_stream_supported(const ExpertArgs& args);
+int32_t launch_experts_stream(const ExpertArgs& args, const DeviceInfo& device, char* message,
+                              size_t capacity);
 
 int32_t launch_ep_push_rows(const NmlSm100EpPushRows& request, const DeviceInfo& device,
                             char* message, size_t capacity);

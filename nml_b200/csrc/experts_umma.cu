@@ -71,13 +71,9 @@ int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* me
   p.status = device.status_word;
   p.scale_buffer_bytes = scale_buffer_bytes;
   p.split_k = 1;
-  fill_decode_constants(&p.decode);
-#ifdef NML_SM100_PROFILE
-  p.knockout = std::getenv("NML_SM100_KNOCKOUT") ? std::atoi(std::getenv("NML_SM100_KNOCKOUT")) : 0;
-#endif
 
   auto kernel = gemm_kernel<BM, KS, PS, XS, WB, DG, MI, PA, WT, AFMT, T, MODE, XTMA>;
-  static bool configured[64] = {};
+  static std::atomic<int> configured[64];
   if (!reserve_smem(kernel, WT ? kSmemBudget : L::kSmemBytes, device.device, configured)) {
     return fail(NML_SM100_LAUNCH_FAILURE, "cannot reserve shared memory for the tcgen05 experts",
                 message, capacity);
@@ -102,9 +98,10 @@ int32_t launch_for_load(const ExpertArgs& args, const DeviceInfo& device, char* 
   // Decoded weights in tensor memory: every tile's block scales (128 rows x K/16 bytes) must
   // form a legal bulk copy and two such buffers must fit beside the rings.
   const int rows_per_expert = args.gate_up ? 2 * args.outputs : args.outputs;
-  const bool tmem_weights = get_kernel_policy() != 3 && rows_per_expert % 4 == 0 &&
+  const bool tmem_weights = get_kernel_policy() != NML_SM100_POLICY_UMMA_SMEM &&
+                            rows_per_expert % 4 == 0 &&
                             reinterpret_cast<uintptr_t>(args.block_scales) % 16 == 0;
-  if (tmem_weights && average <= 160 && AFMT == kAbf16 && get_kernel_policy() != 4) {
+  if (tmem_weights && average <= 160 && AFMT == kAbf16) {
     // bf16 operands through the byte table (32 KB of shared memory; slightly shallower rings)
     int32_t rc;
     if (average <= 16) {
@@ -185,27 +182,10 @@ bool experts_umma_supported(const ExpertArgs& args) {
          reinterpret_cast<uintptr_t>(args.block_scales) % 4 == 0;
 }
 
-#ifdef NML_SM100_DEBUG_WAITS
-extern "C" int nml_nvfp4_sm100_debug_waits(int* out) {
-  static int zero[160 * 11 * 8] = {};
-  if (cudaMemcpyFromSymbol(out, umma::g_wait_debug, sizeof(zero)) != cudaSuccess) return 1;
-  return cudaMemcpyToSymbol(umma::g_wait_debug, zero, sizeof(zero)) == cudaSuccess ? 0 : 1;
-}
-#endif
-
 int32_t launch_experts_umma(const ExpertArgs& args, const DeviceInfo& device, char* message,
                             size_t capacity) {
   return args.gate_up ? launch_mode<kGateUp>(args, device, message, capacity)
                       : launch_mode<kDown>(args, device, message, capacity);
 }
-
-#ifdef NML_SM100_PROFILE
-// Reads and clears the stall counters of the grouped kernels (tuning builds only).
-extern "C" int nml_nvfp4_sm100_profile_read_experts(unsigned long long* out24) {
-  unsigned long long zero[24] = {};
-  if (cudaMemcpyFromSymbol(out24, umma::g_profile, sizeof(zero)) != cudaSuccess) return 1;
-  return cudaMemcpyToSymbol(umma::g_profile, zero, sizeof(zero)) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 }  // namespace nml_sm100

@@ -30,7 +30,7 @@ int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* me
     total_tiles += (args.extra[i].outputs + kTileN - 1) / kTileN;
   }
   int split_k = 1;
-  if (BM <= 32 && args.rows <= BM && get_kernel_policy() != 5) {
+  if (BM <= 32 && args.rows <= BM && get_kernel_policy() != NML_SM100_POLICY_NO_SPLIT_K) {
     const int k_steps = args.inputs / kTileK;
     while (split_k < 4 && total_tiles * (split_k + 1) <= device.sm_count &&
            k_steps / (split_k + 1) >= 8) {
@@ -38,14 +38,10 @@ int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* me
     }
   }
   int smem_bytes = L::kSmemBytes + 2 * scale_buffer_bytes;
-  if (split_k > 1) {
-    const int with_partials = smem_bytes + (split_k - 1) * kTileN * BM * 4;
-    if (with_partials <= kSmemBudget) {
-      smem_bytes = with_partials;
-    } else {
-      split_k = 1;
-    }
-  }
+  // rank 0 keeps the f32 partial tiles of the other ranks behind the scale buffers: step the
+  // split down until they fit instead of giving it up
+  while (split_k > 1 && smem_bytes + (split_k - 1) * kTileN * BM * 4 > kSmemBudget) --split_k;
+  if (split_k > 1) smem_bytes += (split_k - 1) * kTileN * BM * 4;
   if (smem_bytes > kSmemBudget) return kDoesNotFit;
   CUtensorMap tmap_payload, tmap_x, tmap_extra[2];
   if (!encode_payload_map<KS>(&tmap_payload, args.payload, args.outputs, args.inputs) ||
@@ -88,13 +84,9 @@ int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* me
   p.output = args.output;
   p.status = device.status_word;
   p.scale_buffer_bytes = scale_buffer_bytes;
-  fill_decode_constants(&p.decode);
-#ifdef NML_SM100_PROFILE
-  p.knockout = std::getenv("NML_SM100_KNOCKOUT") ? std::atoi(std::getenv("NML_SM100_KNOCKOUT")) : 0;
-#endif
 
   auto kernel = gemm_kernel<BM, KS, PS, XS, WB, DG, MI, PA, WT, AFMT, T, kDense, true, SB>;
-  static bool configured[64] = {};
+  static std::atomic<int> configured[64];
   if (!reserve_smem(kernel, kSmemBudget, device.device, configured)) {
     return fail(NML_SM100_LAUNCH_FAILURE, "cannot reserve shared memory for the tcgen05 linear",
                 message, capacity);
@@ -162,15 +154,7 @@ int32_t launch_for_rows(const LinearArgs& args, const DeviceInfo& device, char* 
                         size_t capacity) {
   // Decoded weights in tensor memory: the unit's block scales (128 rows x K/16 bytes) must
   // form a legal bulk copy and two such buffers must fit beside the rings.
-  // Experiment hooks: policy 100 + BM forces the tile height (tensor-memory variant), 2000 +
-  // BM the same without the byte-table decode, 1000 + BM the shared-memory ring (1257: 256
-  // rows with per-stage scale copies); policy 4 turns the byte-table decode off.
   const int policy = get_kernel_policy();
-  const int forced_rows = policy >= 2000   ? policy - 2000
-                          : policy >= 1000 ? policy - 1000
-                          : policy >= 100  ? policy - 100
-                                           : 0;
-  const bool table_decode = policy != 4 && policy < 2000;
   bool bulk_scales_legal = args.outputs % 4 == 0 &&
                            reinterpret_cast<uintptr_t>(args.block_scales) % 16 == 0;
   int total_outputs = args.outputs;
@@ -179,12 +163,11 @@ int32_t launch_for_rows(const LinearArgs& args, const DeviceInfo& device, char* 
                         reinterpret_cast<uintptr_t>(args.extra[i].block_scales) % 16 == 0;
     total_outputs += args.extra[i].outputs;
   }
-  const bool tmem_weights = policy != 3 && (policy < 1000 || policy >= 2000) && bulk_scales_legal;
-  if (tmem_weights && AFMT == kAbf16 && table_decode) {
+  const bool tmem_weights = policy != NML_SM100_POLICY_UMMA_SMEM && bulk_scales_legal;
+  if (tmem_weights && AFMT == kAbf16) {
     // bf16 operands through the byte table (32 KB of shared memory; slightly shallower rings)
     int32_t rc = kDoesNotFit;
-    switch (forced_rows ? forced_rows
-                        : choose_tile_rows(args.rows, total_outputs, device.sm_count, true)) {
+    switch (choose_tile_rows(args.rows, total_outputs, device.sm_count, true)) {
       case 16:
         rc = launch_config<16, 4, 6, 4, 8, 3, 2, 8, true, kAbf16Lut, T>(args, device, message,
                                                                         capacity);
@@ -212,8 +195,7 @@ int32_t launch_for_rows(const LinearArgs& args, const DeviceInfo& device, char* 
   }
   if (tmem_weights) {
     int32_t rc = kDoesNotFit;
-    switch (forced_rows ? forced_rows
-                        : choose_tile_rows(args.rows, total_outputs, device.sm_count, true)) {
+    switch (choose_tile_rows(args.rows, total_outputs, device.sm_count, true)) {
       case 16:
         rc = launch_config<16, 4, 6, 4, 8, 3, 2, 8, true, AFMT, T>(args, device, message, capacity);
         break;
@@ -236,9 +218,7 @@ int32_t launch_for_rows(const LinearArgs& args, const DeviceInfo& device, char* 
     }
     if (rc != kDoesNotFit) return rc;
   }
-  switch (forced_rows && forced_rows != 192 && forced_rows != 257
-              ? forced_rows
-              : choose_tile_rows(args.rows, total_outputs, device.sm_count, false)) {
+  switch (choose_tile_rows(args.rows, total_outputs, device.sm_count, false)) {
     case 16:
       return launch_config<16, 4, 5, 4, 4, 3, 1, 8, false, AFMT, T>(args, device, message,
                                                                     capacity);
@@ -254,7 +234,7 @@ int32_t launch_for_rows(const LinearArgs& args, const DeviceInfo& device, char* 
     default: {
       // 256-row tiles: scales by bulk copy when the two buffers fit beside three activation
       // stages (K <= ~2900) and the copy is legal; else per-stage 4-byte copies
-      if (bulk_scales_legal && policy != 1257) {
+      if (bulk_scales_legal) {
         const int32_t rc = launch_config<256, 1, 4, 3, 4, 3, 1, 1, false, AFMT, T, true>(
             args, device, message, capacity);
         if (rc != kDoesNotFit) return rc;
@@ -287,14 +267,5 @@ int32_t launch_linear_umma(const LinearArgs& args, const DeviceInfo& device, cha
   }
   return launch_for_rows<kAbf16, __nv_bfloat16>(args, device, message, capacity);
 }
-
-#ifdef NML_SM100_PROFILE
-// Reads and clears the stall counters of the dense kernels (tuning builds only).
-extern "C" int nml_nvfp4_sm100_profile_read(unsigned long long* out16) {
-  unsigned long long zero[24] = {};
-  if (cudaMemcpyFromSymbol(out16, umma::g_profile, sizeof(zero)) != cudaSuccess) return 1;
-  return cudaMemcpyToSymbol(umma::g_profile, zero, sizeof(zero)) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 }  // namespace nml_sm100

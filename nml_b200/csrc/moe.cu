@@ -1,6 +1,8 @@
 // Routed-expert support kernels: top-k routing, the assignment schedule, the portable SIMT
 // expert projections and the k-way combine.  The tcgen05 expert projections live in
 // experts_umma.cu; everything here is integer/elementwise work or the any-shape fallback.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace nml_sm100 {
@@ -427,21 +429,20 @@ int32_t launch_route(const NmlSm100Route& r, char* message, size_t capacity) {
 int32_t launch_assignment_plan(const int32_t* expert_ids, int32_t* sorted_assignments,
                                int32_t* block_experts, int32_t* active_blocks, int assignments,
                                int experts, int expert_offset, int positions, int blocks,
-                               cudaStream_t stream, char* message, size_t capacity) {
+                               int device, cudaStream_t stream, char* message, size_t capacity) {
   // threads * experts histogram words must fit the shared memory requested below.
   int threads = 1024;
   while (threads > 32 && static_cast<int64_t>(threads) * experts > 32768) threads >>= 1;
   const size_t smem = (static_cast<size_t>(threads) * experts + 2 * experts + 2) * 4;
-  static bool configured[64] = {};
-  int device = 0;
-  cudaGetDevice(&device);
-  if (device >= 0 && device < 64 && !configured[device]) {
+  static std::atomic<int> configured[64];
+  const bool known = device >= 0 && device < 64;
+  if (!known || !configured[device].load(std::memory_order_acquire)) {
     if (cudaFuncSetAttribute(assignment_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              144 * 1024) != cudaSuccess) {
       return fail(NML_SM100_LAUNCH_FAILURE, "cannot reserve shared memory for the plan kernel",
                   message, capacity);
     }
-    configured[device] = true;
+    if (known) configured[device].store(1, std::memory_order_release);
   }
   assignment_plan_kernel<<<1, threads, smem, stream>>>(expert_ids, sorted_assignments,
                                                        block_experts, active_blocks, assignments,

@@ -26,18 +26,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void* ptr) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(ptr));
 }
 
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred = 0;
-  asm volatile(
-      "{\n"
-      ".reg .pred px;\n"
-      "elect.sync _|px, 0xffffffff;\n"
-      "selp.b32 %0, 1, 0, px;\n"
-      "}\n"
-      : "=r"(pred));
-  return pred != 0;
-}
-
 // ---- mbarrier -------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count)
@@ -125,11 +113,6 @@ __device__ __forceinline__ void cp_async_4(void* dst, const void* src) {
                : "memory");
 }
 
-__device__ __forceinline__ void cp_async_16(void* dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src)
-               : "memory");
-}
-
 // 16-byte copy that writes zeros when `valid` is false (src-size 0).
 __device__ __forceinline__ void cp_async_16_zfill(void* dst, const void* src, bool valid) {
   const uint32_t size = valid ? 16u : 0u;
@@ -169,30 +152,6 @@ __device__ __forceinline__ void tcgen05_fence_before_sync() {
 
 __device__ __forceinline__ void tcgen05_fence_after_sync() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-
-// D[tmem] (+)= A[smem] * B[smem], 16-bit floating inputs, f32 accumulate.
-// Issued by a single thread.
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
-                                         uint32_t idesc, bool accumulate) {
-  const uint32_t acc = accumulate ? 1u : 0u;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-      "}\n"
-      :
-      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc)
-      : "memory");
-}
-
-// Makes `bar` receive one arrival when every MMA issued so far by this thread
-// has completed (implies tcgen05.fence::before_thread_sync).
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   smem_u32(bar))
-               : "memory");
 }
 
 // ---- thread-block clusters ---------------------------------------------------------
@@ -373,65 +332,12 @@ __device__ __forceinline__ void tmem_store_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-// ---- UMMA descriptors ---------------------------------------------------------
-// Shared-memory operand descriptor for a K-major tile stored as rows of 128
-// bytes with the 128-byte swizzle (16-byte chunk index XOR row-in-group-of-8),
-// groups of 8 rows 1024 bytes apart.  The tile base must be 1024-byte aligned;
-// stepping along K inside the 128-byte row adds the byte offset to the start
-// address field.
-__device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_address) {
-  uint64_t desc = 0;
-  desc |= static_cast<uint64_t>((smem_address & 0x3ffffu) >> 4);  // start address, 16-byte units
-  desc |= static_cast<uint64_t>(1) << 16;                          // leading byte offset (unused)
-  desc |= static_cast<uint64_t>(1024 >> 4) << 32;                  // stride between 8-row groups
-  desc |= static_cast<uint64_t>(1) << 46;                          // descriptor version (sm_100)
-  desc |= static_cast<uint64_t>(2) << 61;                          // 128-byte swizzle
-  return desc;
-}
-
 // The same descriptor split in halves: only the low word (start address, leading offset)
 // changes between operand tiles, so an issue loop keeps the high word constant.
 constexpr uint32_t kUmmaDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
 
 __device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_address) {
   return ((smem_address & 0x3ffffu) >> 4) | (1u << 16);
-}
-
-__device__ __forceinline__ void umma_f16_split(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo,
-                                               uint32_t desc_hi, uint32_t idesc,
-                                               bool accumulate) {
-  const uint32_t acc = accumulate ? 1u : 0u;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      ".reg .b64 da, db;\n"
-      "setp.ne.b32 p, %5, 0;\n"
-      "mov.b64 da, {%1, %3};\n"
-      "mov.b64 db, {%2, %3};\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n"
-      "}\n"
-      :
-      : "r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(acc)
-      : "memory");
-}
-
-// A operand in tensor memory (lane = row of A, 32-bit column c = elements 2c and 2c + 1 of
-// the K = 16 slice), B operand in shared memory.
-__device__ __forceinline__ void umma_f16_tmem_a(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo,
-                                                uint32_t desc_hi, uint32_t idesc,
-                                                bool accumulate) {
-  const uint32_t acc = accumulate ? 1u : 0u;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      ".reg .b64 db;\n"
-      "setp.ne.b32 p, %5, 0;\n"
-      "mov.b64 db, {%2, %3};\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n"
-      "}\n"
-      :
-      : "r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(acc)
-      : "memory");
 }
 
 // Untiled bulk copy global -> shared; both addresses and the size are multiples of 16 bytes.

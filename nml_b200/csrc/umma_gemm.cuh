@@ -33,6 +33,7 @@
 // can advance again) or has itself consumed the previous phase.
 #pragma once
 
+#include <atomic>
 #include <type_traits>
 
 #include "common.cuh"
@@ -114,14 +115,6 @@ struct Layout {
   static_assert(KS == 1 || KS == 2 || KS == 4, "K steps per stage");
 };
 
-// Shift amounts as multipliers that the compiler cannot see through.  The decode is bound by
-// the half-rate integer pipe (logic, shift, byte-permute); a multiply by a power of two held
-// in a register issues on the FMA pipe instead, which the decode otherwise barely uses.
-struct DecodeConstants {
-  uint32_t mul4, mul16, mul64, mul256, mul4096;  // left shifts by 2, 4, 6, 8, 12
-  uint32_t hi26, hi30;                           // mul.hi by 2^26, 2^30: right shifts by 6, 2
-};
-
 // The one place that maps a kernel instantiation to its shared-memory layout; the kernel and
 // its launchers both use it, so the launch can never reserve less than the kernel addresses.
 template <int BM, int KS, int PS, int XS, int WB, bool WT, int AFMT, int MODE, bool SB>
@@ -166,8 +159,6 @@ struct Params {
   int split_k;  // 1: no split
   int* status;
   int scale_buffer_bytes;  // WT: bytes of one scale buffer (128 rows x K / 16, 128-aligned)
-  DecodeConstants decode;  // see DecodeConstants; filled by fill_decode_constants()
-  int knockout;  // tuning builds only: bit 0 skips the decode arithmetic, bit 1 the MMA issue
 };
 
 // One unit of work: a 128-row weight tile against BM activation rows / schedule slots.
@@ -234,36 +225,13 @@ __device__ __forceinline__ void scales2_f16(uint32_t two_bytes, uint32_t& first,
 // read as value * 2^-126 (0.5 is the bf16 subnormal); the sign goes to bit 15.  Nibble i of
 // each 16-bit half (codes i and i + 4) needs its own pair of shifts; all come from the one
 // payload word, so there is no dependent shift chain.
-__device__ __forceinline__ void decode8_bf16(uint32_t q, uint32_t scale2, uint32_t (&out)[4],
-                                             const DecodeConstants& c) {
+__device__ __forceinline__ void decode8_bf16(uint32_t q, uint32_t scale2, uint32_t (&out)[4]) {
   constexpr uint32_t kSign = 0x80008000u, kMagnitude = 0x01c001c0u;
   uint32_t t[4];
-#ifndef NML_DECODE_VARIANT
-#define NML_DECODE_VARIANT 3
-#endif
-#if NML_DECODE_VARIANT == 0
-  uint32_t w = q;
-#pragma unroll
-  for (int i = 3; i >= 0; --i) {
-    t[i] = (w & kSign) | ((w & 0x70007000u) >> 6);
-    w <<= 4;
-  }
-#elif NML_DECODE_VARIANT == 1
-  t[3] = (q & kSign) | (__umulhi(q, c.hi26) & kMagnitude);
-  t[2] = ((q * c.mul16) & kSign) | (__umulhi(q, c.hi30) & kMagnitude);
-  t[1] = ((q * c.mul256) & kSign) | ((q * c.mul4) & kMagnitude);
-  t[0] = ((q * c.mul4096) & kSign) | ((q * c.mul64) & kMagnitude);
-#elif NML_DECODE_VARIANT == 2
-  t[3] = (q & kSign) | ((q >> 6) & kMagnitude);
-  t[2] = ((q * c.mul16) & kSign) | ((q >> 2) & kMagnitude);
-  t[1] = ((q * c.mul256) & kSign) | ((q * c.mul4) & kMagnitude);
-  t[0] = ((q * c.mul4096) & kSign) | ((q * c.mul64) & kMagnitude);
-#else
   t[3] = (q & kSign) | ((q >> 6) & kMagnitude);
   t[2] = ((q << 4) & kSign) | ((q >> 2) & kMagnitude);
   t[1] = ((q << 8) & kSign) | ((q << 2) & kMagnitude);
   t[0] = ((q << 12) & kSign) | ((q << 6) & kMagnitude);
-#endif
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(t[i]) : "r"(scale2));
@@ -306,8 +274,7 @@ __device__ __forceinline__ void scales4_bf16_true(uint32_t four_bytes, uint32_t 
 
 // Four E4M3 scale bytes -> four words holding bf16(scale * 2^119) in both halves: a byte's
 // value bits at bf16 bits 10:4 read as scale * 2^-120; two exact bf16 multiplies rescale.
-__device__ __forceinline__ void scales4_bf16(uint32_t four_bytes, uint32_t (&scale)[4],
-                                             const DecodeConstants& c) {
+__device__ __forceinline__ void scales4_bf16(uint32_t four_bytes, uint32_t (&scale)[4]) {
   const uint32_t two_p120 = 0x7b807b80u;
   const uint32_t two_p119 = 0x7b007b00u;
   uint32_t pair[2];
@@ -315,7 +282,7 @@ __device__ __forceinline__ void scales4_bf16(uint32_t four_bytes, uint32_t (&sca
   pair[1] = __byte_perm(four_bytes, 0u, 0x4342);
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    pair[i] = (pair[i] & 0x007f007fu) * c.mul16;
+    pair[i] = (pair[i] & 0x007f007fu) << 4;
     asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(pair[i]) : "r"(two_p120));
     asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(pair[i]) : "r"(two_p119));
     scale[2 * i] = __byte_perm(pair[i], pair[i], 0x1010);
@@ -358,6 +325,9 @@ __device__ __forceinline__ void build_groups(Groups* groups, const Params& p, in
   }
   __syncwarp();
   const int count = min(starts, kMaxGroups);
+  // A schedule with more runs of equal experts than the table holds (blocks not sorted by
+  // expert) cannot be walked completely: report it instead of dropping the tail silently.
+  if (lane == 0 && starts > kMaxGroups) atomicOr(p.status, NML_SM100_STATUS_INDEX_RANGE);
   if (lane == 0) {
     int prefix = 0;
     for (int g = 0; g < count; ++g) {
@@ -423,25 +393,6 @@ __device__ __forceinline__ Unit get_unit(const Params& p, const Groups* groups, 
   return u;
 }
 
-// Stall accounting for tuning, compiled only with -DNML_SM100_PROFILE: cycles each role
-// leader spends in each wait, summed over CTAs into g_profile (read through
-// nml_nvfp4_sm100_profile_read in the translation unit that owns the kernel).
-#ifdef NML_SM100_PROFILE
-static __device__ unsigned long long g_profile[24];
-#define NML_PROF_DECL unsigned long long prof_acc[4] = {0, 0, 0, 0}; long long prof_t0 = 0;
-#define NML_PROF_BEGIN() prof_t0 = clock64()
-#define NML_PROF_END(slot) prof_acc[slot] += static_cast<unsigned long long>(clock64() - prof_t0)
-#define NML_PROF_FLUSH(base, leader)                                        \
-  if (leader) {                                                             \
-    for (int i = 0; i < 4; ++i) atomicAdd(&g_profile[(base) + i], prof_acc[i]); \
-  }
-#else
-#define NML_PROF_DECL
-#define NML_PROF_BEGIN()
-#define NML_PROF_END(slot)
-#define NML_PROF_FLUSH(base, leader)
-#endif
-
 // Which bounded wait ran out: bit (8 + site) of the device status word.
 enum WaitSite : int {
   kSiteProducerRaw = 0,
@@ -457,11 +408,6 @@ enum WaitSite : int {
   kSiteGather = 10,
 };
 
-#ifdef NML_SM100_DEBUG_WAITS
-// Where each role of each CTA stood when a wait ran out (diagnostic builds only).
-static __device__ int g_wait_debug[160][11][8];
-struct WaitPosition { int unit = -1, stage = -1, step = -1; };
-#endif
 
 struct RingState {
   int index = 0;
@@ -540,9 +486,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
   uint64_t* full_scale = tmem_empty + 2;   // [2] (WT)
   uint64_t* empty_scale = full_scale + 2;  // [2] (WT)
   uint64_t* partial_full = empty_scale + 2;  // [1] (split K, rank 0: partial tiles have landed)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(partial_full + 1);
+  uint64_t* mma_drained = partial_full + 1;  // [1] every MMA of this CTA has completed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mma_drained + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  static_assert((2 * PS + 2 * XS + 2 * WB + 9) * 8 + 8 <= L::kBarrierBytes, "barrier area");
+  static_assert((2 * PS + 2 * XS + 2 * WB + 10) * 8 + 8 <= L::kBarrierBytes, "barrier area");
   Groups* groups = reinterpret_cast<Groups*>(smem + L::kBarrierOffset + L::kBarrierBytes);
   uint64_t* x_free = kSharedEmpty ? empty_w : empty_x;
   // Per-unit weight operands: in dense mode they come from the unit's segment.
@@ -583,6 +530,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       mbar_init(&empty_scale[a], 4 * DG);
     }
     mbar_init(partial_full, p.split_k > 1 ? (p.split_k - 1) * kEpilogueWarps : 1);
+    mbar_init(mma_drained, MI);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -645,36 +593,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     atomicOr(p.status, NML_SM100_STATUS_BARRIER_TIMEOUT | (0x100 << site));
   };
   // Bounded wait that also honours an abort raised by another role.
-#ifdef NML_SM100_DEBUG_WAITS
-  WaitPosition wait_position;
-  auto record = [&](uint64_t* bar, uint32_t parity, int site, int how) {
-    if (blockIdx.x < 160 && (threadIdx.x & 31) == 0) {
-      int* d = g_wait_debug[blockIdx.x][site];
-      d[0] = how;
-      d[1] = wait_position.unit;
-      d[2] = wait_position.stage;
-      d[3] = wait_position.step;
-      d[4] = static_cast<int>(bar - bars);
-      d[5] = static_cast<int>(parity);
-      d[6] = threadIdx.x >> 5;
-      d[7] = static_cast<int>(*reinterpret_cast<volatile uint64_t*>(bar) & 0xffffffffu);
-    }
-  };
-#endif
   auto wait = [&](uint64_t* bar, uint32_t parity, int site) -> bool {
     if (mbar_try_wait(bar, parity)) return true;  // fast path: no shared-memory flag read
     for (uint32_t poll = 0; poll < kWaitPolls; ++poll) {
       if (mbar_try_wait(bar, parity)) return true;
       if ((poll & 63u) == 63u && *abort_flag) {
-#ifdef NML_SM100_DEBUG_WAITS
-        record(bar, parity, site, 2);
-#endif
         return false;
       }
     }
-#ifdef NML_SM100_DEBUG_WAITS
-    record(bar, parity, site, 1);
-#endif
     give_up(site);
     return false;
   };
@@ -684,12 +610,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     int issued = 0;
     int local = 0;
     bool ok = true;
-    NML_PROF_DECL
     for (int index = first_unit; index < units && ok; index += unit_stride, ++local) {
       const Unit u = get_unit<BM, GROUPED>(p, groups, index);
-#ifdef NML_SM100_DEBUG_WAITS
-      wait_position.unit = local;
-#endif
       if constexpr (kBulk) {
         // all block scales of the unit's weight rows: one contiguous range of the tensor
         const int b = local & 1;
@@ -704,15 +626,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         }
       }
       for (int rs = 0; rs < stages; ++rs) {
-        NML_PROF_BEGIN();
-#ifdef NML_SM100_DEBUG_WAITS
-        wait_position.stage = rs;
-#endif
         if (!wait(&empty_p[ps.index], ps.phase ^ 1u, kSiteProducerRaw)) {
           ok = false;
           break;
         }
-        NML_PROF_END(0);
         if (lane == 0) {
           mbar_arrive_expect_tx(&full_p[ps.index], L::kPayloadBytes);
           tma_load_2d(payload_tile(ps.index), payload_map(u), &full_p[ps.index],
@@ -754,7 +671,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         if (!mbar_wait(&full_scale[unit & 1], (unit >> 1) & 1)) give_up(kSiteProducerDrain);
       }
     }
-    NML_PROF_FLUSH(0, lane == 0)
   } else if (XTMA && warp == kGatherWarp0) {
     // ------------------------------------------------------- activation producer
     if constexpr (XTMA) {
@@ -824,55 +740,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       int sequence = 0;  // K steps seen so far by this CTA, over all units
       const uint64_t w_desc = desc_hi | (WT ? 0u : umma_desc_lo(smem_u32(w_tile(0))));
       const uint64_t x_desc = desc_hi | umma_desc_lo(smem_u32(x_tile(0, 0)));
-      NML_PROF_DECL
-#ifdef NML_SM100_PROFILE
-      const long long prof_start = clock64();
-      unsigned long long prof_fine[4] = {0, 0, 0, 0};
-#endif
       for (int index = first_unit; index < units; index += unit_stride, ++local) {
+        // After a timeout anywhere in the CTA nothing further is issued: the waits below have
+        // become no-ops and the operands would not be ready.
+        if (__shfl_sync(0xffffffffu, *abort_flag, 0) != 0) break;
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
-        NML_PROF_BEGIN();
-#ifdef NML_SM100_DEBUG_WAITS
-        wait_position.unit = local;
-#endif
         mbar_wait_or_abort(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, p.status,
                            kSiteMmaAccumulator);
-#ifdef NML_SM100_DEBUG_WAITS
-        if (*abort_flag && issuer == 0) record(&tmem_empty[acc], acc_phase ^ 1u, kSiteMmaAccumulator, 3);
-#endif
-        NML_PROF_END(0);
         tcgen05_fence_after_sync();
         const uint32_t d_base = tmem_base + acc * PA * BM;
         int step = 0;  // K step inside the unit
         for (int rs = 0; rs < stages; ++rs) {
-          NML_PROF_BEGIN();
-#ifdef NML_SM100_DEBUG_WAITS
-          wait_position.stage = rs;
-#endif
           mbar_wait_or_abort(&full_x[xs.index], xs.phase, abort_flag, p.status,
                              kSiteMmaRaw);
-#ifdef NML_SM100_DEBUG_WAITS
-          if (*abort_flag && g_wait_debug[blockIdx.x & 127][kSiteMmaRaw + issuer * 0][0] == 0) {
-            record(&full_x[xs.index], xs.phase, issuer == 0 ? kSiteMmaRaw : kSiteMmaAccumulator, 3);
-          }
-#endif
-          NML_PROF_END(1);
           const int sub_steps = min(KS, k_count - rs * KS);
           for (int j = 0; j < sub_steps; ++j, ++step, ++sequence, wb.advance<WB>()) {
             if (MI == 2 && (sequence & 1) != issuer) continue;
-            NML_PROF_BEGIN();
-#ifdef NML_SM100_DEBUG_WAITS
-            wait_position.step = step;
-#endif
             mbar_wait_or_abort(&full_w[wb.index], wb.phase, abort_flag, p.status,
                                kSiteMmaWeights);
-#ifdef NML_SM100_DEBUG_WAITS
-            if (*abort_flag && g_wait_debug[blockIdx.x & 127][issuer == 0 ? kSiteMmaWeights : kSiteProducerDrain][0] == 0) {
-              record(&full_w[wb.index], wb.phase, issuer == 0 ? kSiteMmaWeights : kSiteProducerDrain, 3);
-            }
-#endif
-            NML_PROF_END(2);
             // Orders the MMAs after the decode threads' tensor-memory stores.  A decoded tile
             // in shared memory needs no such fence: its writers fenced the async proxy before
             // they arrived on the barrier.
@@ -883,10 +769,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
             const uint64_t a_desc = w_desc + wb.index * (kWBytes >> 4);
             const uint64_t b_desc =
                 x_desc + xs.index * (L::kXStageBytes >> 4) + j * (L::kXBytes >> 4);
-#ifdef NML_SM100_PROFILE
-            const long long issue_t0 = clock64();
-            if (!(p.knockout & 2))
-#endif
 #pragma unroll
             for (int q = 0; q < kTileK / kUmmaK; ++q) {
               const int instruction = step * (kTileK / kUmmaK) + q;
@@ -906,37 +788,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
                 umma_f16_elect(d, a_desc + 2 * q, b_desc + 2 * q, idesc, accumulate);
               }
             }
-#ifdef NML_SM100_PROFILE
-            const long long issue_t1 = clock64();
-#endif
             umma_commit_elect(&empty_w[wb.index]);
-#ifdef NML_SM100_PROFILE
-            prof_fine[0] += static_cast<unsigned long long>(issue_t1 - issue_t0);
-            prof_fine[1] += static_cast<unsigned long long>(clock64() - issue_t1);
-#endif
           }
           if constexpr (!kSharedEmpty) {
-#ifdef NML_SM100_PROFILE
-            const long long commit_t0 = clock64();
-#endif
             umma_commit_elect(&empty_x[xs.index]);
-#ifdef NML_SM100_PROFILE
-            prof_fine[2] += static_cast<unsigned long long>(clock64() - commit_t0);
-#endif
           }
           xs.advance<XS>();
         }
         umma_commit_elect(&tmem_full[acc]);
       }
-#ifdef NML_SM100_PROFILE
-      prof_acc[3] = static_cast<unsigned long long>(clock64() - prof_start);
-#endif
-      NML_PROF_FLUSH(4, issuer == 0 && lane == 0)
-#ifdef NML_SM100_PROFILE
-      if (issuer == 0 && lane == 0) {
-        for (int i = 0; i < 4; ++i) atomicAdd(&g_profile[16 + i], prof_fine[i]);
-      }
-#endif
+      // Tensor memory and the barriers may only be released once every MMA this warp issued
+      // (and the arrival of its commits) has completed, also on the abort path.
+      umma_commit_elect(mma_drained);
+      if (!mbar_wait(mma_drained, 0)) give_up(kSiteMmaAccumulator);
     }
     __syncwarp();
   } else if (warp < kDecodeWarp0) {
@@ -949,18 +813,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     int out_columns = p.N;
     const int row = quarter * 32 + lane;  // row of the weight tile this thread reads
     int local = 0;
-    NML_PROF_DECL
     for (int index = first_unit; index < units; index += unit_stride, ++local) {
       const Unit u = get_unit<BM, GROUPED>(p, groups, index);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
-      NML_PROF_BEGIN();
-#ifdef NML_SM100_DEBUG_WAITS
-      wait_position.unit = local;
-#endif
       if (!wait(&tmem_full[acc], acc_phase, kSiteEpilogue)) break;
-      NML_PROF_END(0);
-      NML_PROF_BEGIN();
       tcgen05_fence_after_sync();
       // Grouped modes that address the output by assignment keep the unit's slot -> (assignment,
       // routing weight) map in a table private to this warp, filled with coalesced loads.
@@ -1131,9 +988,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
           cluster_mbar_arrive(cluster_map_shared(smem_u32(partial_full), 0));
         }
       }
-      NML_PROF_END(1);
     }
-    NML_PROF_FLUSH(8, threadIdx.x == 64)
   } else if (warp < kGatherWarp0) {
     // -------------------------------------------------------------------- decode
     const int dt = threadIdx.x - kDecodeWarp0 * 32;
@@ -1146,9 +1001,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     int turn = 0;      // the decode group whose K step `sequence` is
     bool ok = true;
     int local = 0;
-    const DecodeConstants dc = p.decode;
     const uint8_t* lut_lane = smem + L::kLutOffset + lane * 4;  // this lane's copy of the table
-    NML_PROF_DECL
     for (int index = first_unit; index < units && ok; index += unit_stride, ++local) {
       const uint8_t* unit_scales = nullptr;
       if constexpr (kBulk) {
@@ -1156,33 +1009,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         unit_scales = scale_buffer(local & 1) + row * p.scale_width;
       }
       for (int rs = 0; rs < stages && ok; ++rs) {
-        NML_PROF_BEGIN();
-#ifdef NML_SM100_DEBUG_WAITS
-        wait_position.unit = local;
-        wait_position.stage = rs;
-#endif
         if (!wait(&full_p[ps.index], ps.phase, kSiteDecodeRaw)) {
           ok = false;
           break;
         }
-        NML_PROF_END(0);
         const int sub_steps = min(KS, k_count - rs * KS);
         for (int j = 0; j < sub_steps;
              ++j, ++sequence, turn = turn + 1 == DG ? 0 : turn + 1, wb.advance<WB>()) {
           if (turn != group) continue;  // turn == sequence % DG
-#ifdef NML_SM100_DEBUG_WAITS
-          wait_position.step = sequence;
-#endif
           if constexpr (!WT) {
             // the decoded tile is written as it is computed: the slot must be free first
-            NML_PROF_BEGIN();
             if (!wait(&empty_w[wb.index], wb.phase ^ 1u, kSiteDecodeWeights)) {
               ok = false;
               break;
             }
-            NML_PROF_END(1);
           }
-          NML_PROF_BEGIN();
           uint4 codes[2];
           if constexpr (KS == 1) {
             // rows of 32 bytes, 32-byte swizzled by the TMA load (16-byte halves of rows 4..7
@@ -1208,7 +1049,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
           } else if constexpr (kLut) {
             scales4_bf16_true(four_scales, scale);
           } else {
-            scales4_bf16(four_scales, scale, dc);
+            scales4_bf16(four_scales, scale);
+          }
+          // Scale bytes the format does not define (sign bit set, 0x7f) poison their block
+          // with NaN like the reference device kernels (turing_adapter.cu:35-40); 0x7fff is a
+          // NaN in f16 and in bf16, and NaN times any code, zero included, stays NaN.
+          const uint32_t invalid =
+              (four_scales | ((four_scales & 0x7f7f7f7fu) + 0x01010101u)) & 0x80808080u;
+          if (invalid != 0u) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              if (invalid & (0x80u << (8 * i))) scale[i] = 0x7fff7fffu;
+            }
           }
           const uint32_t words[8] = {codes[0].x, codes[0].y, codes[0].z, codes[0].w,
                                      codes[1].x, codes[1].y, codes[1].z, codes[1].w};
@@ -1225,19 +1077,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
                 } else if constexpr (kLut) {
                   decode8_bf16_lut(words[2 * pair + half], scale[pair], q4, lut_lane);
                 } else {
-                  decode8_bf16(words[2 * pair + half], scale[pair], q4, dc);
+                  decode8_bf16(words[2 * pair + half], scale[pair], q4);
                 }
 #pragma unroll
                 for (int i = 0; i < 4; ++i) o[pair][4 * half + i] = q4[i];
               }
             }
-            NML_PROF_END(2);
-            NML_PROF_BEGIN();
             if (!wait(&empty_w[wb.index], wb.phase ^ 1u, kSiteDecodeWeights)) {
               ok = false;
               break;
             }
-            NML_PROF_END(1);
             // 32-bit column c of this thread's lane holds elements 2c and 2c + 1 of the row
             const uint32_t w_address = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
                                        kAccColumns + wb.index * kWColumns;
@@ -1262,7 +1111,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
               } else if constexpr (kLut) {
                 decode8_bf16_lut(words[jj], scale[jj >> 1], o, lut_lane);
               } else {
-                decode8_bf16(words[jj], scale[jj >> 1], o, dc);
+                decode8_bf16(words[jj], scale[jj >> 1], o);
               }
               const int chunk = jj ^ (row & 7);
               *reinterpret_cast<uint4*>(w_row + chunk * 16) = make_uint4(o[0], o[1], o[2], o[3]);
@@ -1272,7 +1121,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
           // one arrival per warp: 128 arrivals on one barrier word serialise
           __syncwarp();
           if (lane == 0) mbar_arrive(&full_w[wb.index]);
-          NML_PROF_END(2);
         }
         // this warp has read its last byte of the stage
         __syncwarp();
@@ -1285,7 +1133,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         if (lane == 0) mbar_arrive(&empty_scale[local & 1]);
       }
     }
-    NML_PROF_FLUSH(12, dt == 0)
   } else {
     // -------------------------------------------------------------------- gather
     if constexpr (!XTMA) {
@@ -1302,7 +1149,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       RingState xs, arrive;
       int in_flight = 0;
       bool ok = true;
-      NML_PROF_DECL
       auto retire = [&](int keep) {
         while (in_flight > keep) {
           if (in_flight - 1 >= 2) {
@@ -1335,17 +1181,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
           source_offset[i] = offset;
         }
         for (int rs = 0; rs < stages; ++rs) {
-          NML_PROF_BEGIN();
-#ifdef NML_SM100_DEBUG_WAITS
-          wait_position.stage = rs;
-          wait_position.step = in_flight;
-#endif
           if (!wait(&x_free[xs.index], xs.phase ^ 1u, kSiteGather)) {
             ok = false;
             break;
           }
-          NML_PROF_END(0);
-          NML_PROF_BEGIN();
 #pragma unroll
           for (int j = 0; j < KS; ++j) {
             const int k_step = rs * KS + j;
@@ -1363,14 +1202,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
           asm volatile("cp.async.commit_group;" ::: "memory");
           ++in_flight;
           xs.advance<XS>();
-          NML_PROF_END(1);
-          NML_PROF_BEGIN();
           retire(kLag);
-          NML_PROF_END(2);
         }
       }
       retire(0);
-      NML_PROF_FLUSH(20, t == 0)
     }
   }
 
@@ -1467,26 +1302,20 @@ inline bool encode_activation_map(CUtensorMap* map, const void* x, int64_t rows,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-inline void fill_decode_constants(DecodeConstants* c) {
-  c->mul4 = 4u;
-  c->mul16 = 16u;
-  c->mul64 = 64u;
-  c->mul256 = 256u;
-  c->mul4096 = 4096u;
-  c->hi26 = 1u << 26;
-  c->hi30 = 1u << 30;
-}
-
 // Opts a kernel into its dynamic shared memory once per device.  `configured` is the
-// caller's per-kernel table (one static array per kernel instantiation).
+// caller's per-kernel table (one static array per kernel instantiation); concurrent first
+// calls may both set the attribute, which is harmless, and later calls see the flag.
 template <typename Kernel>
-inline bool reserve_smem(Kernel kernel, int bytes, int device, bool (&configured)[64]) {
-  if (device >= 0 && device < 64 && configured[device]) return true;
+inline bool reserve_smem(Kernel kernel, int bytes, int device,
+                         std::atomic<int> (&configured)[64]) {
+  if (device >= 0 && device < 64 && configured[device].load(std::memory_order_acquire)) {
+    return true;
+  }
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) !=
       cudaSuccess) {
     return false;
   }
-  if (device >= 0 && device < 64) configured[device] = true;
+  if (device >= 0 && device < 64) configured[device].store(1, std::memory_order_release);
   return true;
 }
 

@@ -360,10 +360,13 @@ _WORKSPACES: dict = {}
 def routed_experts(hidden: torch.Tensor, expert_ids: torch.Tensor,
                    routing_weights: torch.Tensor, gate_up: NvFp4Parameter,
                    gate_up_bias: torch.Tensor, down: NvFp4Parameter, down_bias: torch.Tensor,
-                   expert_offset: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
+                   expert_offset: int = 0, out: torch.Tensor | None = None,
+                   workspace: torch.Tensor | None = None) -> torch.Tensor:
     """The routed layer from given routes, one C-ABI call (plan, gate/up + SwiGLU, down,
     k-way sum); the unit of the reference's CPU target ``nml.nvfp4.routed_swiglu``
-    (crates/nml-kernel-nvfp4/src/ffi.rs:228-428)."""
+    (crates/nml-kernel-nvfp4/src/ffi.rs:228-428).  ``workspace`` (u8, 256-byte aligned, at
+    least ``nml_nvfp4_sm100_routed_swiglu_workspace_bytes``) replaces the cached scratch
+    buffer, e.g. to inspect the intermediates afterwards."""
     if hidden.dim() != 2 or expert_ids.dim() != 2 or \
             tuple(routing_weights.shape) != tuple(expert_ids.shape) or \
             expert_ids.shape[0] != hidden.shape[0]:
@@ -380,11 +383,15 @@ def routed_experts(hidden: torch.Tensor, expert_ids: torch.Tensor,
         tokens, hidden_size, intermediate, experts, top_k)
     if size == 0:
         raise ValueError("MoE routing schedule must be addressable by i32 indices")
-    key = (hidden.device, torch.cuda.current_stream(hidden.device).cuda_stream)
-    workspace = _WORKSPACES.get(key)
-    if workspace is None or workspace.numel() < size:
-        workspace = torch.empty(size, dtype=torch.uint8, device=hidden.device)
-        _WORKSPACES[key] = workspace
+    if workspace is None:
+        key = (hidden.device, torch.cuda.current_stream(hidden.device).cuda_stream)
+        workspace = _WORKSPACES.get(key)
+        if workspace is None or workspace.numel() < size:
+            workspace = torch.empty(size, dtype=torch.uint8, device=hidden.device)
+            _WORKSPACES[key] = workspace
+    elif workspace.dtype != torch.uint8 or workspace.numel() < size or not workspace.is_cuda:
+        raise ValueError("the routed-layer workspace must be a device U8 buffer of at least "
+                         f"{size} bytes")
     if out is None:
         out = torch.empty_like(hidden)
     request = _abi.RoutedSwiglu(

@@ -118,8 +118,18 @@ CONFIG_SHAPES = [(2880, 5120), (4096, 2880), (2880, 5760), (2880, 2880)]
 @pytest.mark.parametrize("K,N", CONFIG_SHAPES)
 @pytest.mark.parametrize("M", [1, 16, 64])
 def test_config_shapes_small_m_full_oracle(K, N, M):
+    # decode shapes: the weight-streaming kernel (these weights stay in L2, so it also takes
+    # M = 64 as four groups of 16 rows)
     from nml_b200 import _abi
-    run_linear(M, K, N, oracle.BF16, _abi.POLICY_AUTO, seed=K + N + M, expect_kernel="umma")
+    run_linear(M, K, N, oracle.BF16, _abi.POLICY_AUTO, seed=K + N + M, expect_kernel="stream")
+
+
+@pytest.mark.parametrize("K,N", CONFIG_SHAPES)
+@pytest.mark.parametrize("M", [1, 16, 64])
+def test_config_shapes_small_m_tensor_core_kernel(K, N, M):
+    # the tcgen05 kernel on the same shapes (it serves them when streaming is not possible)
+    from nml_b200 import _abi
+    run_linear(M, K, N, oracle.BF16, _abi.POLICY_UMMA, seed=K + N + M, expect_kernel="umma")
 
 
 @pytest.mark.parametrize("K,N", CONFIG_SHAPES)
@@ -130,15 +140,41 @@ def test_config_shapes_large_m_sampled_rows(K, N, M):
                expect_kernel="umma")
 
 
-@pytest.mark.parametrize("M", [1, 16, 1024])
+_UNEMBEDDING = {}
+
+
+def unembedding_weight():
+    """The 201088 x 2880 table, quantized once for all row counts (the CPU side of these
+    cases is dominated by generating it)."""
+    if "triple" not in _UNEMBEDDING:
+        _UNEMBEDDING["triple"] = make_weight(4242, (201088, 2880))
+    return _UNEMBEDDING["triple"]
+
+
+@pytest.mark.parametrize("M", [1, 16, 64, 512, 1024, 4096, 16384])
 def test_unembedding_shape(M):
-    from nml_b200 import _abi
-    run_linear(M, 2880, 201088, oracle.BF16, _abi.POLICY_AUTO, seed=M, sample_rows=4,
-               expect_kernel="umma")
+    # every row count of the shape sweep (and 1024 of the logits configuration) on the
+    # vocabulary projection; the oracle evaluates a seeded sample of rows over all columns
+    from nml_b200 import ops, _abi
+    import gpu_util as gu
+    triple = unembedding_weight()
+    if "weight" not in _UNEMBEDDING:
+        _UNEMBEDDING["weight"] = gu.parameter("head", triple, 2880, oracle.BF16)
+    weight = _UNEMBEDDING["weight"]
+    x_bits, x32 = make_activation(200 + M, (M, 2880))
+    y = ops.linear(gu.to_device_bits(x_bits, oracle.BF16), weight)
+    torch.cuda.synchronize()
+    assert _abi.device_status(0x1) == 0
+    assert _abi.last_linear_kernel().startswith("stream" if M <= 16 else "umma")
+    rows = np.arange(M) if M <= 4 else np.sort(rng(M).choice(M, 4, replace=False))
+    expected = oracle.linear(x32[rows], *triple, None)
+    actual = y[torch.from_numpy(rows).cuda()].float().cpu().numpy()
+    del y
+    gu.assert_gemm_close(actual, expected, f"unembedding M={M}")
 
 
-def test_config0_single_linear():
-    # BASELINE config 0: X bf16 [16, 2880], W [5760, 2880]
+def test_single_linear_of_the_cpu_runnable_configuration():
+    # X bf16 [16, 2880], W [5760, 2880]
     from nml_b200 import _abi
     run_linear(16, 2880, 5760, oracle.BF16, _abi.POLICY_AUTO, seed=7)
 
@@ -204,11 +240,13 @@ def test_split_k_over_a_cluster_matches_oracle_and_unsplit_kernel(M, K, N, dtype
     weight = gu.parameter("w", triple, K, dtype)
     x_bits, x32 = make_activation(1001 + M, (M, K), dtype=dtype)
     x = gu.to_device_bits(x_bits, dtype)
-    split = ops.linear(x, weight)
-    again = ops.linear(x, weight)
-    previous = _abi.set_kernel_policy(_abi.POLICY_NO_SPLIT_K)
+    previous = _abi.set_kernel_policy(_abi.POLICY_UMMA)
     try:
+        split = ops.linear(x, weight)
+        again = ops.linear(x, weight)
+        _abi.set_kernel_policy(_abi.POLICY_NO_SPLIT_K)
         unsplit = ops.linear(x, weight)
+        assert _abi.last_linear_kernel().startswith("umma")
     finally:
         _abi.set_kernel_policy(previous)
     torch.cuda.synchronize()

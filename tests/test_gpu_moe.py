@@ -263,3 +263,84 @@ def test_tensor_core_experts_match_portable_kernel_with_expert_offset():
         assert (act[~is_local] == 0).all() and (out[~is_local] == 0).all()
         e_out = oracle.expert_down(act, ids.ravel(), oracle.to_f32(w16, dtype).ravel(), down, db)
         gu.assert_gemm_close(out[is_local], e_out[is_local], f"down policy {policy}")
+
+
+def test_routed_layer_at_the_benchmark_size_against_sampled_oracle():
+    # T = 4096, 32 experts, top-4, hidden = intermediate = 2880: the large-batch path (rows
+    # permuted into schedule-slot order, 256- and 128-slot tiles, un-permute in the down
+    # epilogue).  The schedule is compared in full, bit for bit; each projection on a seeded
+    # sample of tokens against the oracle evaluated on the same inputs; the k-way sum bit for
+    # bit from the device's own weighted rows.
+    import ctypes
+    from nml_b200 import ops, _abi
+    import gpu_util as gu
+    dtype = oracle.BF16
+    T, E, k, H, I = 4096, 32, 4, 2880, 2880
+    gate, down, (gb_bits, gb), (db_bits, db) = make_experts(4000, E, H, I, dtype)
+    x_bits, x = make_activation(4009, (T, H), 1.0, dtype)
+    router = make_activation(4010, (E, H), 0.02, dtype)[1]
+    logits = (x @ router.T).astype(np.float32)
+    active = np.ones(T, np.uint8)
+    active[rng(4011).integers(0, T, 37)] = 0
+    ids, _, w16 = oracle.route(logits, k, dtype, active=active)
+    w = oracle.to_f32(w16, dtype)
+    lib = _abi.load()
+    layout = _abi.RoutedWorkspaceLayout()
+    assert lib.nml_nvfp4_sm100_routed_swiglu_workspace_layout(T, H, I, E, k,
+                                                              ctypes.byref(layout)) == 0
+    assert layout.slot_ordered == 1
+    size = lib.nml_nvfp4_sm100_routed_swiglu_workspace_bytes(T, H, I, E, k)
+    workspace = torch.zeros(size, dtype=torch.uint8, device="cuda")
+    d_ids, d_w = torch.from_numpy(ids).cuda(), gu.to_device_bits(w16, dtype)
+    out = ops.routed_experts(gu.to_device_bits(x_bits, dtype), d_ids, d_w,
+                             gu.parameter("gate_up", gate, H, dtype),
+                             gu.to_device_bits(gb_bits, dtype), gu.parameter("down", down, I, dtype),
+                             gu.to_device_bits(db_bits, dtype), workspace=workspace)
+    # the operator API routes on the device: same ids, same weights, same result
+    routed = ops.routed_clamped_swiglu_masked(
+        gu.to_device_bits(x_bits, dtype), torch.from_numpy(logits).cuda(),
+        gu.parameter("gate_up", gate, H, dtype), gu.to_device_bits(gb_bits, dtype),
+        gu.parameter("down", down, I, dtype), gu.to_device_bits(db_bits, dtype), k,
+        torch.from_numpy(active).bool().cuda())
+    torch.cuda.synchronize()
+    assert _abi.device_status(0x1) == 0
+    assert torch.equal(out.view(torch.int16), routed.view(torch.int16))
+
+    def region(offset, count, torch_dtype):
+        width = torch.empty((), dtype=torch_dtype).element_size()
+        return workspace[offset:offset + count * width].view(torch_dtype)
+
+    positions, blocks = int(layout.schedule_positions), int(layout.schedule_blocks)
+    sorted_dev = region(layout.sorted_assignments, positions, torch.int32).cpu().numpy()
+    blocks_dev = region(layout.block_experts, blocks, torch.int32).cpu().numpy()
+    e_sorted, e_blocks, e_active = oracle.assignment_plan(ids.ravel(), E, 16)
+    assert int(region(layout.active_blocks, 1, torch.int32).item()) == e_active
+    assert np.array_equal(sorted_dev, e_sorted) and np.array_equal(blocks_dev, e_blocks)
+
+    sample = np.sort(rng(4012).choice(T, 64, replace=False))
+    sample_ids = ids[sample]
+    assignments = (sample[:, None] * k + np.arange(k)[None, :]).ravel()
+    valid = sample_ids.ravel() >= 0
+    slot_of = np.full(T * k, -1, np.int64)
+    live = sorted_dev < T * k
+    slot_of[sorted_dev[live]] = np.nonzero(live)[0]
+    slots = torch.from_numpy(slot_of[assignments[valid]]).cuda()
+    # stage 1: gate/up + SwiGLU, device rows in slot order
+    slot_activated = region(layout.slot_activated, positions * I, torch.bfloat16).view(positions, I)
+    act_dev = slot_activated[slots].float().cpu().numpy()
+    e_act = oracle.expert_gate_up(x[sample], sample_ids.ravel(), k, gate, gb)
+    gu.assert_gemm_close(act_dev, e_act[valid], "gate_up at T=4096")
+    # stage 2: down x routing weight from the device's own narrowed activations
+    weighted = region(layout.weighted, T * k * H, torch.bfloat16).view(T * k, H)
+    weighted_dev = weighted[torch.from_numpy(assignments).cuda()]
+    act_in = np.zeros((assignments.size, I), np.float32)
+    act_in[valid] = act_dev
+    e_weighted = oracle.expert_down(act_in, sample_ids.ravel(), w[sample].ravel(), down, db)
+    gu.assert_gemm_close(weighted_dev.float().cpu().numpy()[valid], e_weighted[valid],
+                         "down at T=4096")
+    # stage 3: k-way sum, bit for bit
+    w_bits = gu.from_device_bits(weighted_dev).copy()
+    w_bits[~valid] = 0
+    assert np.array_equal(gu.from_device_bits(out[torch.from_numpy(sample).cuda()]),
+                          oracle.combine(w_bits, sample.size, k, dtype, mode=0))
+    assert (gu.device_f32(out)[active == 0] == 0).all()

@@ -8,7 +8,7 @@ instead of in a caller-provided workspace.
 
 This test drives that entry point through the C ABI and requires its output to equal, bit
 for bit (both run the same kernels), the output of `nml_nvfp4_sm100_routed_swiglu` with a
-caller-provided workspace.  It does so on two calls in a row with different inputs and a
+caller-provided workspace, and to agree with the CPU oracle's evaluation of the layer.  It does so on two calls in a row with different inputs and a
 different token count, so that anything the first call leaves in the shared array would
 show up in the second.  It also checks the size limit.  The file sorts last so that a run
 stopping at the first failure has already run every other test; it passes alone in a fresh
@@ -26,18 +26,29 @@ from helpers import make_activation, make_weight, rng
 pytestmark = pytest.mark.gpu
 
 
+def host_inputs(tokens, H, E, I, k, seed):
+    """The layer's inputs as the oracle takes them (weights as triples, f32 views)."""
+    dtype = oracle.BF16
+    gate, down = make_weight(seed, (E, 2 * I, H)), make_weight(seed + 1, (E, H, I))
+    gate_bias = make_activation(seed + 2, (E, 2 * I), 0.02)
+    down_bias = make_activation(seed + 3, (E, H), 0.02)
+    hidden = make_activation(seed + 4, (tokens, H))
+    logits = rng(seed + 5).standard_normal((tokens, E)).astype(np.float32)
+    ids, _, w16 = oracle.route(logits, k, dtype)
+    ids[0, 0] = -1  # one masked route
+    return gate, down, gate_bias, down_bias, hidden, ids, w16
+
+
 def build_request(tokens, H, E, I, k, seed, workspace=None):
     from nml_b200 import _abi
     import gpu_util as gu
     dtype = oracle.BF16
-    gate = gu.parameter("gate", make_weight(seed, (E, 2 * I, H)), H, dtype)
-    down = gu.parameter("down", make_weight(seed + 1, (E, H, I)), I, dtype)
-    gate_bias = gu.to_device_bits(make_activation(seed + 2, (E, 2 * I), 0.02)[0], dtype)
-    down_bias = gu.to_device_bits(make_activation(seed + 3, (E, H), 0.02)[0], dtype)
-    hidden = gu.to_device_bits(make_activation(seed + 4, (tokens, H))[0], dtype)
-    logits = rng(seed + 5).standard_normal((tokens, E)).astype(np.float32)
-    ids, _, w16 = oracle.route(logits, k, dtype)
-    ids[0, 0] = -1  # one masked route
+    gate_t, down_t, gate_b, down_b, hidden_b, ids, w16 = host_inputs(tokens, H, E, I, k, seed)
+    gate = gu.parameter("gate", gate_t, H, dtype)
+    down = gu.parameter("down", down_t, I, dtype)
+    gate_bias = gu.to_device_bits(gate_b[0], dtype)
+    down_bias = gu.to_device_bits(down_b[0], dtype)
+    hidden = gu.to_device_bits(hidden_b[0], dtype)
     d_ids = torch.from_numpy(ids).cuda()
     d_w = gu.to_device_bits(w16, dtype)
     out = torch.full((tokens, H), float("nan"), dtype=torch.bfloat16, device="cuda")
@@ -73,6 +84,15 @@ def test_static_scratch_entry_point_matches_workspace_entry_point_twice():
         assert _abi.device_status(0x1) == 0
         assert not torch.isnan(actual.float()).any()
         assert np.array_equal(gu.from_device_bits(actual), gu.from_device_bits(expected))
+        # and against the CPU oracle's layer (f32 between the projections; the device narrows
+        # there like the reference's device path, so the bar is the norm-wise one of the
+        # other layer-level tests)
+        gate_t, down_t, gate_b, down_b, hidden_b, ids, w16 = host_inputs(tokens, H, E, I, k, seed)
+        weights = np.where(ids < 0, 0, oracle.to_f32(w16, oracle.BF16))
+        e_layer = oracle.routed_clamped_swiglu(hidden_b[1], np.where(ids < 0, 0, ids), weights,
+                                               gate_t, gate_b[1], down_t, down_b[1])
+        metrics = oracle.error_metrics(gu.device_f32(actual), e_layer)
+        assert metrics["norm_rel"] <= 1e-2, metrics
 
 
 def test_static_scratch_entry_point_rejects_oversized_requests():
