@@ -255,6 +255,10 @@ typedef struct NmlSm100RoutedSwiglu {
   int64_t experts_per_token;
   int32_t expert_offset;        /* first expert id held locally (expert parallel), else 0 */
   int32_t dtype;
+  /* Optional (read when struct_size covers it): how many of the tokens * k routes the caller
+   * expects to be live (not masked, expert held locally); 0 = all.  A hint for kernel
+   * selection only: an expert-parallel owner passes rows of which most are masked. */
+  int64_t live_routes_hint;
 } NmlSm100RoutedSwiglu;
 
 /* Expert-parallel dispatch plan.  The reference shards experts by replicating all tokens on
@@ -351,14 +355,38 @@ int32_t nml_nvfp4_sm100_routed_swiglu(const NmlSm100RoutedSwiglu *request, char 
 /* Expert-parallel token exchange support; together they replace lower_expert_parallel's
  * replicate-and-all-reduce scheme (crates/nml-ir/src/lib.rs:9596-9728). */
 /* Token exchange by direct stores into peer memory (NVLink), for ranks that have mapped each
- * other's receive buffers into their own address space (symmetric memory).  No counterpart in the reference.  Stage order per layer,
- * all on the caller's stream: ep_dispatch_plan; all-gather of send_counts into count_matrix
- * [ranks, ranks] (row = sender); ep_push_rows; a stream-ordered collective over the ranks (all
- * pushes have landed); ep_receive_meta; the routed layer over the received rows (k = 1);
- * ep_return_rows; the same collective again; combine_rows over the return buffer.  Rank r's
- * rows for rank d occupy [sum_{r' < r} C[r'][d], ...) of d's buffer in r's send order.  A row
- * that would fall outside `capacity` is dropped and NML_SM100_STATUS_INDEX_RANGE is raised. */
+ * other's buffers into their own address space (symmetric memory).  No counterpart in the
+ * reference.  Cross-rank ordering is done on the device with flags in peer memory; there is
+ * no host synchronisation and no collective between the stages.  Stage order per layer, all
+ * on the caller's stream: ep_dispatch_plan; ep_push_rows (stores rows and meta into the
+ * owners' buffers, then raises this rank's arrival flag on every rank); ep_receive_meta
+ * (waits for every rank's arrival flag, then writes the expert ids and routing weights of the
+ * received rows); the routed layer over the receive buffer (k = 1); ep_return_rows (stores
+ * result rows into the senders' return buffers, then raises the return flag);
+ * ep_wait_returns; combine_rows over the return buffer.
+ *
+ * Every rank's receive buffer holds one region of `region_rows` rows per sender; sender r
+ * writes its rows for a destination into region r in its send order, so placement needs no
+ * counts from other ranks and cannot overflow when region_rows >= the sender's assignments.
+ * Waits are bounded (`wait_limit` polls of about a quarter microsecond, 0 = one second); a
+ * wait that runs out sets NML_SM100_STATUS_BARRIER_TIMEOUT | NML_SM100_STATUS_PEER_TIMEOUT,
+ * the missing sender counts as having sent nothing, and the kernel returns.  All ranks must
+ * run the same sequence of exchanges on the same buffers; buffers start zeroed. */
 #define NML_SM100_EP_MAX_RANKS 16
+#define NML_SM100_EP_SYNC_WORDS (3 * NML_SM100_EP_MAX_RANKS) /* i32 words per rank */
+#define NML_SM100_EP_STATE_WORDS 4                           /* i32 words, local */
+typedef struct NmlSm100EpExchange {
+  void *peer_rows[NML_SM100_EP_MAX_RANKS];    /* receive rows [ranks * region_rows, width] */
+  int32_t *peer_meta[NML_SM100_EP_MAX_RANKS]; /* receive meta [ranks * region_rows, 4] i32 */
+  void *peer_back[NML_SM100_EP_MAX_RANKS];    /* return rows [region_rows, width] */
+  int32_t *peer_sync[NML_SM100_EP_MAX_RANKS]; /* sync words [NML_SM100_EP_SYNC_WORDS] */
+  int32_t *local_state; /* [NML_SM100_EP_STATE_WORDS], this rank's own memory, starts zeroed */
+  int64_t ranks;
+  int64_t rank;
+  int64_t region_rows;
+  int64_t width;        /* multiple of 8 */
+} NmlSm100EpExchange;
+
 typedef struct NmlSm100EpPushRows {
   size_t struct_size;
   const void *source;              /* [source_rows, width] dtype: this rank's tokens */
@@ -366,48 +394,39 @@ typedef struct NmlSm100EpPushRows {
   const int32_t *local_expert;     /* [assignments] from ep_dispatch_plan */
   const void *routing_weights;     /* [assignments] dtype */
   const int32_t *send_counts;      /* [ranks] from ep_dispatch_plan */
-  const int32_t *count_matrix;     /* [ranks, ranks] all-gathered send_counts */
-  void *peer_rows[NML_SM100_EP_MAX_RANKS];    /* receive rows [capacity, width] of every rank */
-  int32_t *peer_meta[NML_SM100_EP_MAX_RANKS]; /* receive meta [capacity, 4] i32 of every rank */
+  NmlSm100EpExchange exchange;
   void *stream;
-  int64_t assignments;
+  int64_t assignments;             /* <= exchange.region_rows */
   int64_t source_rows;
   int64_t experts_per_token;
-  int64_t width;                   /* multiple of 8 */
-  int64_t ranks;
-  int64_t rank;
-  int64_t capacity;
   int32_t dtype;
 } NmlSm100EpPushRows;
 
 typedef struct NmlSm100EpReceiveMeta {
   size_t struct_size;
-  const int32_t *meta;             /* this rank's receive meta [capacity, 4] */
-  const int32_t *count_matrix;
-  int32_t *expert_ids;             /* [capacity] local expert or -1 past the received rows */
-  void *routing_weights;           /* [capacity] dtype */
+  NmlSm100EpExchange exchange;
+  int32_t *expert_ids;             /* [ranks * region_rows] local expert, -1 where no row arrived */
+  void *routing_weights;           /* [ranks * region_rows] dtype */
   int32_t *received;               /* device scalar: rows received */
   void *stream;
-  int64_t ranks;
-  int64_t rank;
-  int64_t capacity;
+  int64_t wait_limit;
   int32_t dtype;
 } NmlSm100EpReceiveMeta;
 
 typedef struct NmlSm100EpReturnRows {
   size_t struct_size;
-  const void *computed;            /* [capacity, width] dtype: result rows in receive order */
-  const int32_t *meta;             /* this rank's receive meta */
-  const int32_t *count_matrix;
-  void *peer_return[NML_SM100_EP_MAX_RANKS];  /* return rows [return_capacity, width] */
+  const void *computed;            /* [ranks * region_rows, width] dtype: results in receive order */
+  NmlSm100EpExchange exchange;
   void *stream;
-  int64_t width;
-  int64_t ranks;
-  int64_t rank;
-  int64_t capacity;
-  int64_t return_capacity;
   int32_t dtype;
 } NmlSm100EpReturnRows;
+
+typedef struct NmlSm100EpWaitReturns {
+  size_t struct_size;
+  NmlSm100EpExchange exchange;
+  void *stream;
+  int64_t wait_limit;
+} NmlSm100EpWaitReturns;
 
 int32_t nml_nvfp4_sm100_ep_push_rows(const NmlSm100EpPushRows *request, char *error_message,
                                      size_t error_message_capacity);
@@ -415,6 +434,8 @@ int32_t nml_nvfp4_sm100_ep_receive_meta(const NmlSm100EpReceiveMeta *request,
                                         char *error_message, size_t error_message_capacity);
 int32_t nml_nvfp4_sm100_ep_return_rows(const NmlSm100EpReturnRows *request, char *error_message,
                                        size_t error_message_capacity);
+int32_t nml_nvfp4_sm100_ep_wait_returns(const NmlSm100EpWaitReturns *request,
+                                        char *error_message, size_t error_message_capacity);
 int32_t nml_nvfp4_sm100_ep_dispatch_plan(const NmlSm100EpDispatchPlan *request,
                                          char *error_message, size_t error_message_capacity);
 int32_t nml_nvfp4_sm100_gather_rows(const NmlSm100GatherRows *request, char *error_message,
@@ -494,6 +515,7 @@ int32_t nml_nvfp4_sm100_plan_capacity(int64_t assignments, int64_t experts, int6
 #define NML_SM100_STATUS_BARRIER_TIMEOUT 1
 #define NML_SM100_STATUS_TMEM_ALLOC 2
 #define NML_SM100_STATUS_INDEX_RANGE 4
+#define NML_SM100_STATUS_PEER_TIMEOUT 8 /* an expert-parallel wait for another rank ran out */
 int32_t nml_nvfp4_sm100_device_status(void *stream, int32_t clear, int32_t *status);
 
 /* Kernel selection override for tests: every shape has one automatic choice, and each kernel
@@ -518,7 +540,7 @@ const char *nml_nvfp4_sm100_last_linear_kernel(void);
 int32_t nml_nvfp4_sm100_last_linear_tile_rows(void);
 
 /* ABI version of this header. */
-#define NML_NVFP4_SM100_ABI_VERSION 1
+#define NML_NVFP4_SM100_ABI_VERSION 2
 int32_t nml_nvfp4_sm100_abi_version(void);
 
 #ifdef __cplusplus

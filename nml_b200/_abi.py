@@ -21,6 +21,7 @@ LAUNCH_FAILURE = 2
 STATUS_BARRIER_TIMEOUT = 1
 STATUS_TMEM_ALLOC = 2
 STATUS_INDEX_RANGE = 4
+STATUS_PEER_TIMEOUT = 8
 
 STATIC_SCRATCH_BYTES = 8 << 20
 
@@ -107,7 +108,8 @@ class RoutedSwiglu(ctypes.Structure):
                 ("down_scales", _vp), ("down_global", _vp), ("down_bias", _vp), ("output", _vp),
                 ("workspace", _vp), ("workspace_bytes", _sz), ("stream", _vp), ("tokens", _i64),
                 ("hidden_size", _i64), ("intermediate_size", _i64), ("experts", _i64),
-                ("experts_per_token", _i64), ("expert_offset", _i32), ("dtype", _i32)]
+                ("experts_per_token", _i64), ("expert_offset", _i32), ("dtype", _i32),
+                ("live_routes_hint", _i64)]
 
 
 class EpDispatchPlan(ctypes.Structure):
@@ -139,26 +141,38 @@ class RoutedWorkspaceLayout(ctypes.Structure):
 EP_MAX_RANKS = 16
 
 
+EP_SYNC_WORDS = 3 * EP_MAX_RANKS
+EP_STATE_WORDS = 4
+
+
+class EpExchange(ctypes.Structure):
+    _fields_ = [("peer_rows", _vp * EP_MAX_RANKS), ("peer_meta", _vp * EP_MAX_RANKS),
+                ("peer_back", _vp * EP_MAX_RANKS), ("peer_sync", _vp * EP_MAX_RANKS),
+                ("local_state", _vp), ("ranks", _i64), ("rank", _i64), ("region_rows", _i64),
+                ("width", _i64)]
+
+
 class EpPushRows(ctypes.Structure):
     _fields_ = [("struct_size", _sz), ("source", _vp), ("send_order", _vp),
                 ("local_expert", _vp), ("routing_weights", _vp), ("send_counts", _vp),
-                ("count_matrix", _vp), ("peer_rows", _vp * EP_MAX_RANKS),
-                ("peer_meta", _vp * EP_MAX_RANKS), ("stream", _vp), ("assignments", _i64),
-                ("source_rows", _i64), ("experts_per_token", _i64), ("width", _i64),
-                ("ranks", _i64), ("rank", _i64), ("capacity", _i64), ("dtype", _i32)]
+                ("exchange", EpExchange), ("stream", _vp), ("assignments", _i64),
+                ("source_rows", _i64), ("experts_per_token", _i64), ("dtype", _i32)]
 
 
 class EpReceiveMeta(ctypes.Structure):
-    _fields_ = [("struct_size", _sz), ("meta", _vp), ("count_matrix", _vp), ("expert_ids", _vp),
-                ("routing_weights", _vp), ("received", _vp), ("stream", _vp), ("ranks", _i64),
-                ("rank", _i64), ("capacity", _i64), ("dtype", _i32)]
+    _fields_ = [("struct_size", _sz), ("exchange", EpExchange), ("expert_ids", _vp),
+                ("routing_weights", _vp), ("received", _vp), ("stream", _vp),
+                ("wait_limit", _i64), ("dtype", _i32)]
 
 
 class EpReturnRows(ctypes.Structure):
-    _fields_ = [("struct_size", _sz), ("computed", _vp), ("meta", _vp), ("count_matrix", _vp),
-                ("peer_return", _vp * EP_MAX_RANKS), ("stream", _vp), ("width", _i64),
-                ("ranks", _i64), ("rank", _i64), ("capacity", _i64), ("return_capacity", _i64),
-                ("dtype", _i32)]
+    _fields_ = [("struct_size", _sz), ("computed", _vp), ("exchange", EpExchange),
+                ("stream", _vp), ("dtype", _i32)]
+
+
+class EpWaitReturns(ctypes.Structure):
+    _fields_ = [("struct_size", _sz), ("exchange", EpExchange), ("stream", _vp),
+                ("wait_limit", _i64)]
 
 
 # name -> request structure, for the entry points of the form fn(const Request*, char*, size_t)
@@ -166,6 +180,7 @@ REQUEST_ENTRY_POINTS = {
     "nml_nvfp4_sm100_ep_push_rows": EpPushRows,
     "nml_nvfp4_sm100_ep_receive_meta": EpReceiveMeta,
     "nml_nvfp4_sm100_ep_return_rows": EpReturnRows,
+    "nml_nvfp4_sm100_ep_wait_returns": EpWaitReturns,
     "nml_nvfp4_sm100_linear": Linear,
     "nml_nvfp4_sm100_linear_qkv": LinearQkv,
     "nml_nvfp4_sm100_embedding": Embedding,

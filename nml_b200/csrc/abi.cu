@@ -100,7 +100,8 @@ int32_t launch_ep_dispatch_plan(const int32_t* expert_ids, int32_t* send_order,
                                 size_t capacity);
 int32_t launch_gather_rows(const void* source, const int32_t* row_index, void* output,
                            int64_t rows, int width, int divisor, int64_t source_rows, int dtype,
-                           cudaStream_t stream, char* message, size_t capacity);
+                           cudaStream_t stream, char* message, size_t capacity,
+                           const int32_t* live_blocks = nullptr);
 int32_t launch_combine_rows(const void* rows, const int32_t* row_index, void* output, int tokens,
                             int top_k, int width, int64_t row_count, int dtype,
                             cudaStream_t stream, char* message, size_t capacity);
@@ -634,7 +635,8 @@ extern "C" int32_t nml_nvfp4_sm100_routed_swiglu_workspace_layout(
 extern "C" int32_t nml_nvfp4_sm100_routed_swiglu(const NmlSm100RoutedSwiglu* request,
                                                  char* error_message,
                                                  size_t error_message_capacity) {
-  if (request == nullptr || request->struct_size < sizeof(NmlSm100RoutedSwiglu)) {
+  if (request == nullptr ||
+      request->struct_size < offsetof(NmlSm100RoutedSwiglu, live_routes_hint)) {
     return fail(NML_SM100_INVALID_ARGUMENT, "truncated NVFP4 routed SwiGLU request",
                 error_message, error_message_capacity);
   }
@@ -694,6 +696,10 @@ extern "C" int32_t nml_nvfp4_sm100_routed_swiglu(const NmlSm100RoutedSwiglu* req
   args.experts = static_cast<int>(request->experts);
   args.experts_per_token = static_cast<int>(request->experts_per_token);
   args.dtype = request->dtype;
+  if (has_field(request, offsetof(NmlSm100RoutedSwiglu, live_routes_hint), sizeof(int64_t)) &&
+      request->live_routes_hint > 0 && request->live_routes_hint < assignments) {
+    args.live_routes = static_cast<int>(request->live_routes_hint);
+  }
 
   args.inputs = static_cast<int>(request->hidden_size);
   args.outputs = static_cast<int>(request->intermediate_size);
@@ -708,8 +714,9 @@ extern "C" int32_t nml_nvfp4_sm100_routed_swiglu(const NmlSm100RoutedSwiglu* req
   // Large batches: permute the hidden rows into slot order once (token permute) so that both
   // projections stream contiguous rows by TMA instead of gathering through the load/store
   // unit; the result rows go back to assignment order in the down epilogue (unpermute).
+  const int64_t live = args.live_routes > 0 ? args.live_routes : assignments;
   const bool slot_ordered =
-      static_cast<int64_t>(assignments) > kPermuteThreshold * request->experts &&
+      live > kPermuteThreshold * request->experts &&
       request->workspace_bytes >= w.total_permuted &&
       get_kernel_policy() != NML_SM100_POLICY_SIMT &&
       experts_umma_supported(args) && request->hidden_size % 8 == 0 &&
@@ -721,7 +728,8 @@ extern "C" int32_t nml_nvfp4_sm100_routed_swiglu(const NmlSm100RoutedSwiglu* req
     status = launch_gather_rows(request->hidden, sorted, permuted, w.positions,
                                 static_cast<int>(request->hidden_size),
                                 static_cast<int>(request->experts_per_token), request->tokens,
-                                request->dtype, stream, error_message, error_message_capacity);
+                                request->dtype, stream, error_message, error_message_capacity,
+                                active);
     if (status != NML_SM100_OK) return status;
     args.input = permuted;
     args.output = slot_activated;
@@ -799,7 +807,8 @@ uint8_t* static_scratch_address(int device, char* message, size_t capacity) {
 extern "C" int32_t nml_nvfp4_sm100_routed_swiglu_static(const NmlSm100RoutedSwiglu* request,
                                                         char* error_message,
                                                         size_t error_message_capacity) {
-  if (request == nullptr || request->struct_size < sizeof(NmlSm100RoutedSwiglu)) {
+  if (request == nullptr ||
+      request->struct_size < offsetof(NmlSm100RoutedSwiglu, live_routes_hint)) {
     return fail(NML_SM100_INVALID_ARGUMENT, "truncated NVFP4 routed SwiGLU request",
                 error_message, error_message_capacity);
   }
@@ -955,12 +964,6 @@ extern "C" int32_t nml_nvfp4_sm100_gather_rows(const NmlSm100GatherRows* request
                             error_message_capacity);
 }
 
-namespace {
-bool valid_ranks(int64_t ranks, int64_t rank) {
-  return ranks >= 1 && ranks <= NML_SM100_EP_MAX_RANKS && rank >= 0 && rank < ranks;
-}
-}  // namespace
-
 extern "C" int32_t nml_nvfp4_sm100_ep_push_rows(const NmlSm100EpPushRows* request,
                                                 char* error_message,
                                                 size_t error_message_capacity) {
@@ -968,19 +971,13 @@ extern "C" int32_t nml_nvfp4_sm100_ep_push_rows(const NmlSm100EpPushRows* reques
     return fail(NML_SM100_INVALID_ARGUMENT, "truncated NVFP4 row push request", error_message,
                 error_message_capacity);
   }
-  bool valid = request->source != nullptr && request->send_order != nullptr &&
-               request->local_expert != nullptr && request->routing_weights != nullptr &&
-               request->send_counts != nullptr && request->count_matrix != nullptr &&
-               request->stream != nullptr && fits_i32(request->assignments) &&
-               fits_i32(request->source_rows) && fits_i32(request->width) &&
-               request->width % 8 == 0 && request->experts_per_token > 0 &&
-               fits_i32(request->capacity) && valid_ranks(request->ranks, request->rank) &&
-               reinterpret_cast<uintptr_t>(request->source) % 16 == 0;
-  for (int r = 0; valid && r < request->ranks; ++r) {
-    valid = request->peer_rows[r] != nullptr && request->peer_meta[r] != nullptr &&
-            reinterpret_cast<uintptr_t>(request->peer_rows[r]) % 16 == 0 &&
-            reinterpret_cast<uintptr_t>(request->peer_meta[r]) % 16 == 0;
-  }
+  const bool valid = request->source != nullptr && request->send_order != nullptr &&
+                     request->local_expert != nullptr && request->routing_weights != nullptr &&
+                     request->send_counts != nullptr && request->stream != nullptr &&
+                     fits_i32(request->assignments) && fits_i32(request->source_rows) &&
+                     request->experts_per_token > 0 && valid_exchange(request->exchange) &&
+                     request->assignments <= request->exchange.region_rows &&
+                     reinterpret_cast<uintptr_t>(request->source) % 16 == 0;
   if (!valid || !valid_dtype(request->dtype)) {
     return fail(NML_SM100_INVALID_ARGUMENT, "invalid NVFP4 row push request", error_message,
                 error_message_capacity);
@@ -997,18 +994,15 @@ extern "C" int32_t nml_nvfp4_sm100_ep_receive_meta(const NmlSm100EpReceiveMeta* 
     return fail(NML_SM100_INVALID_ARGUMENT, "truncated NVFP4 receive meta request", error_message,
                 error_message_capacity);
   }
-  if (request->meta == nullptr || request->count_matrix == nullptr ||
-      request->expert_ids == nullptr || request->routing_weights == nullptr ||
-      request->received == nullptr || request->stream == nullptr ||
-      !fits_i32(request->capacity) || !valid_ranks(request->ranks, request->rank) ||
-      reinterpret_cast<uintptr_t>(request->meta) % 16 != 0 || !valid_dtype(request->dtype)) {
+  if (request->expert_ids == nullptr || request->routing_weights == nullptr ||
+      request->received == nullptr || request->stream == nullptr || request->wait_limit < 0 ||
+      !valid_exchange(request->exchange) || !valid_dtype(request->dtype)) {
     return fail(NML_SM100_INVALID_ARGUMENT, "invalid NVFP4 receive meta request", error_message,
                 error_message_capacity);
   }
-  if (current_device(error_message, error_message_capacity) == nullptr) {
-    return NML_SM100_LAUNCH_FAILURE;
-  }
-  return launch_ep_receive_meta(*request, error_message, error_message_capacity);
+  const DeviceInfo* device = current_device(error_message, error_message_capacity);
+  if (device == nullptr) return NML_SM100_LAUNCH_FAILURE;
+  return launch_ep_receive_meta(*request, *device, error_message, error_message_capacity);
 }
 
 extern "C" int32_t nml_nvfp4_sm100_ep_return_rows(const NmlSm100EpReturnRows* request,
@@ -1018,24 +1012,32 @@ extern "C" int32_t nml_nvfp4_sm100_ep_return_rows(const NmlSm100EpReturnRows* re
     return fail(NML_SM100_INVALID_ARGUMENT, "truncated NVFP4 row return request", error_message,
                 error_message_capacity);
   }
-  bool valid = request->computed != nullptr && request->meta != nullptr &&
-               request->count_matrix != nullptr && request->stream != nullptr &&
-               fits_i32(request->width) && request->width % 8 == 0 &&
-               fits_i32(request->capacity) && fits_i32(request->return_capacity) &&
-               valid_ranks(request->ranks, request->rank) &&
-               reinterpret_cast<uintptr_t>(request->computed) % 16 == 0 &&
-               reinterpret_cast<uintptr_t>(request->meta) % 16 == 0;
-  for (int r = 0; valid && r < request->ranks; ++r) {
-    valid = request->peer_return[r] != nullptr &&
-            reinterpret_cast<uintptr_t>(request->peer_return[r]) % 16 == 0;
-  }
-  if (!valid || !valid_dtype(request->dtype)) {
+  if (request->computed == nullptr || request->stream == nullptr ||
+      !valid_exchange(request->exchange) || !valid_dtype(request->dtype) ||
+      reinterpret_cast<uintptr_t>(request->computed) % 16 != 0) {
     return fail(NML_SM100_INVALID_ARGUMENT, "invalid NVFP4 row return request", error_message,
                 error_message_capacity);
   }
   const DeviceInfo* device = current_device(error_message, error_message_capacity);
   if (device == nullptr) return NML_SM100_LAUNCH_FAILURE;
   return launch_ep_return_rows(*request, *device, error_message, error_message_capacity);
+}
+
+extern "C" int32_t nml_nvfp4_sm100_ep_wait_returns(const NmlSm100EpWaitReturns* request,
+                                                   char* error_message,
+                                                   size_t error_message_capacity) {
+  if (request == nullptr || request->struct_size < sizeof(NmlSm100EpWaitReturns)) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "truncated NVFP4 return wait request", error_message,
+                error_message_capacity);
+  }
+  if (request->stream == nullptr || request->wait_limit < 0 ||
+      !valid_exchange(request->exchange)) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "invalid NVFP4 return wait request", error_message,
+                error_message_capacity);
+  }
+  const DeviceInfo* device = current_device(error_message, error_message_capacity);
+  if (device == nullptr) return NML_SM100_LAUNCH_FAILURE;
+  return launch_ep_wait_returns(*request, *device, error_message, error_message_capacity);
 }
 
 extern "C" int32_t nml_nvfp4_sm100_combine_rows(const NmlSm100CombineRows* request,

@@ -177,6 +177,8 @@ struct ExpertArgs {
   // Orchestrated layer only: `input` holds one row per schedule slot (rows permuted into slot
   // order); gate/up then also writes its result rows in slot order.
   bool slot_input = false;
+  // Routes expected to be live (kernel selection only); 0: all of `assignments`.
+  int live_routes = 0;
 };
 
 int32_t launch_experts_simt(const ExpertArgs& args, const DeviceInfo& device, char* message,
@@ -191,8 +193,11 @@ int32_t launch_experts_stream(const ExpertArgs& args, const DeviceInfo& device, 
 
 int32_t launch_ep_push_rows(const NmlSm100EpPushRows& request, const DeviceInfo& device,
                             char* message, size_t capacity);
-int32_t launch_ep_receive_meta(const NmlSm100EpReceiveMeta& request, char* message,
-                               size_t capacity);
+int32_t launch_ep_receive_meta(const NmlSm100EpReceiveMeta& request, const DeviceInfo& device,
+                               char* message, size_t capacity);
+int32_t launch_ep_wait_returns(const NmlSm100EpWaitReturns& request, const DeviceInfo& device,
+                               char* message, size_t capacity);
+bool valid_exchange(const NmlSm100EpExchange& exchange);
 int32_t launch_ep_return_rows(const NmlSm100EpReturnRows& request, const DeviceInfo& device,
                               char* message, size_t capacity);
 

@@ -83,15 +83,18 @@ ep_dispatch_plan_kernel(const int32_t* __restrict__ expert_ids, int32_t* __restr
   }
 }
 
-// output[r, :] = source[row_index[r] / divisor, :]; a negative index yields a zero row.
+// output[r, :] = source[row_index[r] / divisor, :]; a negative index yields a zero row.  With
+// `live_blocks`, rows at or past 16 * live_blocks[0] are left untouched (schedule positions
+// behind the active blocks, which no consumer reads).
 template <typename T>
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const T* __restrict__ source, const int32_t* __restrict__ row_index,
                    T* __restrict__ output, int64_t rows, int vectors, int divisor,
-                   int64_t source_rows) {
+                   int64_t source_rows, const int32_t* __restrict__ live_blocks) {
   const int64_t item = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (item >= rows * vectors) return;
   const int64_t row = item / vectors;
+  if (live_blocks != nullptr && row >= static_cast<int64_t>(live_blocks[0]) * 16) return;
   const int vector = static_cast<int>(item - row * vectors);
   const int32_t index = row_index[row];
   uint4 value = make_uint4(0, 0, 0, 0);
@@ -154,7 +157,8 @@ int32_t launch_ep_dispatch_plan(const int32_t* expert_ids, int32_t* send_order,
 
 int32_t launch_gather_rows(const void* source, const int32_t* row_index, void* output,
                            int64_t rows, int width, int divisor, int64_t source_rows, int dtype,
-                           cudaStream_t stream, char* message, size_t capacity) {
+                           cudaStream_t stream, char* message, size_t capacity,
+                           const int32_t* live_blocks) {
   const int vectors = width / 8;
   const int64_t grid = (rows * vectors + 255) / 256;
   if (grid > std::numeric_limits<int32_t>::max()) {
@@ -164,11 +168,11 @@ int32_t launch_gather_rows(const void* source, const int32_t* row_index, void* o
   if (dtype == NML_SM100_F16) {
     gather_rows_kernel<__half><<<static_cast<unsigned>(grid), 256, 0, stream>>>(
         static_cast<const __half*>(source), row_index, static_cast<__half*>(output), rows,
-        vectors, divisor, source_rows);
+        vectors, divisor, source_rows, live_blocks);
   } else {
     gather_rows_kernel<__nv_bfloat16><<<static_cast<unsigned>(grid), 256, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(source), row_index,
-        static_cast<__nv_bfloat16*>(output), rows, vectors, divisor, source_rows);
+        static_cast<__nv_bfloat16*>(output), rows, vectors, divisor, source_rows, live_blocks);
   }
   return launch_result(message, capacity);
 }

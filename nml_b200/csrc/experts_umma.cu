@@ -92,9 +92,10 @@ template <int AFMT, typename T, int MODE, bool XTMA>
 int32_t launch_for_load(const ExpertArgs& args, const DeviceInfo& device, char* message,
                         size_t capacity) {
   // Expected slots per expert under balanced routing decide the slot-tile height.
-  const int64_t average = args.assignments <= args.experts
-                              ? 1
-                              : (args.assignments + args.experts - 1) / args.experts;
+  const int64_t routes = args.live_routes > 0 && args.live_routes < args.assignments
+                             ? args.live_routes
+                             : args.assignments;
+  const int64_t average = routes <= args.experts ? 1 : (routes + args.experts - 1) / args.experts;
   // Decoded weights in tensor memory: every tile's block scales (128 rows x K/16 bytes) must
   // form a legal bulk copy and two such buffers must fit beside the rings.
   const int rows_per_expert = args.gate_up ? 2 * args.outputs : args.outputs;

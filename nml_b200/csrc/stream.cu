@@ -129,14 +129,15 @@ bool experts_stream_supported(const ExpertArgs& args) {
          args.experts * rows_per_expert <= std::numeric_limits<int32_t>::max() &&
          aligned16(args.payload) && aligned16(args.block_scales) && aligned16(args.input) &&
          // decode-size batches: at most one full schedule block per expert on average
-         static_cast<int64_t>(args.assignments) <= 16ll * args.experts;
+         static_cast<int64_t>(args.live_routes > 0 ? args.live_routes : args.assignments) <=
+             16ll * args.experts;
 }
 
 int32_t launch_experts_stream(const ExpertArgs& args, const DeviceInfo& device, char* message,
                               size_t capacity) {
   Params p = {};
   // sparse schedule form (one route per block, nml-ir/src/lib.rs:5696-5721): slot 0 only
-  const int nt = args.assignments <= args.experts ? 1 : 2;
+  const int nt = args.assignments <= args.experts ? 1 : 2;  // (the plan's form follows all routes)
   int smem_bytes = 0;
   if (!plan_layout(args.inputs, nt, &p, &smem_bytes)) {
     return fail(NML_SM100_INVALID_ARGUMENT,

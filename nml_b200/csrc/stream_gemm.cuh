@@ -38,7 +38,6 @@
 // end of the kernel.
 #pragma once
 
-#include <cstdlib>
 #include <type_traits>
 
 #include "common.cuh"
@@ -53,7 +52,7 @@ constexpr int kTileRows = 16;
 constexpr int kUnitK = 64;            // K values of one unit: a quad of lanes reads 32 bytes per row
 constexpr int kMaxComputeWarps = 16;
 constexpr int kMaxThreads = (kMaxComputeWarps + 2) * 32;  // + reducer warp + producer warp
-constexpr int kMaxStages = 8;         // weight tiles in flight per CTA
+constexpr int kMaxStages = 4;         // weight tiles in flight per CTA (more were measured to add nothing)
 constexpr int kSlots = 4;             // partial-sum slots between compute warps and reducer
 constexpr int kSmemBudget = 227 * 1024;
 
@@ -120,30 +119,6 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
 
 // 8 codes (one payload word, K order) -> 8 exact f16 products with the block scale.
 __device__ __forceinline__ void decode8(uint32_t word, uint32_t scale2, uint32_t (&out)[4]) {
-#if defined(NML_STREAM_VARIANT) && NML_STREAM_VARIANT == 1
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const uint32_t shifted = word >> (8 * i);
-    asm("{\n"
-        ".reg .b8 t;\n"
-        "cvt.u8.u32 t, %1;\n"
-        "cvt.rn.f16x2.e2m1x2 %0, t;\n"
-        "}\n"
-        : "=r"(out[i])
-        : "r"(shifted));
-  }
-#elif defined(NML_STREAM_VARIANT) && NML_STREAM_VARIANT == 4
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    asm("{\n"
-        ".reg .b8 t;\n"
-        "cvt.u8.u32 t, %1;\n"
-        "cvt.rn.f16x2.e2m1x2 %0, t;\n"
-        "}\n"
-        : "=r"(out[i])
-        : "r"(word + i));
-  }
-#else
   asm("{\n"
       ".reg .b8 b0, b1, b2, b3;\n"
       "mov.b32 {b0, b1, b2, b3}, %4;\n"
@@ -154,13 +129,10 @@ __device__ __forceinline__ void decode8(uint32_t word, uint32_t scale2, uint32_t
       "}\n"
       : "=r"(out[0]), "=r"(out[1]), "=r"(out[2]), "=r"(out[3])
       : "r"(word));
-#endif
-#if !(defined(NML_STREAM_VARIANT) && NML_STREAM_VARIANT == 3)
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     asm("mul.rn.f16x2 %0, %0, %1;" : "+r"(out[i]) : "r"(scale2));
   }
-#endif
 }
 
 // One E4M3 scale byte -> the f16 scale in both halves of a word.
@@ -695,7 +667,6 @@ inline bool plan_layout(int K, int nt, Params* p, int* smem_bytes) {
   const int partial_bytes = kSlots * p->compute_warps * nt * 32 * 16;
   const int fixed = partial_bytes + 256 /* barriers */ + 128 /* alignment slack */;
   int stages = kMaxStages;
-  if (const char* forced = std::getenv("NML_STREAM_STAGES")) stages = std::atoi(forced);
   while (stages > 1 && stages * p->stage_bytes + fixed > kSmemBudget) --stages;
   if (stages < 2) return false;
   p->stages = stages;

@@ -11,12 +11,13 @@ tokens on every device and all-reducing the partial outputs
               routed to it, and the token's home rank sums its k returned rows in route order.
               Every per-assignment row is produced by the same kernels as on one GPU, so the
               result equals the single-GPU result bit for bit.
-``push``      the same exchange without NCCL on the data path and without any host
-              synchronisation: every rank maps the others' receive buffers (torch symmetric
-              memory) and the
-              dispatch kernel stores each routed row straight into its owner's buffer over
-              NVLink; results come back the same way.  Row placement follows from the
-              all-gathered count matrix, so the layout is deterministic.  CUDA only.
+``push``      the same exchange in this library's own kernels, with no collective and no host
+              synchronisation inside the layer: every rank maps the others' buffers (torch
+              symmetric memory), the dispatch kernel stores each routed row straight into its
+              owner's buffer over NVLink and raises an arrival flag there, the owner's next
+              kernel waits (bounded) for the flags of all senders; results come back the same
+              way.  Every sender has its own region in every receive buffer, so placement is
+              deterministic and cannot overflow whatever the routing.  CUDA only.
 ``allreduce`` the reference's scheme: hidden states are all-gathered, every rank runs its local
               experts over all tokens and partial outputs are summed with an all-reduce.  No
               host synchronisation; meant for decode-size batches.
@@ -90,45 +91,44 @@ class CudaBackend:
         _abi.call("nml_nvfp4_sm100_combine_rows", request)
         return out
 
-    def push_rows(self, hidden, order, local_expert, weights, counts, count_matrix, peers, rank,
-                  top_k, capacity):
+    def push_rows(self, hidden, order, local_expert, weights, counts, exchange, top_k):
         request = _abi.EpPushRows(
             source=hidden.data_ptr(), send_order=order.data_ptr(),
             local_expert=local_expert.data_ptr(), routing_weights=weights.data_ptr(),
-            send_counts=counts.data_ptr(), count_matrix=count_matrix.data_ptr(),
-            peer_rows=(_abi._vp * _abi.EP_MAX_RANKS)(*[p.rows_ptr for p in peers]),
-            peer_meta=(_abi._vp * _abi.EP_MAX_RANKS)(*[p.meta_ptr for p in peers]),
+            send_counts=counts.data_ptr(), exchange=exchange.descriptor(),
             stream=ops._stream(hidden), assignments=order.numel(), source_rows=hidden.shape[0],
-            experts_per_token=top_k, width=hidden.shape[1], ranks=len(peers), rank=rank,
-            capacity=capacity, dtype=ops._code(hidden.dtype))
+            experts_per_token=top_k, dtype=ops._code(hidden.dtype))
         _abi.call("nml_nvfp4_sm100_ep_push_rows", request)
 
-    def receive_meta(self, meta, count_matrix, dtype, ranks, rank, capacity):
-        device = meta.device
-        ids = torch.empty((capacity, 1), dtype=torch.int32, device=device)
-        weights = torch.empty((capacity, 1), dtype=dtype, device=device)
+    def receive_meta(self, exchange, dtype, wait_limit=0):
+        rows = exchange.ranks * exchange.region_rows
+        device = exchange.rows.device
+        ids = torch.empty((rows, 1), dtype=torch.int32, device=device)
+        weights = torch.empty((rows, 1), dtype=dtype, device=device)
         received = torch.empty(1, dtype=torch.int32, device=device)
         request = _abi.EpReceiveMeta(
-            meta=meta.data_ptr(), count_matrix=count_matrix.data_ptr(), expert_ids=ids.data_ptr(),
+            exchange=exchange.descriptor(), expert_ids=ids.data_ptr(),
             routing_weights=weights.data_ptr(), received=received.data_ptr(),
-            stream=ops._stream(meta), ranks=ranks, rank=rank, capacity=capacity,
-            dtype=ops._code(dtype))
+            stream=ops._stream(ids), wait_limit=wait_limit, dtype=ops._code(dtype))
         _abi.call("nml_nvfp4_sm100_ep_receive_meta", request)
         return ids, weights, received
 
-    def return_rows(self, computed, meta, count_matrix, peers, rank, capacity, return_capacity):
-        request = _abi.EpReturnRows(
-            computed=computed.data_ptr(), meta=meta.data_ptr(),
-            count_matrix=count_matrix.data_ptr(),
-            peer_return=(_abi._vp * _abi.EP_MAX_RANKS)(*[p.back_ptr for p in peers]),
-            stream=ops._stream(computed), width=computed.shape[1], ranks=len(peers), rank=rank,
-            capacity=capacity, return_capacity=return_capacity, dtype=ops._code(computed.dtype))
+    def return_rows(self, computed, exchange):
+        request = _abi.EpReturnRows(computed=computed.data_ptr(),
+                                    exchange=exchange.descriptor(),
+                                    stream=ops._stream(computed), dtype=ops._code(computed.dtype))
         _abi.call("nml_nvfp4_sm100_ep_return_rows", request)
 
-    def routed_experts(self, hidden, expert_ids, routing_weights, layer, expert_offset=0):
+    def wait_returns(self, exchange, wait_limit=0):
+        request = _abi.EpWaitReturns(exchange=exchange.descriptor(),
+                                     stream=ops._stream(exchange.rows), wait_limit=wait_limit)
+        _abi.call("nml_nvfp4_sm100_ep_wait_returns", request)
+
+    def routed_experts(self, hidden, expert_ids, routing_weights, layer, expert_offset=0,
+                       live_routes=0):
         return ops.routed_experts(hidden, expert_ids, routing_weights, layer.gate_up,
                                   layer.gate_up_bias, layer.down, layer.down_bias,
-                                  expert_offset=expert_offset)
+                                  expert_offset=expert_offset, live_routes=live_routes)
 
     def linear(self, hidden, weight, bias=None):
         return ops.linear(hidden, weight, bias)
@@ -159,53 +159,88 @@ class LocalExperts:
                             experts, start)
 
 
-@dataclass
-class PeerBuffers:
-    """Device addresses of one rank's receive rows / receive meta / return rows, valid for
-    kernels of this process; `rows`, `meta` and `back` are tensors for this rank's own."""
+class PeerExchange:
+    """The buffers of the peer-push schedule: one allocation per rank in symmetric memory
+    (receive rows and meta with one region per sender, return rows, sync words), mapped into
+    every rank's address space, plus this rank's local state words.  Collective over `group`
+    at construction; sized once for `region_rows` assignments per rank and reused by every
+    call (and every layer) that fits."""
 
-    rows_ptr: int
-    meta_ptr: int
-    back_ptr: int
-    rows: torch.Tensor | None = None  # [capacity, H]
-    meta: torch.Tensor | None = None  # [capacity, 4] i32: expert, weight bits, origin rank, slot
-    back: torch.Tensor | None = None  # [return_capacity, H]
+    def __init__(self, region_rows: int, width: int, dtype, device, group=None,
+                 emulate: tuple | None = None):
+        """``emulate=(rank, ranks)`` builds one of several exchanges that live on ONE device
+        (see ``emulated``): no process group is involved and `bases` is filled in later."""
+        self.world = dist.get_world_size(group) if dist.is_initialized() and not emulate else 1
+        self.ranks = emulate[1] if emulate else self.world
+        self.rank = emulate[0] if emulate else (
+            dist.get_rank(group) if dist.is_initialized() else 0)
+        if self.ranks > _abi.EP_MAX_RANKS:
+            raise ValueError(f"at most {_abi.EP_MAX_RANKS} ranks")
+        self.region_rows, self.width, self.dtype = region_rows, width, dtype
+        element = torch.empty((), dtype=dtype).element_size()
+        align = lambda n: -(-n // 256) * 256
+        rows = self.ranks * region_rows
+        self._rows_bytes = align(rows * width * element)
+        self._meta_bytes = align(rows * 16)
+        self._back_bytes = align(region_rows * width * element)
+        self._sync_bytes = align(_abi.EP_SYNC_WORDS * 4)
+        total = self._rows_bytes + self._meta_bytes + self._back_bytes + self._sync_bytes
+        if self.world == 1:
+            self.block = torch.zeros(total, dtype=torch.uint8, device=device)
+            bases = [self.block.data_ptr()]
+        else:
+            import os
+            # plain peer mappings only: this path never uses multicast (multimem) accesses
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symmetric
+            self.block = symmetric.empty(total, dtype=torch.uint8, device=device)
+            self.block.zero_()
+            handle = symmetric.rendezvous(self.block,
+                                          group if group is not None else dist.group.WORLD)
+            bases = [int(p) for p in handle.buffer_ptrs]
+            if bases[self.rank] != self.block.data_ptr():
+                raise RuntimeError("symmetric memory handle does not describe the local buffer")
+            # every rank has zeroed its flags before any rank may push
+            torch.cuda.synchronize(device)
+            dist.barrier(group)
+        self.bases = bases
+        offset = 0
+        self.rows = self.block[offset:offset + rows * width * element].view(dtype).view(rows, width)
+        offset += self._rows_bytes
+        self.meta = self.block[offset:offset + rows * 16].view(torch.int32).view(rows, 4)
+        offset += self._meta_bytes
+        self.back = self.block[offset:offset + region_rows * width * element].view(dtype).view(
+            region_rows, width)
+        offset += self._back_bytes
+        self.sync = self.block[offset:offset + _abi.EP_SYNC_WORDS * 4].view(torch.int32)
+        self.state = torch.zeros(_abi.EP_STATE_WORDS, dtype=torch.int32, device=device)
+        self._descriptor = None
 
+    @staticmethod
+    def emulated(ranks: int, region_rows: int, width: int, dtype, device) -> list:
+        """`ranks` exchanges on one device whose "peers" are each other's buffers.  No kernel
+        of the exchange waits for a flag that an earlier launch has not already raised when
+        the stages are replayed stage by stage over all ranks, so the whole protocol can be
+        exercised on one GPU."""
+        group = [PeerExchange(region_rows, width, dtype, device, emulate=(r, ranks))
+                 for r in range(ranks)]
+        bases = [x.block.data_ptr() for x in group]
+        for x in group:
+            x.bases = bases
+        return group
 
-def exchange_peer_buffers(capacity: int, return_capacity: int, width: int, dtype, device,
-                          group=None) -> list:
-    """Allocates this rank's buffers in symmetric memory and maps every other rank's (a
-    collective over `group`): one allocation per rank, the same layout everywhere, peer
-    addresses from the rendezvous handle."""
-    element = torch.empty((), dtype=dtype).element_size()
-    rows_bytes = -(-capacity * width * element // 256) * 256
-    meta_bytes = -(-capacity * 16 // 256) * 256
-    back_bytes = -(-return_capacity * width * element // 256) * 256
-    world = dist.get_world_size(group) if dist.is_initialized() else 1
-    rank = dist.get_rank(group) if dist.is_initialized() else 0
-    total = rows_bytes + meta_bytes + back_bytes
-    if world == 1:
-        block = torch.empty(total, dtype=torch.uint8, device=device)
-        bases = [block.data_ptr()]
-    else:
-        import os
-        # plain peer mappings only: this path never uses multicast (multimem) accesses
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
-        import torch.distributed._symmetric_memory as symmetric
-        block = symmetric.empty(total, dtype=torch.uint8, device=device)
-        handle = symmetric.rendezvous(block, group if group is not None else dist.group.WORLD)
-        bases = [int(p) for p in handle.buffer_ptrs]
-        if bases[rank] != block.data_ptr():
-            raise RuntimeError("symmetric memory handle does not describe the local buffer")
-    peers = [PeerBuffers(b, b + rows_bytes, b + rows_bytes + meta_bytes) for b in bases]
-    own = peers[rank]
-    own.rows = block[:capacity * width * element].view(dtype).view(capacity, width)
-    own.meta = block[rows_bytes:rows_bytes + capacity * 16].view(torch.int32).view(capacity, 4)
-    own.back = block[rows_bytes + meta_bytes:
-                     rows_bytes + meta_bytes + return_capacity * width * element] \
-        .view(dtype).view(return_capacity, width)
-    own.block = block  # keeps the allocation (and the mapping) alive
-    return peers
+    def descriptor(self) -> "_abi.EpExchange":
+        if self._descriptor is None:
+            pad = [None] * (_abi.EP_MAX_RANKS - self.ranks)
+            table = lambda offset: (_abi._vp * _abi.EP_MAX_RANKS)(
+                *([b + offset for b in self.bases] + pad))
+            self._descriptor = _abi.EpExchange(
+                peer_rows=table(0), peer_meta=table(self._rows_bytes),
+                peer_back=table(self._rows_bytes + self._meta_bytes),
+                peer_sync=table(self._rows_bytes + self._meta_bytes + self._back_bytes),
+                local_state=self.state.data_ptr(), ranks=self.ranks, rank=self.rank,
+                region_rows=self.region_rows, width=self.width)
+        return self._descriptor
 
 
 class ExpertParallelMoE:
@@ -217,15 +252,15 @@ class ExpertParallelMoE:
     """
 
     def __init__(self, layer: LocalExperts, experts_per_token: int, group=None,
-                 schedule: str = "alltoall", backend=None, capacity_factor: float = 2.0):
+                 schedule: str = "alltoall", backend=None, exchange: PeerExchange | None = None,
+                 wait_limit: int = 0):
         if schedule not in ("alltoall", "allreduce", "push"):
             raise ValueError("schedule must be 'alltoall', 'push' or 'allreduce'")
-        if capacity_factor < 1.0:
-            raise ValueError("capacity_factor must be at least 1")
-        self.capacity_factor = capacity_factor
-        self._peers = None       # push schedule: mapped buffers, allocated on first use
-        self._peer_key = None
-        self._fence_word = None
+        # push schedule: mapped buffers, shared between layers when passed in, else allocated
+        # on first use for that call's token count (a later, larger batch reallocates: a
+        # collective, done only after every rank has drained its stream)
+        self.exchange = exchange
+        self.wait_limit = wait_limit
         self.layer = layer
         self.top_k = experts_per_token
         self.group = group
@@ -286,47 +321,34 @@ class ExpertParallelMoE:
         return backend.combine_rows(returned, slot_of, tokens, k)  # unpermute + k-way sum
 
     # ------------------------------------------------------------------ peer push
-    def _fence(self, device):
-        """Stream-ordered meeting point of the ranks: every rank's earlier kernels (and their
-        stores into peer memory) have completed when it returns on the stream."""
-        if self.world > 1:
-            if self._fence_word is None:
-                self._fence_word = torch.zeros(1, dtype=torch.int32, device=device)
-            dist.all_reduce(self._fence_word, group=self.group)
+    def _exchange_for(self, assignments, width, dtype, device):
+        x = self.exchange
+        if x is None or x.region_rows < assignments or x.width != width or x.dtype != dtype:
+            if x is not None:
+                # no rank may still be storing into the old mapping
+                torch.cuda.synchronize(device)
+                if self.world > 1:
+                    dist.barrier(self.group)
+            self.exchange = x = PeerExchange(-(-assignments // 16) * 16, width, dtype, device,
+                                             self.group)
+        return x
 
     def _forward_push(self, hidden, router_logits, active_tokens):
         backend, k = self.backend, self.top_k
         tokens, width = hidden.shape
         assignments = tokens * k
-        # rows one rank may receive: `capacity_factor` times its fair share, at most everything
-        capacity = min(self.world * assignments,
-                       -(-int(self.capacity_factor * assignments) // 16) * 16)
-        key = (tokens, width, hidden.dtype, hidden.device, capacity)
-        if self._peer_key != key:
-            self._peers = exchange_peer_buffers(capacity, assignments, width, hidden.dtype,
-                                                hidden.device, self.group)
-            self._peer_key = key
-        peers = self._peers
+        exchange = self._exchange_for(assignments, width, hidden.dtype, hidden.device)
         ids, weights = backend.route(router_logits, k, hidden.dtype, active_tokens)
         order, local_expert, slot_of, counts = backend.dispatch_plan(
             ids.reshape(-1), self.world, self.layer.experts_local)
-        count_matrix = torch.empty((self.world, self.world), dtype=torch.int32,
-                                   device=hidden.device)
-        if self.world > 1:
-            dist.all_gather_into_tensor(count_matrix, counts, group=self.group)
-        else:
-            count_matrix.copy_(counts.reshape(1, 1))
-        backend.push_rows(hidden, order, local_expert, weights.reshape(-1), counts, count_matrix,
-                          peers, self.rank, k, capacity)
-        self._fence(hidden.device)  # every row routed to this rank has landed
-        mine = peers[self.rank]
-        recv_ids, recv_weights, _ = backend.receive_meta(mine.meta, count_matrix, hidden.dtype,
-                                                         self.world, self.rank, capacity)
-        computed = backend.routed_experts(mine.rows, recv_ids, recv_weights, self.layer)
-        backend.return_rows(computed, mine.meta, count_matrix, peers, self.rank, capacity,
-                            assignments)
-        self._fence(hidden.device)  # every row of this rank's tokens is back
-        return backend.combine_rows(mine.back, slot_of, tokens, k)
+        backend.push_rows(hidden, order, local_expert, weights.reshape(-1), counts, exchange, k)
+        recv_ids, recv_weights, _ = backend.receive_meta(exchange, hidden.dtype, self.wait_limit)
+        # of the world * region_rows rows an owner's buffer holds, about `assignments` are live
+        computed = backend.routed_experts(exchange.rows, recv_ids, recv_weights, self.layer,
+                                          live_routes=assignments)
+        backend.return_rows(computed, exchange)
+        backend.wait_returns(exchange, self.wait_limit)
+        return backend.combine_rows(exchange.back, slot_of, tokens, k)
 
     # ------------------------------------------------------------------ all-reduce
     def _forward_allreduce(self, hidden, router_logits, active_tokens):

@@ -361,12 +361,13 @@ def routed_experts(hidden: torch.Tensor, expert_ids: torch.Tensor,
                    routing_weights: torch.Tensor, gate_up: NvFp4Parameter,
                    gate_up_bias: torch.Tensor, down: NvFp4Parameter, down_bias: torch.Tensor,
                    expert_offset: int = 0, out: torch.Tensor | None = None,
-                   workspace: torch.Tensor | None = None) -> torch.Tensor:
+                   workspace: torch.Tensor | None = None, live_routes: int = 0) -> torch.Tensor:
     """The routed layer from given routes, one C-ABI call (plan, gate/up + SwiGLU, down,
     k-way sum); the unit of the reference's CPU target ``nml.nvfp4.routed_swiglu``
     (crates/nml-kernel-nvfp4/src/ffi.rs:228-428).  ``workspace`` (u8, 256-byte aligned, at
     least ``nml_nvfp4_sm100_routed_swiglu_workspace_bytes``) replaces the cached scratch
-    buffer, e.g. to inspect the intermediates afterwards."""
+    buffer, e.g. to inspect the intermediates afterwards.  ``live_routes`` (optional) tells
+    the kernel selection how many routes are expected not to be masked."""
     if hidden.dim() != 2 or expert_ids.dim() != 2 or \
             tuple(routing_weights.shape) != tuple(expert_ids.shape) or \
             expert_ids.shape[0] != hidden.shape[0]:
@@ -402,7 +403,8 @@ def routed_experts(hidden: torch.Tensor, expert_ids: torch.Tensor,
         down_global=_ptr(down.global_scale), down_bias=_ptr(down_bias), output=_ptr(out),
         workspace=_ptr(workspace), workspace_bytes=workspace.numel(), stream=_stream(hidden),
         tokens=tokens, hidden_size=hidden_size, intermediate_size=intermediate, experts=experts,
-        experts_per_token=top_k, expert_offset=expert_offset, dtype=_code(hidden.dtype))
+        experts_per_token=top_k, expert_offset=expert_offset, dtype=_code(hidden.dtype),
+        live_routes_hint=live_routes)
     _abi.call("nml_nvfp4_sm100_routed_swiglu", request)
     return out
 

@@ -66,7 +66,8 @@ class OracleBackend:
             out[ok] += values[index[ok, route]]
         return bits_to_tensor(oracle.from_f32(out, self.dtype))
 
-    def routed_experts(self, hidden, expert_ids, routing_weights, layer, expert_offset=0):
+    def routed_experts(self, hidden, expert_ids, routing_weights, layer, expert_offset=0,
+                       live_routes=0):
         tokens, top_k = expert_ids.shape
         ids = expert_ids.numpy().astype(np.int32) - expert_offset
         ids = np.where((expert_ids.numpy() >= 0) & (ids >= 0) & (ids < layer.experts_local), ids,
@@ -82,6 +83,22 @@ class OracleBackend:
             oracle.expert_down(activated, ids.ravel(), w.ravel(), down, down_bias), self.dtype)
         weighted[ids.ravel() < 0] = 0
         return bits_to_tensor(oracle.combine(weighted, tokens, top_k, self.dtype, mode=0))
+
+    def layer_f32(self, hidden, expert_ids, routing_weights, layer):
+        """The routed layer with the device path's narrowing of the two intermediates, as f32
+        BEFORE the final narrowing: the reference point of the GEMM bar for layer outputs."""
+        tokens, top_k = expert_ids.shape
+        ids = expert_ids.numpy().astype(np.int32)
+        x = oracle.to_f32(tensor_to_bits(hidden), self.dtype)
+        w = oracle.to_f32(tensor_to_bits(routing_weights), self.dtype)
+        gate, down = triple(layer.gate_up), triple(layer.down)
+        gate_bias = oracle.to_f32(tensor_to_bits(layer.gate_up_bias), self.dtype)
+        down_bias = oracle.to_f32(tensor_to_bits(layer.down_bias), self.dtype)
+        narrow = lambda v: oracle.to_f32(oracle.from_f32(v, self.dtype), self.dtype)
+        activated = narrow(oracle.expert_gate_up(x, ids.ravel(), top_k, gate, gate_bias))
+        weighted = narrow(oracle.expert_down(activated, ids.ravel(), w.ravel(), down, down_bias))
+        weighted[ids.ravel() < 0] = 0
+        return weighted.reshape(tokens, top_k, -1).sum(axis=1, dtype=np.float32)
 
     def linear(self, hidden, weight, bias=None):
         out16, _ = oracle.linear_16(tensor_to_bits(hidden), *triple(weight), self.dtype)

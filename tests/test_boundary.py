@@ -20,7 +20,7 @@ def test_library_exports_every_declared_symbol():
     lib = ctypes.CDLL(str(_abi.library_path()))
     for name in declared:
         assert getattr(lib, name) is not None
-    assert _abi.load().nml_nvfp4_sm100_abi_version() == 1
+    assert _abi.load().nml_nvfp4_sm100_abi_version() == 2
 
 
 def test_struct_sizes_match_reference_prefix():
