@@ -14,9 +14,15 @@ data-path collective).
 Prints ONE JSON line (rank 0).  `value` is whole-job TFLOP/s with inputs resident in HBM;
 `e2e` is the same pass driven from pinned host buffers with the host<->device copies inside
 the timed region; `roofline` describes the dominant kernel (the tcgen05 linear with its
-192/256-row activation tiles) against the measured bf16 tensor peak; `cpu_baseline` times the CPU
-restatement of the reference's kernel on this host.  `--impl reference` times only that CPU
-restatement (the reference itself is Rust behind Bazel and cannot be built here).
+192/256-row activation tiles) against the measured bf16 tensor peak, with the fraction of the
+nominal dense NVFP4 peak beside it; `shapes` holds every (shape, M) case, the M <= 64 ones
+timed cold from a CUDA graph over rotating weight copies against the measured HBM bandwidth;
+`cpu_baseline` times the CPU restatement of the reference's kernel on this host (before any
+GPU work).  `sharded`, printed last, holds the configurations that shard over GPUs: the
+routed layer (T = 4096 and the decode batch, every exchange schedule, outputs checked before
+they are timed), the vocabulary projection with merged per-shard candidates, and the
+GPT-OSS-20B-shaped decode step (batch 64, 4096 prior tokens).  `--impl reference` times only
+the CPU restatement (the reference itself is Rust behind Bazel and cannot be built here).
 """
 from __future__ import annotations
 
@@ -53,13 +59,13 @@ def parse_args():
     parser.add_argument("--no-detail", action="store_true", help="skip the per-shape table")
     parser.add_argument("--no-extras", action="store_true",
                         help="skip the sharded MoE / unembedding / embedding figures")
-    parser.add_argument("--graph-extras", action="store_true",
-                        help="also time the expert-parallel layer replayed from a CUDA graph "
-                             "(push and all-reduce schedules; removes the host time per call)")
+    parser.add_argument("--no-decode-step", action="store_true",
+                        help="skip the 24-layer decode step (its weights take ~15 s to build)")
+    parser.add_argument("--decode-layers", type=int, default=0,
+                        help="layers of the decode step (0: all 24; fewer only for quick runs, "
+                             "the record then says so)")
     parser.add_argument("--kernel-policy", type=int, default=0,
-                        help="nml_nvfp4_sm100_set_kernel_policy value (profiling captures: "
-                             "100 + BM forces the tile height, 1000 + BM with the "
-                             "shared-memory weight ring)")
+                        help="nml_nvfp4_sm100_set_kernel_policy value for this process")
     parser.add_argument("--rows", type=str, default="",
                         help="comma-separated subset of M values (profiling captures)")
     parser.add_argument("--shapes", type=str, default="",
@@ -86,6 +92,23 @@ def measured_peaks() -> dict:
                 "source": "measured"}
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
             "source": "fallback"}
+
+
+# Nominal dense NVFP4 tensor throughput of one B200 (NVIDIA's HGX B200 datasheet figure of
+# 144 PFLOP/s FP4 for 8 GPUs is with 2:4 sparsity; half of it, per GPU).  The parity-preserving
+# path multiplies exact 16-bit decodes of the weights with kind::f16, so its own ceiling is the
+# bf16 peak; this figure is printed beside it because the target is worded against it.
+NVFP4_DENSE_TFLOPS_NOMINAL = 9000.0
+
+
+def ncu_traffic(key: str):
+    """dram read + write bytes per launch of a captured kernel, from the data file kept next
+    to the ncu summaries (None when there is no capture for `key`)."""
+    path = ROOT / "profiles" / "ncu_traffic.json"
+    try:
+        return json.loads(path.read_text()).get(key)
+    except (OSError, ValueError):
+        return None
 
 
 class ClockSampler:
@@ -262,15 +285,14 @@ def run_ours(args) -> None:
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
-        # NCCL prints its version banner on stdout at any NCCL_DEBUG level; the contract is
-        # one JSON line on stdout.
-        os.environ.pop("NCCL_DEBUG", None)
         dist.init_process_group("nccl", device_id=device)
     _abi.load()
     if args.kernel_policy:
         _abi.set_kernel_policy(args.kernel_policy)
     shapes, rows = select(args)
     full_sweep = shapes == SHAPES and rows == ROWS
+    # the CPU leg runs before any GPU work, while no other thread of this process is busy
+    cpu_baseline = time_cpu_baseline() if rank == 0 and world == 1 and full_sweep else None
 
     generator = torch.Generator(device=device).manual_seed(1234 + rank)
     weights = {}
@@ -360,19 +382,20 @@ def run_ours(args) -> None:
         d_time = sum(durations[c] for c in dominant)
         achieved = d_flops / d_time / 1e12
         variants = sorted({f"{selected[c][0]}/BM={selected[c][1]}" for c in dominant})
+        traffic = ncu_traffic("gemm_kernel_bm256_gate_up_m16384")
         roofline = {"bound": "tensor",
                     "kernel": "umma::gemm_kernel dense, bf16 operands: " + ", ".join(variants),
                     "achieved": achieved, "peak": peaks["bf16_tflops_sustained"],
                     "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops_sustained"],
+                    "frac_of_nominal_dense_nvfp4_peak": achieved / NVFP4_DENSE_TFLOPS_NOMINAL,
+                    "nominal_dense_nvfp4_peak": NVFP4_DENSE_TFLOPS_NOMINAL,
                     "peak_source": f"bf16_tflops_sustained of {peaks['source']} "
                                    "(the kernel runs inside a long step); kind::f16 MMA on exact "
                                    "bf16 decodes of the NVFP4 weights",
                     "launches_per_step": len(dominant),
                     "avg_launch_ms": d_time / len(dominant) * 1e3,
-                    "traffic": NCU_TRAFFIC["gemm_kernel_large_tiles"],
-                    "traffic_case": "dram read+write bytes of one launch of 2880->5760 at "
-                                    "M=16384 (algorithmic 292e6); the other launches were "
-                                    "not captured"}
+                    "traffic": None if traffic is None else traffic["dram_bytes"],
+                    "traffic_case": None if traffic is None else traffic["case"]}
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -392,6 +415,18 @@ def run_ours(args) -> None:
     if rank == 0 and not args.no_detail:
         line["shapes"] = shape_table(cases, durations, weights, activations, outputs, peaks,
                                      selected)
+        small = [e for e in line["shapes"] if e["M"] <= 64 and e["name"] == "unembed"]
+        if small:
+            # the weight-streaming kernel on the one shape whose single launch is a clean HBM
+            # measurement (the 2880-class weights take about a microsecond at the roofline)
+            best = max(small, key=lambda e: e["frac_of_hbm_peak"])
+            traffic = ncu_traffic("stream_kernel_unembed_m1")
+            line["roofline_small_m"] = {
+                "bound": "hbm", "kernel": f"{best['kernel']} 2880->201088 at M={best['M']}",
+                "achieved": best["cold_gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": best["frac_of_hbm_peak"],
+                "traffic": None if traffic is None else traffic["dram_bytes"],
+                "traffic_case": None if traffic is None else traffic["case"]}
     if not args.no_e2e:
         line["e2e"] = end_to_end(args, cases, weights, activations, outputs, world, barrier,
                                  flops_per_pass)
@@ -401,29 +436,58 @@ def run_ours(args) -> None:
         head = weights.pop("unembed")
         weights.clear()
         torch.cuda.empty_cache()
-        extras = sharded_extras(args, rank, world, device, barrier, head, peaks)
+        sharded = sharded_extras(args, rank, world, device, barrier, head, peaks)
+        del head
+        torch.cuda.empty_cache()
+        if not args.no_decode_step:
+            sharded["decode_step"] = decode_step_figures(args, rank, world, device, barrier, peaks)
         if rank == 0:
-            line.update(extras)
             line["qkv_fused"] = qkv_fusion_figures(device)
+            line["sharded"] = sharded  # last, so that it survives a truncated record
     if rank == 0:
-        if world == 1 and full_sweep:
-            line["cpu_baseline"] = time_cpu_baseline()
+        if cpu_baseline is not None:
+            line["cpu_baseline"] = cpu_baseline
+            line["sharded"] = line.pop("sharded", None)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from ncu captures, filled in from
-# the summaries under profiles/ (None until a capture exists).
-NCU_TRAFFIC = {"gemm_kernel_large_tiles": 251.7e6}  # 2880->5760 at M=16384, BM=256 (292 MB algorithmic)
+def graph_replay_ms(fn, launches_per_replay: int, repeats: int = 5):
+    """Device time per call of `fn` when `launches_per_replay` calls are captured once in a
+    CUDA graph and replayed: no host time between the launches.  Best of `repeats` replays."""
+    import torch
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(launches_per_replay):
+            fn()
+    graph.replay()
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    best = float("inf")
+    for _ in range(repeats):
+        begin.record()
+        graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        best = min(best, begin.elapsed_time(end))
+    return best / launches_per_replay
 
 
 def shape_table(cases, durations, weights, activations, outputs, peaks, selected):
     """Per (shape, M) figures.  Large M: device time of the launch inside the timed region.
-    M <= 64 is HBM-bound and the four small weights fit in L2, so those cases are timed
-    again over a rotation of distinct weight copies (>= 600 MB in total) to read them cold
-    from HBM; the L2-warm time from the timed region is kept next to it."""
-    import torch
+    M <= 64 is HBM-bound, the roofline times of the four small weights are below a launch
+    latency and those weights fit in L2: these cases are timed from a CUDA graph of >= 100
+    launches that rotate over distinct weight copies (>= 600 MB in total), i.e. cold from HBM
+    and without host time between launches; the L2-warm graph time of one weight is kept next
+    to it."""
     from nml_b200 import ops
     table = []
     for name, k, n, m in cases:
@@ -437,27 +501,23 @@ def shape_table(cases, durations, weights, activations, outputs, peaks, selected
             weight = weights[name]
             weight_bytes = weight.payload.numel() + weight.block_scales.numel()
             copies = max(2, min(128, int(600e6 // weight_bytes) + 1))
-            if weight_bytes > 300e6:
-                copies = 3
             rotation = [ops.NvFp4Parameter(weight.name, weight.shape, weight.dtype,
                                            weight.payload.clone(), weight.block_scales.clone(),
                                            weight.global_scale) for _ in range(copies)]
             x, out = activations[(k, m)], outputs[(name, m)]
-            for w in rotation:  # warm-up pass (also pages the copies in)
-                ops.linear(x, w, out=out)
-            begin = torch.cuda.Event(enable_timing=True)
-            end = torch.cuda.Event(enable_timing=True)
-            repeats = 3
-            begin.record()
-            for _ in range(repeats):
-                for w in rotation:
-                    ops.linear(x, w, out=out)
-            end.record()
-            torch.cuda.synchronize()
-            cold = begin.elapsed_time(end) * 1e-3 / (repeats * copies)
+            state = {"next": 0}
+
+            def one_launch():
+                ops.linear(x, rotation[state["next"] % copies], out=out)
+                state["next"] += 1
+
+            launches = max(copies, -(-100 // copies) * copies)
+            cold = graph_replay_ms(one_launch, launches) * 1e-3
+            warm_graph = graph_replay_ms(lambda: ops.linear(x, rotation[0], out=out), 100) * 1e-3
             entry.update({"bound": "hbm", "cold_us": cold * 1e6, "cold_gbs": nbytes / cold / 1e9,
                           "frac_of_hbm_peak": nbytes / cold / 1e9 / peaks["hbm_gbs"],
-                          "weight_copies": copies})
+                          "l2_warm_us": warm_graph * 1e6, "weight_copies": copies,
+                          "timing": f"cuda graph of {launches} launches, best of 5 replays"})
             del rotation
         else:
             peak = peaks["bf16_tflops_sustained"]
@@ -556,8 +616,8 @@ def timed(fn, warmup, steps, barrier, world):
 
 
 def timed_from_graph(fn, steps, barrier, world):
-    """Device time per replay of `fn` captured once in a CUDA graph (collectives included), in
-    ms, max over ranks; None when the capture fails."""
+    """Device time per replay of `fn` captured once in a CUDA graph (collectives and waits for
+    other ranks included), in ms, max over ranks; None when the capture fails."""
     import torch
     import torch.distributed as dist
     try:
@@ -589,6 +649,23 @@ def timed_from_graph(fn, steps, barrier, world):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         elapsed = float(t.item())
     return elapsed
+
+
+def layer_check(actual, expected) -> dict:
+    """The layer bar of the parity tests on device tensors: mean relative error <= 2e-3
+    (denominator floored at 1 % of the RMS) and the reference's own elementwise bound for the
+    operator, |a - e| <= 6e-2 (1 + |e|) in bf16."""
+    a, e = actual.float(), expected.float()
+    floor = 0.01 * e.pow(2).mean().sqrt()
+    mean_rel = ((a - e).abs() / torch_maximum(e.abs(), floor)).mean().item()
+    mixed = ((a - e).abs() / (1 + e.abs())).max().item()
+    return {"mean_rel": mean_rel, "max_mixed": mixed,
+            "ok": bool(mean_rel <= 2e-3 and mixed <= 6e-2)}
+
+
+def torch_maximum(tensor, floor):
+    import torch
+    return torch.maximum(tensor, floor.expand_as(tensor))
 
 
 def qkv_fusion_figures(device) -> list:
@@ -630,15 +707,20 @@ def qkv_fusion_figures(device) -> list:
 
 def sharded_extras(args, rank, world, device, barrier, head, peaks) -> dict:
     """Figures for the configurations that shard over GPUs (not part of `value`):
-    config 2, the GPT-OSS-20B-shaped routed layer (T=4096, 32 experts, top-4), expert-parallel
-    over the job's ranks with the NCCL token all-to-all (fixed total work: strong scaling);
-    config 3, the packed embedding gather (8192 rows) and the 201088-wide unembedding at
-    M in {1, 64, 1024} column-sharded over the ranks."""
+    the GPT-OSS-20B-shaped routed layer at T = 4096 and at the decode batch of 64 (32 experts,
+    top-4), expert-parallel over the job's ranks with every exchange schedule (fixed total
+    work: strong scaling; efficiency = t(1) / (N t(N)) with t(1) the one-GPU layer over all
+    tokens timed in the same process); the packed embedding gather (8192 rows); the 201088-wide
+    unembedding at M in {1, 64, 1024}, column-sharded, as a sampler needs it (per-shard
+    candidates merged) and with all logit columns gathered.  Every routed-layer schedule is
+    checked on a sample of this rank's tokens against the one-GPU layer before it is timed; a
+    schedule whose check fails reports `unavailable` instead of a number."""
     import torch
+    import torch.distributed as dist
     from nml_b200 import expert_parallel as ep, ops, quantize
-    out = {}
+    out = {"n_gpus": world}
     generator = torch.Generator(device=device).manual_seed(99)  # same on every rank
-    hidden_size, inter, experts, top_k, tokens = 2880, 2880, 32, 4, 4096
+    hidden_size, inter, experts, top_k = 2880, 2880, 32, 4
 
     def normal(shape, std):
         return (torch.randn(shape, device=device, generator=generator) * std).to(torch.bfloat16)
@@ -647,56 +729,72 @@ def sharded_extras(args, rank, world, device, barrier, head, peaks) -> dict:
     down = quantize.quantize_parameter("down", normal((experts, hidden_size, inter), 0.02))
     gate_bias, down_bias = normal((experts, 2 * inter), 0.02), normal((experts, hidden_size), 0.02)
     router = normal((experts, hidden_size), 0.02)
-    x = normal((tokens, hidden_size), 1.0)
-    logits = (x.float() @ router.float().t()).contiguous()  # dense router, computed once
-    lo, hi = ep.shard_range(tokens, rank, world)
     layer = ep.LocalExperts.shard(gate_up, gate_bias, down, down_bias, rank, world)
-    del gate_up, down
-    torch.cuda.empty_cache()
-    x_local, logits_local = x[lo:hi].contiguous(), logits[lo:hi].contiguous()
-    moe_flops = 2.0 * tokens * top_k * (2 * inter * hidden_size + hidden_size * inter)
-    for schedule in ("alltoall", "push", "allreduce"):
-        moe = ep.ExpertParallelMoE(layer, top_k, schedule=schedule)
-        if schedule == "push":
-            # needs every rank's buffers mapped into this process (symmetric memory); a box
-            # that cannot do that gets a note instead of a number
+    moe_flops_per_token = 2.0 * top_k * (2 * inter * hidden_size + hidden_size * inter)
+    steps = max(args.steps, 5)
+    exchange = None
+    for label, tokens in (("moe_t4096", 4096), ("moe_decode64", 64)):
+        tokens = tokens // world * world
+        x = normal((tokens, hidden_size), 1.0)
+        logits = (x.float() @ router.float().t()).contiguous()  # dense router, computed once
+        lo, hi = ep.shard_range(tokens, rank, world)
+        x_local, logits_local = x[lo:hi].contiguous(), logits[lo:hi].contiguous()
+
+        def single():
+            return ops.routed_clamped_swiglu(x, logits, gate_up, gate_bias, down, down_bias, top_k)
+
+        t1_eager = timed(single, 3, steps, barrier, world)
+        t1_graph = timed_from_graph(single, steps, barrier, world)
+        t1 = t1_graph if t1_graph is not None else t1_eager
+        sample = slice(0, min(64, x_local.shape[0]))
+        expected = ops.routed_clamped_swiglu(x_local[sample], logits_local[sample], gate_up,
+                                             gate_bias, down, down_bias, top_k)
+        record = {"tokens": tokens, "experts": experts, "top_k": top_k, "scaling": "strong",
+                  "one_gpu": {"ms_per_layer": t1, "ms_eager": t1_eager,
+                              "tokens_per_s": tokens / (t1 * 1e-3),
+                              "tflops": moe_flops_per_token * tokens / (t1 * 1e-3) / 1e12,
+                              "weight_gbs": experts * 3 * inter * hidden_size * 0.5625 /
+                              (t1 * 1e-3) / 1e9},
+                  "schedules": {}}
+        for schedule in ("push", "alltoall", "allreduce"):
             try:
-                moe(x_local, logits_local)
+                moe = ep.ExpertParallelMoE(layer, top_k, schedule=schedule, exchange=exchange)
+                result = moe(x_local, logits_local)
                 torch.cuda.synchronize()
-            except Exception as error:  # noqa: BLE001
-                out["moe_push"] = {"unavailable": f"{type(error).__name__}: {error}"[:200]}
+                if schedule == "push":
+                    exchange = moe.exchange  # sized by the first (largest) batch, then reused
+            except Exception as error:  # noqa: BLE001 -- e.g. no peer mapping on this box
+                record["schedules"][schedule] = {
+                    "unavailable": f"{type(error).__name__}: {error}"[:200]}
                 continue
-        ms = timed(lambda: moe(x_local, logits_local), 3, max(args.steps, 5), barrier, world)
-        graph_ms = None
-        if args.graph_extras and schedule != "alltoall":  # all-to-all-v synchronises the host
-            graph_ms = timed_from_graph(lambda: moe(x_local, logits_local), max(args.steps, 5),
-                                        barrier, world)
-        out[f"moe_{schedule}"] = {
-            "ms_per_layer_from_cuda_graph": graph_ms,
-            "metric": "moe_layer_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
-            "ms_per_layer": ms, "tflops": moe_flops / (ms * 1e-3) / 1e12, "tokens": tokens,
-            "experts": experts, "top_k": top_k, "n_gpus": world, "scaling": "strong",
-            "schedule": schedule, "frac_of_bf16_peak":
-                moe_flops / (ms * 1e-3) / 1e12 / (world * peaks["bf16_tflops_sustained"])}
-    # decode-size batch (config 4's routed layer): 64 tokens
-    x64, l64 = x[:64 // world * world], logits[:64 // world * world]
-    lo, hi = ep.shard_range(x64.shape[0], rank, world)
-    moe = ep.ExpertParallelMoE(layer, top_k, schedule="allreduce")
-    ms = timed(lambda: moe(x64[lo:hi].contiguous(), l64[lo:hi].contiguous()), 3, 20, barrier,
-               world)
-    expert_bytes = experts * (2 * inter * hidden_size + hidden_size * inter) * 0.5625
-    out["moe_decode64"] = {"metric": "moe_layer_tokens_per_s", "value": x64.shape[0] / (ms * 1e-3),
-                           "unit": "tokens/s", "us_per_layer": ms * 1e3, "n_gpus": world,
-                           "schedule": "allreduce",
-                           "weight_gbs_if_all_experts_hit": expert_bytes / (ms * 1e-3) / 1e9}
-    del layer, moe
+            check = layer_check(result[sample], expected)
+            if world > 1:
+                verdict = torch.tensor([1.0 if check["ok"] else 0.0], device=device)
+                dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
+                check["ok"] = bool(verdict.item() == 1.0)
+            if not check["ok"]:
+                record["schedules"][schedule] = {"unavailable": "output check failed", **check}
+                continue
+            eager = timed(lambda: moe(x_local, logits_local), 3, steps, barrier, world)
+            graph = None
+            if schedule != "alltoall":  # the all-to-all-v needs its split sizes on the host
+                graph = timed_from_graph(lambda: moe(x_local, logits_local), steps, barrier, world)
+            ms = graph if graph is not None else eager
+            record["schedules"][schedule] = {
+                "checked": True, "check": check, "ms_per_layer": ms, "ms_eager": eager,
+                "timing": "cuda graph replay" if graph is not None else "eager launches",
+                "tokens_per_s": tokens / (ms * 1e-3),
+                "tflops": moe_flops_per_token * tokens / (ms * 1e-3) / 1e12,
+                "per_gpu_efficiency": t1 / (world * ms)}
+        out[label] = record
+    del layer, gate_up, down, exchange
     torch.cuda.empty_cache()
 
-    # config 3: embedding gather + column-sharded unembedding on the 201088 x 2880 table
+    # packed embedding gather + column-sharded unembedding on the 201088 x 2880 table
     ids = torch.randint(0, head.shape[0], (8192,), device=device, generator=generator,
                         dtype=torch.int32)
     rows = torch.empty((8192, hidden_size), dtype=torch.bfloat16, device=device)
-    ms = timed(lambda: ops.token_embedding(head, ids, out=rows), 3, 20, barrier, world)
+    ms = graph_replay_ms(lambda: ops.token_embedding(head, ids, out=rows), 20)
     gather_bytes = 8192 * (hidden_size // 2 + hidden_size // 16 + 2 * hidden_size + 4)
     out["embedding_gather"] = {"rows": 8192, "us": ms * 1e3, "gbs": gather_bytes / (ms * 1e-3) / 1e9,
                                "frac_of_hbm_peak": gather_bytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
@@ -704,14 +802,50 @@ def sharded_extras(args, rank, world, device, barrier, head, peaks) -> dict:
     sharded = ep.ShardedUnembedding(head)
     out["unembed_sharded"] = []
     for m in (1, 64, 1024):
-        h = x[:m].contiguous()
-        ms = timed(lambda: sharded(h, gather_rows=False), 3, 10, barrier, world)
+        h = normal((m, hidden_size), 1.0)
         flops = 2.0 * m * hidden_size * head.shape[0]
-        out["unembed_sharded"].append({
-            "M": m, "n_gpus": world, "us": ms * 1e3, "tflops": flops / (ms * 1e-3) / 1e12,
-            "weight_gbs": head.shape[0] * hidden_size * 0.5625 / (ms * 1e-3) / 1e9,
-            "includes": "local linear on N/G columns + all-gather of the logit columns"})
+        weight_bytes = head.shape[0] * hidden_size * 0.5625
+        entry = {"M": m}
+        for label, fn in (("top8_merged", lambda: sharded.topk(h, 8, gather_rows=False)),
+                          ("all_logits", lambda: sharded(h, gather_rows=False))):
+            ms = timed(fn, 3, 10, barrier, world)
+            entry[label] = {"us": ms * 1e3, "tflops": flops / (ms * 1e-3) / 1e12,
+                            "weight_gbs": weight_bytes / (ms * 1e-3) / 1e9}
+        out["unembed_sharded"].append(entry)
     return out
+
+
+def decode_step_figures(args, rank, world, device, barrier, peaks) -> dict:
+    """The GPT-OSS-20B-shaped decode step (24 layers, batch 64 over a KV cache of 4096 prior
+    tokens per sequence, page size 16; see nml_b200/decode_step.py): tokens/s of the whole job
+    and the fraction of the HBM bound of the step (packed weights touched + KV read + head).
+    Non-NVFP4 operators are torch stand-ins."""
+    import torch
+    from nml_b200 import decode_step
+    shape = decode_step.GptOssShape()
+    layers = args.decode_layers or shape.layers
+    batch, prior = 64, 4096
+    try:
+        model = decode_step.DecodeModel(shape, batch, prior, device, layers=layers)
+        model.step()
+        torch.cuda.synchronize()
+        barrier()
+        eager = timed(model.step, 2, 5, barrier, world)
+        graph = timed_from_graph(model.step, 10, barrier, world)
+    except Exception as error:  # noqa: BLE001
+        return {"unavailable": f"{type(error).__name__}: {error}"[:300]}
+    ms = graph if graph is not None else eager
+    ms_full = ms * shape.layers / layers  # the head and embedding are counted once too often
+    bound_bytes = shape.weight_bytes_per_step(batch, prior)
+    bound_ms = bound_bytes / world / (peaks["hbm_gbs"] * 1e9) * 1e3
+    return {"metric": "decode_tokens_per_s", "value": batch / (ms_full * 1e-3), "unit": "tokens/s",
+            "batch": batch, "prior_tokens": prior, "layers_run": layers, "n_gpus": world,
+            "ms_per_step": ms_full, "ms_eager": eager,
+            "timing": "cuda graph replay" if graph is not None else "eager launches",
+            "hbm_bound_ms_per_gpu": bound_ms, "frac_of_hbm_bound": bound_ms / ms_full,
+            "parallelism": "single" if world == 1 else
+            f"dp{world} attention, ep{world} experts (peer push), head columns / {world}",
+            "stand_ins": "RMSNorm, RoPE, cache write, attention, router, arg-max are torch ops"}
 
 
 def main() -> int:

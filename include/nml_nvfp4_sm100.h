@@ -443,6 +443,68 @@ int32_t nml_nvfp4_sm100_gather_rows(const NmlSm100GatherRows *request, char *err
 int32_t nml_nvfp4_sm100_combine_rows(const NmlSm100CombineRows *request, char *error_message,
                                      size_t error_message_capacity);
 
+/* Row-wise top-k of 16-bit logits, the per-shard half of a sampler's reduction over the
+ * column-sharded vocabulary projection (the reference plans a global top-k merge for its
+ * column-sharded head, PRODUCT.md:673-674; it has no kernel for it).  values[r, :] are the k
+ * largest logits of row r in descending order, indices[r, :] their columns plus
+ * `index_offset` (the shard's first vocabulary index); equal values go to the lower index.
+ * k <= 16 and ceil(columns / 8192) * k <= 512. */
+typedef struct NmlSm100TopkRows {
+  size_t struct_size;
+  const void *logits;      /* [rows, columns] dtype, rows `row_stride` elements apart */
+  float *values;           /* [rows, k] f32 */
+  int32_t *indices;        /* [rows, k] */
+  void *workspace;         /* nml_nvfp4_sm100_topk_rows_workspace_bytes(rows, columns, k) */
+  size_t workspace_bytes;
+  void *stream;
+  int64_t rows;
+  int64_t columns;
+  int64_t row_stride;
+  int64_t k;
+  int32_t index_offset;
+  int32_t dtype;
+} NmlSm100TopkRows;
+int32_t nml_nvfp4_sm100_topk_rows(const NmlSm100TopkRows *request, char *error_message,
+                                  size_t error_message_capacity);
+size_t nml_nvfp4_sm100_topk_rows_workspace_bytes(int64_t rows, int64_t columns, int64_t k);
+
+/* Paged-attention decode: one query token per sequence over a paged K/V cache, grouped-query
+ * heads, causal, optional sliding window and learned per-head sinks.  Not part of the
+ * reference's NVFP4 kernel ABI: it is the operator next to it in the product graph
+ * (Graph::paged_attention, crates/nml-ir/src/lib.rs:4717-4730, lowered on GPUs to the Triton
+ * kernels of crates/nml-kernel-triton/src/unified_attention.rs:82,189,755), provided because it
+ * moves the most bytes of a decode step after the expert weights.  Same argument meaning as
+ * the graph operator for a query length of one; the query is the last visible token.
+ * This kernel takes head_dim 64, page_size 16 and 8 query heads per kv head. */
+typedef struct NmlSm100PagedAttentionDecode {
+  size_t struct_size;
+  const void *query;               /* [batch, query_heads, head_dim] dtype */
+  const void *key_cache;           /* [physical_pages, page_size, kv_heads, head_dim] dtype */
+  const void *value_cache;         /* same shape */
+  const int32_t *page_table;       /* [batch, table_width] physical page of every logical page */
+  const int32_t *sequence_lengths; /* [batch] visible tokens, the query token included */
+  const float *sinks;              /* [query_heads] f32 or NULL */
+  void *output;                    /* [batch, query_heads, head_dim] dtype */
+  void *workspace;                 /* f32 scratch, ..._workspace_bytes(batch, query_heads, splits) */
+  size_t workspace_bytes;
+  void *stream;
+  int64_t batch;
+  int64_t query_heads;
+  int64_t kv_heads;
+  int64_t head_dim;
+  int64_t page_size;
+  int64_t physical_pages;
+  int64_t table_width;
+  int64_t sliding_window;          /* 0: none; else only the last `sliding_window` tokens */
+  int64_t splits;                  /* CTAs per (sequence, kv head) along the sequence, 1..64 */
+  float scale;                     /* softmax scale, usually head_dim^-0.5 */
+  int32_t dtype;
+} NmlSm100PagedAttentionDecode;
+int32_t nml_sm100_paged_attention_decode(const NmlSm100PagedAttentionDecode *request,
+                                         char *error_message, size_t error_message_capacity);
+size_t nml_sm100_paged_attention_decode_workspace_bytes(int64_t batch, int64_t query_heads,
+                                                        int64_t splits);
+
 /* Routed clamped-SwiGLU layer for callers that cannot hand over scratch memory.
  *
  * This entry point has no counterpart in the reference.  Some hosts of this library have

@@ -131,6 +131,23 @@ class CombineRows(ctypes.Structure):
                 ("hidden_size", _i64), ("row_count", _i64), ("dtype", _i32)]
 
 
+class TopkRows(ctypes.Structure):
+    _fields_ = [("struct_size", _sz), ("logits", _vp), ("values", _vp), ("indices", _vp),
+                ("workspace", _vp), ("workspace_bytes", _sz), ("stream", _vp), ("rows", _i64),
+                ("columns", _i64), ("row_stride", _i64), ("k", _i64), ("index_offset", _i32),
+                ("dtype", _i32)]
+
+
+class PagedAttentionDecode(ctypes.Structure):
+    _fields_ = [("struct_size", _sz), ("query", _vp), ("key_cache", _vp), ("value_cache", _vp),
+                ("page_table", _vp), ("sequence_lengths", _vp), ("sinks", _vp), ("output", _vp),
+                ("workspace", _vp), ("workspace_bytes", _sz), ("stream", _vp), ("batch", _i64),
+                ("query_heads", _i64), ("kv_heads", _i64), ("head_dim", _i64),
+                ("page_size", _i64), ("physical_pages", _i64), ("table_width", _i64),
+                ("sliding_window", _i64), ("splits", _i64), ("scale", ctypes.c_float),
+                ("dtype", _i32)]
+
+
 class RoutedWorkspaceLayout(ctypes.Structure):
     _fields_ = [("sorted_assignments", _sz), ("block_experts", _sz), ("active_blocks", _sz),
                 ("activated", _sz), ("weighted", _sz), ("permuted_hidden", _sz),
@@ -194,6 +211,8 @@ REQUEST_ENTRY_POINTS = {
     "nml_nvfp4_sm100_ep_dispatch_plan": EpDispatchPlan,
     "nml_nvfp4_sm100_gather_rows": GatherRows,
     "nml_nvfp4_sm100_combine_rows": CombineRows,
+    "nml_sm100_paged_attention_decode": PagedAttentionDecode,
+    "nml_nvfp4_sm100_topk_rows": TopkRows,
 }
 
 OTHER_ENTRY_POINTS = [
@@ -205,6 +224,8 @@ OTHER_ENTRY_POINTS = [
     "nml_nvfp4_sm100_last_linear_kernel",
     "nml_nvfp4_sm100_last_linear_tile_rows",
     "nml_nvfp4_sm100_abi_version",
+    "nml_sm100_paged_attention_decode_workspace_bytes",
+    "nml_nvfp4_sm100_topk_rows_workspace_bytes",
 ]
 
 
@@ -239,6 +260,10 @@ def load() -> ctypes.CDLL:
     lib.nml_nvfp4_sm100_routed_swiglu_workspace_layout.restype = _i32
     lib.nml_nvfp4_sm100_routed_swiglu_workspace_layout.argtypes = [_i64] * 5 + [
         ctypes.POINTER(RoutedWorkspaceLayout)]
+    lib.nml_nvfp4_sm100_topk_rows_workspace_bytes.restype = _sz
+    lib.nml_nvfp4_sm100_topk_rows_workspace_bytes.argtypes = [_i64] * 3
+    lib.nml_sm100_paged_attention_decode_workspace_bytes.restype = _sz
+    lib.nml_sm100_paged_attention_decode_workspace_bytes.argtypes = [_i64] * 3
     lib.nml_nvfp4_sm100_plan_capacity.restype = _i32
     lib.nml_nvfp4_sm100_plan_capacity.argtypes = [_i64, _i64, ctypes.POINTER(_i64),
                                                   ctypes.POINTER(_i64)]

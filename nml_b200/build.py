@@ -20,7 +20,7 @@ CSRC = HERE / "csrc"
 LIB_DIR = HERE / "lib"
 LIB_PATH = LIB_DIR / "libnml_nvfp4_sm100.so"
 SOURCES = ["abi.cu", "embedding.cu", "linear_simt.cu", "linear_umma.cu", "stream.cu", "moe.cu",
-           "experts_umma.cu", "ep.cu", "ep_push.cu"]
+           "experts_umma.cu", "ep.cu", "ep_push.cu", "attention_decode.cu", "topk.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -98,6 +98,69 @@ route_kernel(const float* __restrict__ logits, const uint8_t* __restrict__ activ
   }
 }
 
+// One warp routes one token, lane e holding expert e (up to 32 experts): the same operations
+// in the same order as route_kernel (maximum, exponentials, denominator summed in expert
+// order, k rounds of first-maximum selection with ties to the lower index), so the bits agree;
+// only the latency differs (decode-size batches spend longer in the one-thread-per-token
+// kernel than in an expert projection).
+template <typename T>
+__global__ void __launch_bounds__(128)
+route_warp_kernel(const float* __restrict__ logits, const uint8_t* __restrict__ active,
+                  int32_t* __restrict__ expert_ids, T* __restrict__ weights, int tokens,
+                  int experts, int top_k) {
+  const int lane = threadIdx.x & 31;
+  const int token = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (token >= tokens) return;
+  constexpr unsigned kAll = 0xffffffffu;
+  float probability = lane < experts ? logits[static_cast<int64_t>(token) * experts + lane]
+                                     : -INFINITY;
+  float maximum = probability;
+#pragma unroll
+  for (int offset = 16; offset != 0; offset >>= 1) {
+    maximum = fmaxf(maximum, __shfl_xor_sync(kAll, maximum, offset));
+  }
+  if (maximum > -INFINITY) {
+    if (lane < experts) probability = exp_deterministic(__fsub_rn(probability, maximum));
+    float denominator = 0.0f;
+    for (int e = 0; e < experts; ++e) {  // expert order, like the sequential kernel
+      denominator = __fadd_rn(denominator, __shfl_sync(kAll, probability, e));
+    }
+    probability = lane < experts ? __fdiv_rn(probability, denominator) : -1.0f;
+  } else {
+    probability = lane < experts ? 0.0f : -1.0f;
+  }
+  const bool is_active = active == nullptr || active[token] != 0;
+  float sum = 0.0f;
+  float mine = 0.0f;  // lane r keeps the r-th selected probability and id
+  int mine_id = 0;
+  for (int route = 0; route < top_k; ++route) {
+    // first maximum: larger value wins, equal values go to the lower lane
+    float best = probability;
+    int best_lane = lane;
+#pragma unroll
+    for (int offset = 16; offset != 0; offset >>= 1) {
+      const float other = __shfl_xor_sync(kAll, best, offset);
+      const int other_lane = __shfl_xor_sync(kAll, best_lane, offset);
+      if (other > best || (other == best && other_lane < best_lane)) {
+        best = other;
+        best_lane = other_lane;
+      }
+    }
+    if (lane == best_lane) probability = -3.0f;  // taken
+    if (lane == route) {
+      mine = best;
+      mine_id = best_lane;
+    }
+    sum = __fadd_rn(sum, best);
+  }
+  const float normalizer = fmaxf(sum, 1.1920928955078125e-7f);
+  if (lane < top_k) {
+    const int64_t a = static_cast<int64_t>(token) * top_k + lane;
+    expert_ids[a] = is_active ? mine_id : -1;
+    weights[a] = Elem<T>::store(is_active ? __fdiv_rn(mine, normalizer) : 0.0f);
+  }
+}
+
 // ====================================================================== assignment plan
 
 // Single-CTA construction of the schedule of crates/nml-ir/src/lib.rs:5644-5779.  Thread t
@@ -402,6 +465,20 @@ int32_t launch_route(const NmlSm100Route& r, char* message, size_t capacity) {
   const int top_k = static_cast<int>(r.experts_per_token);
   const unsigned grid = static_cast<unsigned>((tokens + 127) / 128);
   cudaStream_t stream = static_cast<cudaStream_t>(r.stream);
+  if (experts <= 32 && top_k <= 32 && tokens <= 4096) {
+    // few tokens: one warp per token
+    const unsigned warp_grid = static_cast<unsigned>((tokens + 3) / 4);
+    if (r.dtype == NML_SM100_F16) {
+      route_warp_kernel<__half><<<warp_grid, 128, 0, stream>>>(
+          r.logits, r.active_tokens, r.expert_ids, static_cast<__half*>(r.routing_weights),
+          tokens, experts, top_k);
+    } else {
+      route_warp_kernel<__nv_bfloat16><<<warp_grid, 128, 0, stream>>>(
+          r.logits, r.active_tokens, r.expert_ids,
+          static_cast<__nv_bfloat16*>(r.routing_weights), tokens, experts, top_k);
+    }
+    return launch_result(message, capacity);
+  }
 #define NML_ROUTE(MAXE, T)                                                                  \
   route_kernel<MAXE, T><<<grid, 128, 0, stream>>>(r.logits, r.active_tokens, r.expert_ids,   \
                                                   static_cast<T*>(r.routing_weights), tokens, \
@@ -431,7 +508,10 @@ int32_t launch_assignment_plan(const int32_t* expert_ids, int32_t* sorted_assign
                                int experts, int expert_offset, int positions, int blocks,
                                int device, cudaStream_t stream, char* message, size_t capacity) {
   // threads * experts histogram words must fit the shared memory requested below.
-  int threads = 1024;
+  // one thread per couple of assignments for small batches (the per-thread histograms make
+  // the kernel's fixed cost grow with the thread count), up to 1024
+  int threads = 32;
+  while (threads < 1024 && threads * 2 < assignments) threads <<= 1;
   while (threads > 32 && static_cast<int64_t>(threads) * experts > 32768) threads >>= 1;
   const size_t smem = (static_cast<size_t>(threads) * experts + 2 * experts + 2) * 4;
   static std::atomic<int> configured[64];

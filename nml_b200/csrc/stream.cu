@@ -38,7 +38,7 @@ int32_t launch_variant(const Params& p, int smem_bytes, int64_t units_bound,
   }
   const unsigned grid =
       static_cast<unsigned>(units_bound < device.sm_count ? units_bound : device.sm_count);
-  const unsigned threads = static_cast<unsigned>((p.compute_warps + 2) * 32);
+  const unsigned threads = static_cast<unsigned>((p.compute_warps + NT + 1) * 32);
   kernel<<<grid, threads, smem_bytes, stream>>>(p);
   return launch_result(message, capacity);
 }

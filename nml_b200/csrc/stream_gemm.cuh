@@ -21,7 +21,8 @@
 // f32 accumulation.  No tensor memory, no decoded tile in shared memory, no per-K-step
 // hand-off between warps.  Per tile every compute warp leaves its 16 x 8 (x NT) partial sums
 // in a ring of shared-memory slots; the reducer warp adds them in warp order (ascending K, so
-// the result is deterministic), applies the global scale and the mode's epilogue, and stores.
+// the result is deterministic), applies the global scale and the mode's epilogue, and stores
+// (one reducer warp per tile of 8 activation rows).
 //
 // bf16 activations: mma.sync wants both operands in one format and the decoded weights are
 // f16, so every warp rescales its slice of each activation row by a power of two that puts
@@ -51,7 +52,7 @@ enum Mode : int { kDense = 0, kGateUp = 1, kDown = 2 };
 constexpr int kTileRows = 16;
 constexpr int kUnitK = 64;            // K values of one unit: a quad of lanes reads 32 bytes per row
 constexpr int kMaxComputeWarps = 16;
-constexpr int kMaxThreads = (kMaxComputeWarps + 2) * 32;  // + reducer warp + producer warp
+constexpr int kMaxThreads = (kMaxComputeWarps + 3) * 32;  // + reducer warp(s) + producer warp
 constexpr int kMaxStages = 4;         // weight tiles in flight per CTA (more were measured to add nothing)
 constexpr int kSlots = 4;             // partial-sum slots between compute warps and reducer
 constexpr int kSmemBudget = 227 * 1024;
@@ -204,7 +205,7 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
     }
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(&full_s[s], W);
-      mbar_init(&empty_s[s], 1);
+      mbar_init(&empty_s[s], NT);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -441,7 +442,7 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
       if (lane == 0) mbar_arrive(&full_s[slots.index]);
       slots.advance(kSlots);
     }
-  } else if (warp == W + 1) {
+  } else if (warp == W + NT) {
     // ------------------------------------------------------------------ producer
     // Lane 0 owns the ring (waits, transaction counts); when rows are padded in shared memory
     // and have to be copied one by one, payload row r is issued by lane r and scale row r by
@@ -520,44 +521,39 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
     }
   } else {
     // -------------------------------------------------------------------- reducer
+    // One reducer warp per activation-row tile of 8: warp W + jn sums and finishes tile jn.
+    const int jn = warp - W;
     Ring slots;
     int loaded_group = -1;
     // grouped: the assignment (output row) and routing weight of this lane's columns
-    int32_t target[NT][2];
-    float route_weight[NT][2];
+    int32_t target[2];
+    float route_weight[2];
     for (Walk w = walk_begin(); w.unit < last; walk_next(w)) {
       if constexpr (kGrouped) {
         if (loaded_group != w.group) {
 #pragma unroll
-          for (int jn = 0; jn < NT; ++jn) {
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-              const int32_t a = p.sorted_assignments[w.group * 16 + 8 * jn + 2 * c + i];
-              const bool valid = a >= 0 && a < p.assignments;
-              target[jn][i] = valid ? a : -1;
-              route_weight[jn][i] = 0.0f;
-              if (MODE == kDown && valid) {
-                route_weight[jn][i] = Elem<T>::load(static_cast<const T*>(p.routing_weights)[a]);
-              }
+          for (int i = 0; i < 2; ++i) {
+            const int32_t a = p.sorted_assignments[w.group * 16 + 8 * jn + 2 * c + i];
+            const bool valid = a >= 0 && a < p.assignments;
+            target[i] = valid ? a : -1;
+            route_weight[i] = 0.0f;
+            if (MODE == kDown && valid) {
+              route_weight[i] = Elem<T>::load(static_cast<const T*>(p.routing_weights)[a]);
             }
           }
           loaded_group = w.group;
         }
       }
       if (!wait(&full_s[slots.index], slots.phase, kSiteReducer)) break;
-      float4 sum[NT];
-      const float4* slot = partials + (slots.index * W) * NT * 32 + lane;
-#pragma unroll
-      for (int jn = 0; jn < NT; ++jn) sum[jn] = slot[jn * 32];
+      const float4* slot = partials + ((slots.index * W) * NT + jn) * 32 + lane;
+      float4 sum = slot[0];
+#pragma unroll 4
       for (int cw = 1; cw < W; ++cw) {  // ascending K
-#pragma unroll
-        for (int jn = 0; jn < NT; ++jn) {
-          const float4 v = slot[(cw * NT + jn) * 32];
-          sum[jn].x = __fadd_rn(sum[jn].x, v.x);
-          sum[jn].y = __fadd_rn(sum[jn].y, v.y);
-          sum[jn].z = __fadd_rn(sum[jn].z, v.z);
-          sum[jn].w = __fadd_rn(sum[jn].w, v.w);
-        }
+        const float4 v = slot[cw * NT * 32];
+        sum.x = __fadd_rn(sum.x, v.x);
+        sum.y = __fadd_rn(sum.y, v.y);
+        sum.z = __fadd_rn(sum.z, v.z);
+        sum.w = __fadd_rn(sum.w, v.w);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_s[slots.index]);
@@ -577,19 +573,16 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
           const int n = n0 + 8 * half;
           if (n < segment.outputs) {
             const float bias_value = bias != nullptr ? Elem<T>::load(bias[n]) : 0.0f;
-#pragma unroll
-            for (int jn = 0; jn < NT; ++jn) {
-              const float v0 = half == 0 ? sum[jn].x : sum[jn].z;
-              const float v1 = half == 0 ? sum[jn].y : sum[jn].w;
-              const int m = w.group * 16 + 8 * jn + 2 * c;
-              if (m < p.M) {
-                out[static_cast<int64_t>(m) * segment.outputs + n] =
-                    Elem<T>::store(fmaf(v0, scale, bias_value));
-              }
-              if (m + 1 < p.M) {
-                out[static_cast<int64_t>(m + 1) * segment.outputs + n] =
-                    Elem<T>::store(fmaf(v1, scale, bias_value));
-              }
+            const float v0 = half == 0 ? sum.x : sum.z;
+            const float v1 = half == 0 ? sum.y : sum.w;
+            const int m = w.group * 16 + 8 * jn + 2 * c;
+            if (m < p.M) {
+              out[static_cast<int64_t>(m) * segment.outputs + n] =
+                  Elem<T>::store(fmaf(v0, scale, bias_value));
+            }
+            if (m + 1 < p.M) {
+              out[static_cast<int64_t>(m + 1) * segment.outputs + n] =
+                  Elem<T>::store(fmaf(v1, scale, bias_value));
             }
           }
         }
@@ -604,25 +597,29 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
           const int n = n0 + 8 * half;  // weight row inside the expert
           const bool n_ok = n < p.rows_per_expert;
           const float bias_value = n_ok ? Elem<T>::load(bias[n]) : 0.0f;
-#pragma unroll
-          for (int jn = 0; jn < NT; ++jn) {
-            const float v[2] = {fmaf(half == 0 ? sum[jn].x : sum[jn].z, scale, bias_value),
-                                fmaf(half == 0 ? sum[jn].y : sum[jn].w, scale, bias_value)};
+          const float v[2] = {fmaf(half == 0 ? sum.x : sum.z, scale, bias_value),
+                              fmaf(half == 0 ? sum.y : sum.w, scale, bias_value)};
+          if constexpr (MODE == kGateUp) {
+            // Even weight rows carry gate, odd rows up of the same intermediate column, and
+            // the lane four further on holds the partner row.  The even lane finishes
+            // activation row 2 c, the odd lane row 2 c + 1, so both halves of the warp share
+            // the SwiGLU evaluations.
+            const bool odd = (g & 1) != 0;
+            const float received0 = __shfl_xor_sync(0xffffffffu, v[0], 4);
+            const float received1 = __shfl_xor_sync(0xffffffffu, v[1], 4);
+            const float gate = odd ? received1 : v[0];
+            const float up = odd ? v[1] : received0;
+            const int32_t row = odd ? target[1] : target[0];
+            if (n_ok && row >= 0) {
+              out[static_cast<int64_t>(row) * p.N + (n >> 1)] =
+                  Elem<T>::store(clamped_swiglu(gate, up));
+            }
+          } else {
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
-              if constexpr (MODE == kGateUp) {
-                // even weight rows carry gate, odd rows up of the same intermediate column:
-                // the lane four further on holds the partner row
-                const float partner = __shfl_xor_sync(0xffffffffu, v[i], 4);
-                if ((g & 1) == 0 && n_ok && target[jn][i] >= 0) {
-                  out[static_cast<int64_t>(target[jn][i]) * p.N + (n >> 1)] =
-                      Elem<T>::store(clamped_swiglu(v[i], partner));
-                }
-              } else {
-                if (n_ok && target[jn][i] >= 0) {
-                  out[static_cast<int64_t>(target[jn][i]) * p.N + n] =
-                      Elem<T>::store(v[i] * route_weight[jn][i]);
-                }
+              if (n_ok && target[i] >= 0) {
+                out[static_cast<int64_t>(target[i]) * p.N + n] =
+                    Elem<T>::store(v[i] * route_weight[i]);
               }
             }
           }

@@ -133,6 +133,10 @@ class CudaBackend:
     def linear(self, hidden, weight, bias=None):
         return ops.linear(hidden, weight, bias)
 
+    def topk(self, logits, k, index_offset):
+        values, indices = ops.topk_rows(logits, k, index_offset)
+        return values, indices.long()
+
 
 @dataclass
 class LocalExperts:
@@ -392,9 +396,15 @@ class ShardedUnembedding:
     """The vocabulary projection with output columns sharded over the ranks of ``group``.
 
     Rank r holds rows [r*N/G, (r+1)*N/G) of the packed table (payload and block scales sliced
-    on axis 0, global scale replicated).  ``forward`` all-gathers the batch-sharded hidden
-    rows, runs the local linear and all-gathers the logit columns; every logit is produced by
-    the same kernel as on one GPU, so the result is bit-identical to the unsharded call.
+    on axis 0, global scale replicated).  Every logit is produced by the same kernels as on
+    one GPU.  What leaves a rank is chosen by the caller:
+
+    ``forward``  all logits on every rank (an all-gather of the logit columns: rows x N values
+                 land on every rank, which is what bounds it);
+    ``topk`` / ``argmax``  each rank reduces its own columns to k candidates per row and only
+                 those k * G (value, index) pairs are exchanged and merged, which is all a
+                 sampler needs (the reference plans the same for its column-sharded head,
+                 PRODUCT.md:673-674).  Ties go to the lower vocabulary index.
     """
 
     def __init__(self, weight, group=None, backend=None, already_sharded: bool = False):
@@ -409,17 +419,19 @@ class ShardedUnembedding:
             start, stop = shard_range(weight.shape[0], self.rank, self.world)
             self.weight = weight.slice_rows(start, stop)
             self.columns_total = weight.shape[0]
+        self.column_offset = self.rank * (self.columns_total // self.world)
+
+    def _all_rows(self, hidden: torch.Tensor, gather_rows: bool) -> torch.Tensor:
+        if self.world > 1 and gather_rows:
+            all_hidden = torch.empty((self.world * hidden.shape[0], hidden.shape[1]),
+                                     dtype=hidden.dtype, device=hidden.device)
+            dist.all_gather_into_tensor(all_hidden, hidden.contiguous(), group=self.group)
+            return all_hidden
+        return hidden
 
     def forward(self, hidden: torch.Tensor, gather_rows: bool = True,
                 gather_columns: bool = True) -> torch.Tensor:
-        rows = hidden.shape[0]
-        if self.world > 1 and gather_rows:
-            all_hidden = torch.empty((self.world * rows, hidden.shape[1]), dtype=hidden.dtype,
-                                     device=hidden.device)
-            dist.all_gather_into_tensor(all_hidden, hidden.contiguous(), group=self.group)
-        else:
-            all_hidden = hidden
-        local = self.backend.linear(all_hidden, self.weight)  # [rows_total, N / G]
+        local = self.backend.linear(self._all_rows(hidden, gather_rows), self.weight)
         if self.world == 1 or not gather_columns:
             return local
         gathered = torch.empty((self.world * local.shape[0], local.shape[1]), dtype=local.dtype,
@@ -429,3 +441,40 @@ class ShardedUnembedding:
             1, 0, 2).reshape(local.shape[0], self.columns_total)
 
     __call__ = forward
+
+    def topk(self, hidden: torch.Tensor, k: int, gather_rows: bool = True):
+        """(values f32 [rows, k], vocabulary indices i64 [rows, k]) of the k largest logits of
+        every row, rows of all ranks when ``gather_rows`` (else of ``hidden`` as given, which
+        must then be the same on every rank)."""
+        local = self.backend.linear(self._all_rows(hidden, gather_rows), self.weight)
+        values, indices = self.backend.topk(local, k, self.column_offset)
+        if self.world == 1:
+            return values, indices
+        rows = local.shape[0]
+        packed = torch.cat((values, indices.float()), dim=1) \
+            if self.columns_total < (1 << 24) else None
+        if packed is not None:  # indices below 2^24 are exact in f32: one collective
+            gathered = torch.empty((self.world, rows, 2 * k), dtype=torch.float32,
+                                   device=local.device)
+            dist.all_gather_into_tensor(gathered.view(self.world * rows, 2 * k), packed,
+                                        group=self.group)
+            all_values = gathered[:, :, :k].permute(1, 0, 2).reshape(rows, self.world * k)
+            all_indices = gathered[:, :, k:].permute(1, 0, 2).reshape(rows, self.world * k).long()
+        else:
+            gv = torch.empty((self.world * rows, k), dtype=torch.float32, device=local.device)
+            gi = torch.empty((self.world * rows, k), dtype=torch.int64, device=local.device)
+            dist.all_gather_into_tensor(gv, values.contiguous(), group=self.group)
+            dist.all_gather_into_tensor(gi, indices.contiguous(), group=self.group)
+            all_values = gv.view(self.world, rows, k).permute(1, 0, 2).reshape(rows, -1)
+            all_indices = gi.view(self.world, rows, k).permute(1, 0, 2).reshape(rows, -1)
+        # candidates are ordered by rank, i.e. by vocabulary index inside equal values
+        best, position = torch.topk(all_values, k, dim=1)
+        return best, torch.gather(all_indices, 1, position)
+
+    def argmax(self, hidden: torch.Tensor, gather_rows: bool = True) -> torch.Tensor:
+        """Greedy pick for this rank's rows of ``hidden`` (i64 [rows])."""
+        rows = hidden.shape[0]
+        _, indices = self.topk(hidden, 1, gather_rows)
+        if self.world > 1 and gather_rows:
+            return indices[self.rank * rows:(self.rank + 1) * rows, 0]
+        return indices[:, 0]

@@ -437,3 +437,85 @@ def routed_clamped_swiglu_masked(hidden: torch.Tensor, router_logits: torch.Tens
     ids, weights = route(router_logits, experts_per_token, hidden.dtype, active_tokens)
     return routed_experts(hidden, ids, weights, gate_up_weights, gate_up_bias, down_weights,
                           down_bias)
+
+
+# ------------------------------------------------------------------ attention (decode)
+
+_ATTENTION_SCRATCH: dict = {}
+
+
+def paged_attention_decode(query: torch.Tensor, key_cache: torch.Tensor,
+                           value_cache: torch.Tensor, page_table: torch.Tensor,
+                           sequence_lengths: torch.Tensor, sinks: torch.Tensor | None = None,
+                           sliding_window: int | None = None, scale: float | None = None,
+                           splits: int | None = None) -> torch.Tensor:
+    """One query token per sequence over a paged K/V cache
+    (``Graph::paged_attention``, crates/nml-ir/src/lib.rs:4717-4730, for a query length of one).
+
+    ``query`` [batch, query_heads, head_dim]; caches [physical_pages, page_size, kv_heads,
+    head_dim]; ``page_table`` i32 [batch, logical_pages]; ``sequence_lengths`` i32 [batch]
+    (visible tokens, the query token included); ``sinks`` f32 [query_heads] or None."""
+    if query.dim() != 3 or key_cache.dim() != 4 or key_cache.shape != value_cache.shape:
+        raise ValueError("paged attention expects query [batch, heads, dim] and K/V caches "
+                         "[pages, page_size, kv_heads, dim] of one shape")
+    batch, query_heads, head_dim = query.shape
+    pages, page_size, kv_heads, cache_dim = key_cache.shape
+    if cache_dim != head_dim or query_heads % kv_heads != 0:
+        raise ValueError("paged query/KV head geometry is incompatible")
+    if query.dtype != key_cache.dtype or query.dtype != value_cache.dtype:
+        raise ValueError("query and paged K/V cache dtypes must match")
+    if page_table.dtype != torch.int32 or sequence_lengths.dtype != torch.int32 or \
+            page_table.dim() != 2 or page_table.shape[0] != batch or \
+            tuple(sequence_lengths.shape) != (batch,):
+        raise ValueError("page table must be I32 [batch, pages], sequence lengths I32 [batch]")
+    if sinks is not None and (sinks.dtype != torch.float32 or tuple(sinks.shape) != (query_heads,)):
+        raise ValueError("attention sinks must be F32 [query_heads]")
+    _require_cuda(query, key_cache, value_cache, page_table, sequence_lengths, sinks)
+    if splits is None:
+        # enough CTAs for a few waves over the SMs, at most one split per 8 pages
+        sms = torch.cuda.get_device_properties(query.device).multi_processor_count
+        wanted = -(-4 * sms // max(1, batch * kv_heads))
+        visible = page_table.shape[1] if not sliding_window else -(-sliding_window // page_size) + 1
+        splits = max(1, min(wanted, max(1, visible // 8), 64))
+    lib = _abi.load()
+    size = lib.nml_sm100_paged_attention_decode_workspace_bytes(batch, query_heads, splits)
+    key = (query.device, torch.cuda.current_stream(query.device).cuda_stream)
+    scratch = _ATTENTION_SCRATCH.get(key)
+    if scratch is None or scratch.numel() < size:
+        scratch = torch.empty(size, dtype=torch.uint8, device=query.device)
+        _ATTENTION_SCRATCH[key] = scratch
+    out = torch.empty_like(query)
+    request = _abi.PagedAttentionDecode(
+        query=_ptr(query), key_cache=_ptr(key_cache), value_cache=_ptr(value_cache),
+        page_table=_ptr(page_table), sequence_lengths=_ptr(sequence_lengths), sinks=_ptr(sinks),
+        output=_ptr(out), workspace=_ptr(scratch), workspace_bytes=scratch.numel(),
+        stream=_stream(query), batch=batch, query_heads=query_heads, kv_heads=kv_heads,
+        head_dim=head_dim, page_size=page_size, physical_pages=pages,
+        table_width=page_table.shape[1], sliding_window=sliding_window or 0, splits=splits,
+        scale=float(scale if scale is not None else head_dim ** -0.5), dtype=_code(query.dtype))
+    _abi.call("nml_sm100_paged_attention_decode", request)
+    return out
+
+
+def topk_rows(logits: torch.Tensor, k: int, index_offset: int = 0):
+    """(values f32 [rows, k], indices i32 [rows, k]) of the k largest entries of every row of a
+    16-bit matrix, descending, equal values to the lower index (``nml_nvfp4_sm100_topk_rows``)."""
+    if logits.dim() != 2 or logits.stride(1) != 1:
+        raise ValueError("top-k expects a matrix with contiguous rows")
+    rows, columns = logits.shape
+    if not 0 < k <= min(16, columns):
+        raise ValueError("top-k supports 1 <= k <= 16")
+    if not logits.is_cuda:
+        raise RuntimeError("NVFP4 operators run on a CUDA device only (no CPU fallback)")
+    lib = _abi.load()
+    size = lib.nml_nvfp4_sm100_topk_rows_workspace_bytes(rows, columns, k)
+    scratch = torch.empty(size, dtype=torch.uint8, device=logits.device)
+    values = torch.empty((rows, k), dtype=torch.float32, device=logits.device)
+    indices = torch.empty((rows, k), dtype=torch.int32, device=logits.device)
+    request = _abi.TopkRows(logits=_ptr(logits), values=_ptr(values), indices=_ptr(indices),
+                            workspace=_ptr(scratch), workspace_bytes=size,
+                            stream=_stream(logits), rows=rows, columns=columns,
+                            row_stride=logits.stride(0), k=k, index_offset=index_offset,
+                            dtype=_code(logits.dtype))
+    _abi.call("nml_nvfp4_sm100_topk_rows", request)
+    return values, indices

@@ -84,6 +84,11 @@ class OracleBackend:
         weighted[ids.ravel() < 0] = 0
         return bits_to_tensor(oracle.combine(weighted, tokens, top_k, self.dtype, mode=0))
 
+    def topk(self, logits, k, index_offset):
+        # descending, equal values to the lower index (a stable sort keeps index order)
+        values, order = torch.sort(logits.float(), dim=1, descending=True, stable=True)
+        return values[:, :k].contiguous(), (order[:, :k] + index_offset).contiguous()
+
     def layer_f32(self, hidden, expert_ids, routing_weights, layer):
         """The routed layer with the device path's narrowing of the two intermediates, as f32
         BEFORE the final narrowing: the reference point of the GEMM bar for layer outputs."""

@@ -41,7 +41,8 @@ def assert_gemm_close(actual_f32: np.ndarray, expected_f32: np.ndarray, what: st
     return m
 
 
-def assert_layer_close(actual_f32: np.ndarray, expected_f32: np.ndarray, what: str = ""):
+def assert_layer_close(actual_f32: np.ndarray, expected_f32: np.ndarray, what: str = "",
+                       mean_bar: float = 2e-3):
     """The bar for outputs of the whole routed layer (after the k-way sum of rows that were
     narrowed to the activation dtype).  The mean relative error keeps the GEMM bar (<= 2e-3).
     The elementwise bound is the reference's own one for this operator, |a - e| <= t + t |e|
@@ -49,5 +50,6 @@ def assert_layer_close(actual_f32: np.ndarray, expected_f32: np.ndarray, what: s
     in one narrowed term is 2^-8 of that term, and the sum of the k terms can be far smaller
     than the term, so a max *relative* error has no fixed bound here."""
     m = oracle.error_metrics(actual_f32, expected_f32)
-    assert m["mean_rel"] <= 2e-3 and m["max_mixed"] <= 6e-2 and m["norm_rel"] <= 5e-3, (what, m)
+    assert m["mean_rel"] <= mean_bar and m["max_mixed"] <= 6e-2 and m["norm_rel"] <= 5e-3, (
+        what, m)
     return m

@@ -15,7 +15,7 @@ HEADER = (ROOT / "include" / "nml_nvfp4_sm100.h").read_text()
 
 
 def test_library_exports_every_declared_symbol():
-    declared = set(re.findall(r"\b(nml_nvfp4_sm100_[a-z0-9_]+)\s*\(", HEADER))
+    declared = set(re.findall(r"\b(nml_(?:nvfp4_)?sm100_[a-z0-9_]+)\s*\(", HEADER))
     assert declared == set(_abi.REQUEST_ENTRY_POINTS) | set(_abi.OTHER_ENTRY_POINTS)
     lib = ctypes.CDLL(str(_abi.library_path()))
     for name in declared:

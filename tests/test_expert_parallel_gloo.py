@@ -58,6 +58,11 @@ def worker(rank, world, port, schedule, results):
             logits_out = head(x[lo:hi].contiguous())
             reference = backend.linear(x, table)
             results[("unembed", rank)] = (tensor_to_bits(logits_out), tensor_to_bits(reference))
+            # the sampler's view: per-shard candidates merged across ranks
+            values, indices = head.topk(x[lo:hi].contiguous(), 3)
+            picked = head.argmax(x[lo:hi].contiguous())
+            results[("topk", rank)] = (values.numpy(), indices.numpy(), picked.numpy(),
+                                       reference.float().numpy(), lo, hi)
     finally:
         dist.destroy_process_group()
 
@@ -86,6 +91,11 @@ def test_two_cpu_ranks(schedule):
         for rank in range(world):
             got, reference = results[("unembed", rank)]
             assert np.array_equal(got, reference)
+            values, indices, picked, logits, lo, hi = results[("topk", rank)]
+            order = np.argsort(-logits, axis=1, kind="stable")[:, :3]  # ties: lower index first
+            assert np.array_equal(values, np.take_along_axis(logits, order, axis=1))
+            assert np.array_equal(np.take_along_axis(logits, indices, axis=1), values)
+            assert np.array_equal(picked, order[lo:hi, 0])
 
 
 def test_shard_range_follows_the_contiguous_rule():

@@ -217,5 +217,12 @@ def test_nccl_ranks_match_single_device_evaluation():
         outcome = results[rank]
         for schedule in ("alltoall", "allreduce", "push", "unembed"):
             out, expected = outcome[schedule]
-            check = gu.assert_gemm_close if schedule == "unembed" else gu.assert_layer_close
-            check(oracle.to_f32(out, oracle.BF16), expected, f"{schedule} rank {rank} of {world}")
+            what = f"{schedule} rank {rank} of {world}"
+            if schedule == "unembed":
+                gu.assert_gemm_close(oracle.to_f32(out, oracle.BF16), expected, what)
+            else:
+                # the all-reduce schedule (the reference's scheme) narrows every rank's partial
+                # sum and reduces in the activation dtype: roundings the token exchange does
+                # not have, hence three times the mean bar
+                gu.assert_layer_close(oracle.to_f32(out, oracle.BF16), expected, what,
+                                      mean_bar=6e-3 if schedule == "allreduce" else 2e-3)
