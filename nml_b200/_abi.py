@@ -23,6 +23,8 @@ STATUS_TMEM_ALLOC = 2
 STATUS_INDEX_RANGE = 4
 STATUS_PEER_TIMEOUT = 8
 
+ROUTED_LEAVE_MASKED_ROWS = 1
+
 STATIC_SCRATCH_BYTES = 8 << 20
 
 POLICY_AUTO = 0
@@ -109,7 +111,7 @@ class RoutedSwiglu(ctypes.Structure):
                 ("workspace", _vp), ("workspace_bytes", _sz), ("stream", _vp), ("tokens", _i64),
                 ("hidden_size", _i64), ("intermediate_size", _i64), ("experts", _i64),
                 ("experts_per_token", _i64), ("expert_offset", _i32), ("dtype", _i32),
-                ("live_routes_hint", _i64)]
+                ("live_routes_hint", _i64), ("flags", _i32)]
 
 
 class EpDispatchPlan(ctypes.Structure):

@@ -757,8 +757,13 @@ extern "C" int32_t nml_nvfp4_sm100_routed_swiglu(const NmlSm100RoutedSwiglu* req
                 "NVFP4 routed SwiGLU: the down projection cannot read slot-ordered rows",
                 error_message, error_message_capacity);
   }
+  const bool rows_are_routes =
+      request->experts_per_token == 1 &&
+      has_field(request, offsetof(NmlSm100RoutedSwiglu, flags), sizeof(int32_t)) &&
+      (request->flags & NML_SM100_ROUTED_LEAVE_MASKED_ROWS) != 0;
+  if (rows_are_routes) args.output = request->output;  // assignment a is token a
   status = dispatch_experts(args, *device, error_message, error_message_capacity);
-  if (status != NML_SM100_OK) return status;
+  if (status != NML_SM100_OK || rows_are_routes) return status;
 
   return launch_combine(weighted, request->expert_ids, request->output,
                         static_cast<int>(request->tokens),

@@ -120,17 +120,20 @@ __device__ __forceinline__ unsigned wait_for_epoch(const int32_t* words, int ran
   return missing;
 }
 
-// One block per send slot.  Slots are grouped by destination in rank order (the layout of
+constexpr int kRowsPerBlock = 8;  // one warp per row; one system-scope fence per block
+
+// One warp per send slot.  Slots are grouped by destination in rank order (the layout of
 // ep_dispatch_plan), so the destination of slot s follows from the prefix of send_counts.
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kRowsPerBlock * 32)
 ep_push_rows_kernel(const T* __restrict__ source, const int32_t* __restrict__ send_order,
                     const int32_t* __restrict__ local_expert,
                     const uint16_t* __restrict__ routing_weights,
                     const int32_t* __restrict__ send_counts, Exchange x, int assignments,
                     int source_rows, int top_k, int* status) {
-  const int slot = blockIdx.x;
-  const int32_t assignment = send_order[slot];
+  const int lane = threadIdx.x & 31;
+  const int slot = blockIdx.x * kRowsPerBlock + (threadIdx.x >> 5);
+  const int32_t assignment = slot < assignments ? send_order[slot] : -1;
   if (assignment >= 0 && assignment < assignments) {  // else: tail of the send arrays
     int destination = -1, first = 0;
     for (int d = 0; d < x.ranks; ++d) {
@@ -144,14 +147,14 @@ ep_push_rows_kernel(const T* __restrict__ source, const int32_t* __restrict__ se
     const int position = slot - first;
     const int source_row = assignment / top_k;
     if (destination < 0 || position >= x.region_rows || source_row >= source_rows) {
-      if (threadIdx.x == 0) atomicOr(status, NML_SM100_STATUS_INDEX_RANGE);
+      if (lane == 0) atomicOr(status, NML_SM100_STATUS_INDEX_RANGE);
     } else {
       const int64_t row = static_cast<int64_t>(x.rank) * x.region_rows + position;
       const uint4* from = reinterpret_cast<const uint4*>(source) +
                           static_cast<int64_t>(source_row) * x.vectors;
       uint4* to = reinterpret_cast<uint4*>(x.rows[destination]) + row * x.vectors;
-      for (int v = threadIdx.x; v < x.vectors; v += blockDim.x) to[v] = from[v];
-      if (threadIdx.x == 0) {
+      for (int v = lane; v < x.vectors; v += 32) to[v] = from[v];
+      if (lane == 0) {
         int4 meta;
         meta.x = local_expert[slot];
         meta.y = routing_weights[assignment];
@@ -207,25 +210,26 @@ ep_receive_meta_kernel(Exchange x, int32_t* __restrict__ expert_ids, T* __restri
   }
 }
 
-// One block per received row: computed[i] of region r goes to row meta[i].z of rank r's return
+// One warp per received row: computed[i] of region r goes to row meta[i].z of rank r's return
 // buffer.  The last block raises this rank's return flag on every rank.
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kRowsPerBlock * 32)
 ep_return_rows_kernel(const T* __restrict__ computed, Exchange x, int* status) {
-  const int i = blockIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int i = blockIdx.x * kRowsPerBlock + (threadIdx.x >> 5);
   const int sender = i / x.region_rows;
   const int position = i - sender * x.region_rows;
   const int32_t* sync = x.sync[x.rank];
-  if (position < min(sync[kCountWords + sender], x.region_rows)) {
+  if (sender < x.ranks && position < min(sync[kCountWords + sender], x.region_rows)) {
     const int4 m = reinterpret_cast<const int4*>(x.meta[x.rank])[i];
     if (m.z < 0 || m.z >= x.region_rows) {
-      if (threadIdx.x == 0) atomicOr(status, NML_SM100_STATUS_INDEX_RANGE);
+      if (lane == 0) atomicOr(status, NML_SM100_STATUS_INDEX_RANGE);
     } else {
       const uint4* from = reinterpret_cast<const uint4*>(computed) +
                           static_cast<int64_t>(i) * x.vectors;
       uint4* to = reinterpret_cast<uint4*>(x.back[sender]) +
                   static_cast<int64_t>(m.z) * x.vectors;
-      for (int v = threadIdx.x; v < x.vectors; v += blockDim.x) to[v] = from[v];
+      for (int v = lane; v < x.vectors; v += 32) to[v] = from[v];
     }
   }
   if (last_block_done(x.local_state + kReturnDoneWord)) {
@@ -269,15 +273,17 @@ int32_t launch_ep_push_rows(const NmlSm100EpPushRows& q, const DeviceInfo& devic
                             size_t capacity) {
   const Exchange x = make_exchange(q.exchange);
   cudaStream_t stream = static_cast<cudaStream_t>(q.stream);
-  const unsigned grid = static_cast<unsigned>(q.assignments);
+  const unsigned grid =
+      static_cast<unsigned>((q.assignments + kRowsPerBlock - 1) / kRowsPerBlock);
   const uint16_t* weights = static_cast<const uint16_t*>(q.routing_weights);
+  constexpr int kBlock = kRowsPerBlock * 32;
   if (q.dtype == NML_SM100_F16) {
-    ep_push_rows_kernel<__half><<<grid, 128, 0, stream>>>(
+    ep_push_rows_kernel<__half><<<grid, kBlock, 0, stream>>>(
         static_cast<const __half*>(q.source), q.send_order, q.local_expert, weights, q.send_counts,
         x, static_cast<int>(q.assignments), static_cast<int>(q.source_rows),
         static_cast<int>(q.experts_per_token), device.status_word);
   } else {
-    ep_push_rows_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
+    ep_push_rows_kernel<__nv_bfloat16><<<grid, kBlock, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(q.source), q.send_order, q.local_expert, weights,
         q.send_counts, x, static_cast<int>(q.assignments), static_cast<int>(q.source_rows),
         static_cast<int>(q.experts_per_token), device.status_word);
@@ -308,12 +314,14 @@ int32_t launch_ep_return_rows(const NmlSm100EpReturnRows& q, const DeviceInfo& d
                               char* message, size_t capacity) {
   const Exchange x = make_exchange(q.exchange);
   cudaStream_t stream = static_cast<cudaStream_t>(q.stream);
-  const unsigned grid = static_cast<unsigned>(q.exchange.ranks * q.exchange.region_rows);
+  const unsigned grid = static_cast<unsigned>(
+      (q.exchange.ranks * q.exchange.region_rows + kRowsPerBlock - 1) / kRowsPerBlock);
+  constexpr int kBlock = kRowsPerBlock * 32;
   if (q.dtype == NML_SM100_F16) {
-    ep_return_rows_kernel<__half><<<grid, 128, 0, stream>>>(
+    ep_return_rows_kernel<__half><<<grid, kBlock, 0, stream>>>(
         static_cast<const __half*>(q.computed), x, device.status_word);
   } else {
-    ep_return_rows_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
+    ep_return_rows_kernel<__nv_bfloat16><<<grid, kBlock, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(q.computed), x, device.status_word);
   }
   return launch_result(message, capacity);

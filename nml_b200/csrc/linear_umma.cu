@@ -235,8 +235,12 @@ int32_t launch_for_rows(const LinearArgs& args, const DeviceInfo& device, char* 
       // 256-row tiles: scales by bulk copy when the two buffers fit beside three activation
       // stages (K <= ~2900) and the copy is legal; else per-stage 4-byte copies
       if (bulk_scales_legal) {
-        const int32_t rc = launch_config<256, 1, 4, 3, 4, 3, 1, 1, false, AFMT, T, true>(
+        int32_t rc = launch_config<256, 1, 4, 3, 4, 3, 1, 1, false, AFMT, T, true>(
             args, device, message, capacity);
+        if (rc != kDoesNotFit) return rc;
+        // larger K (4096): the two scale buffers leave room for two activation stages
+        rc = launch_config<256, 1, 4, 2, 4, 3, 1, 1, false, AFMT, T, true>(args, device, message,
+                                                                           capacity);
         if (rc != kDoesNotFit) return rc;
       }
       return launch_config<256, 1, 6, 4, 4, 3, 1, 1, false, AFMT, T>(args, device, message,

@@ -20,7 +20,8 @@ the KV read divides too), experts are sharded with the peer-push schedule of
 ``expert_parallel.ExpertParallelMoE``, the vocabulary projection is column-sharded with a
 per-shard arg-max merged across ranks; the attention-side weights are replicas.
 
-Weights are random (N(0, 0.02) quantized with the recipe); there is no checkpoint reader here.
+Weights are random (N(0, 0.02) quantized with the recipe); ``checkpoint.NvFp4Checkpoint`` reads
+stored records, the harness does not need them.
 """
 from __future__ import annotations
 

@@ -125,10 +125,11 @@ class CudaBackend:
         _abi.call("nml_nvfp4_sm100_ep_wait_returns", request)
 
     def routed_experts(self, hidden, expert_ids, routing_weights, layer, expert_offset=0,
-                       live_routes=0):
+                       live_routes=0, leave_masked_rows=False):
         return ops.routed_experts(hidden, expert_ids, routing_weights, layer.gate_up,
                                   layer.gate_up_bias, layer.down, layer.down_bias,
-                                  expert_offset=expert_offset, live_routes=live_routes)
+                                  expert_offset=expert_offset, live_routes=live_routes,
+                                  leave_masked_rows=leave_masked_rows)
 
     def linear(self, hidden, weight, bias=None):
         return ops.linear(hidden, weight, bias)
@@ -349,7 +350,7 @@ class ExpertParallelMoE:
         recv_ids, recv_weights, _ = backend.receive_meta(exchange, hidden.dtype, self.wait_limit)
         # of the world * region_rows rows an owner's buffer holds, about `assignments` are live
         computed = backend.routed_experts(exchange.rows, recv_ids, recv_weights, self.layer,
-                                          live_routes=assignments)
+                                          live_routes=assignments, leave_masked_rows=True)
         backend.return_rows(computed, exchange)
         backend.wait_returns(exchange, self.wait_limit)
         return backend.combine_rows(exchange.back, slot_of, tokens, k)

@@ -361,13 +361,15 @@ def routed_experts(hidden: torch.Tensor, expert_ids: torch.Tensor,
                    routing_weights: torch.Tensor, gate_up: NvFp4Parameter,
                    gate_up_bias: torch.Tensor, down: NvFp4Parameter, down_bias: torch.Tensor,
                    expert_offset: int = 0, out: torch.Tensor | None = None,
-                   workspace: torch.Tensor | None = None, live_routes: int = 0) -> torch.Tensor:
+                   workspace: torch.Tensor | None = None, live_routes: int = 0,
+                   leave_masked_rows: bool = False) -> torch.Tensor:
     """The routed layer from given routes, one C-ABI call (plan, gate/up + SwiGLU, down,
     k-way sum); the unit of the reference's CPU target ``nml.nvfp4.routed_swiglu``
     (crates/nml-kernel-nvfp4/src/ffi.rs:228-428).  ``workspace`` (u8, 256-byte aligned, at
     least ``nml_nvfp4_sm100_routed_swiglu_workspace_bytes``) replaces the cached scratch
     buffer, e.g. to inspect the intermediates afterwards.  ``live_routes`` (optional) tells
-    the kernel selection how many routes are expected not to be masked."""
+    the kernel selection how many routes are expected not to be masked.  ``leave_masked_rows``
+    (one route per token only) skips the k-way sum pass: rows of masked tokens stay untouched."""
     if hidden.dim() != 2 or expert_ids.dim() != 2 or \
             tuple(routing_weights.shape) != tuple(expert_ids.shape) or \
             expert_ids.shape[0] != hidden.shape[0]:
@@ -404,7 +406,8 @@ def routed_experts(hidden: torch.Tensor, expert_ids: torch.Tensor,
         workspace=_ptr(workspace), workspace_bytes=workspace.numel(), stream=_stream(hidden),
         tokens=tokens, hidden_size=hidden_size, intermediate_size=intermediate, experts=experts,
         experts_per_token=top_k, expert_offset=expert_offset, dtype=_code(hidden.dtype),
-        live_routes_hint=live_routes)
+        live_routes_hint=live_routes,
+        flags=_abi.ROUTED_LEAVE_MASKED_ROWS if leave_masked_rows and top_k == 1 else 0)
     _abi.call("nml_nvfp4_sm100_routed_swiglu", request)
     return out
 

@@ -67,7 +67,7 @@ class OracleBackend:
         return bits_to_tensor(oracle.from_f32(out, self.dtype))
 
     def routed_experts(self, hidden, expert_ids, routing_weights, layer, expert_offset=0,
-                       live_routes=0):
+                       live_routes=0, leave_masked_rows=False):
         tokens, top_k = expert_ids.shape
         ids = expert_ids.numpy().astype(np.int32) - expert_offset
         ids = np.where((expert_ids.numpy() >= 0) & (ids >= 0) & (ids < layer.experts_local), ids,

@@ -108,7 +108,8 @@ def test_push_schedule_with_several_ranks_emulated_on_one_device(ranks, experts,
             recv_ids, recv_weights, received = backend.receive_meta(exchanges[r], torch.bfloat16)
             assert int(received.item()) == int((recv_ids >= 0).sum().item())
             computed.append(backend.routed_experts(exchanges[r].rows, recv_ids, recv_weights,
-                                                   layers[r], live_routes=per_rank * k))
+                                                   layers[r], live_routes=per_rank * k,
+                                                   leave_masked_rows=True))
         for r in range(ranks):
             backend.return_rows(computed[r], exchanges[r])
         for r in range(ranks):
