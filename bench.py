@@ -48,6 +48,15 @@ UNIT = "TFLOP/s"
 WORKLOAD = "config1_nvfp4_gemm_shape_sweep(5 shapes x M in {1,16,64,512,4096,16384})"
 
 
+PROFILE_CASES = {
+    "moe_decode64": "routed layer, 64 tokens, 32 experts, top-4 (weight-streaming expert kernels)",
+    "moe_t4096": "routed layer, 4096 tokens, 32 experts, top-4 (tcgen05 grouped kernels)",
+    "embedding": "packed embedding gather, 8192 rows of the 201088 x 2880 table",
+    "attention": "paged-attention decode, batch 64, 4096 prior tokens, 64 query / 8 kv heads",
+    "topk": "row-wise top-8 of 64 x 201088 f32 logits",
+}
+
+
 def parse_args():
     parser = argparse.ArgumentParser(description=__doc__,
                                      formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -70,6 +79,9 @@ def parse_args():
                         help="comma-separated subset of M values (profiling captures)")
     parser.add_argument("--shapes", type=str, default="",
                         help="comma-separated subset of shape names (profiling captures)")
+    parser.add_argument("--case", choices=sorted(PROFILE_CASES), default="",
+                        help="run only this single-GPU case `--steps` times and print its device "
+                             "time (profiling captures of the kernels outside the sweep)")
     return parser.parse_args()
 
 
@@ -853,8 +865,81 @@ def decode_step_figures(args, rank, world, device, barrier, peaks) -> dict:
             "stand_ins": "RMSNorm, RoPE, cache write and the bf16 router matmul are torch ops; attention, top-1 and every NVFP4 operator are this library's kernels"}
 
 
+def run_case(args) -> None:
+    """One small single-GPU case of a kernel the sweep does not launch, `--steps` times."""
+    import torch
+    from nml_b200 import _abi, ops, quantize
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the NVFP4 path has no CPU fallback")
+    device = torch.device("cuda", 0)
+    _abi.load()
+    generator = torch.Generator(device=device).manual_seed(5)
+
+    def normal(shape, std=0.02, dtype=torch.bfloat16):
+        return (torch.randn(shape, device=device, generator=generator) * std).to(dtype)
+
+    hidden, experts, top_k = 2880, 32, 4
+    if args.case in ("moe_decode64", "moe_t4096"):
+        tokens = 64 if args.case == "moe_decode64" else 4096
+        gate_up = quantize.quantize_parameter("gate_up", normal((experts, 2 * hidden, hidden)))
+        down = quantize.quantize_parameter("down", normal((experts, hidden, hidden)))
+        gate_bias, down_bias = normal((experts, 2 * hidden)), normal((experts, hidden))
+        x, logits = normal((tokens, hidden), 1.0), normal((tokens, experts), 1.0, torch.float32)
+
+        def fn():
+            ops.routed_clamped_swiglu(x, logits, gate_up, gate_bias, down, down_bias, top_k)
+        nbytes = experts * 3 * hidden * hidden * 0.5625
+    elif args.case == "embedding":
+        rows = 201088
+        table = quantize.quantize_parameter("table", normal((rows, hidden)))
+        ids = torch.randint(0, rows, (8192,), device=device, generator=generator,
+                            dtype=torch.int32)
+        out = torch.empty((8192, hidden), dtype=torch.bfloat16, device=device)
+
+        def fn():
+            ops.token_embedding(table, ids, out=out)
+        nbytes = 8192 * (hidden // 2 + hidden // 16 + 2 * hidden + 4)
+    elif args.case == "attention":
+        batch, prior, heads, kv_heads, dim, page = 64, 4096, 64, 8, 64, 16
+        pages_per_sequence = (prior + 1 + page - 1) // page
+        keys = normal((batch * pages_per_sequence, page, kv_heads, dim), 1.0)
+        values = normal((batch * pages_per_sequence, page, kv_heads, dim), 1.0)
+        table = torch.randperm(batch * pages_per_sequence, device=device, generator=generator) \
+            .view(batch, pages_per_sequence).to(torch.int32).contiguous()
+        lengths = torch.full((batch,), prior + 1, dtype=torch.int32, device=device)
+        query, sinks = normal((batch, heads, dim), 1.0), normal((heads,), 1.0, torch.float32)
+
+        def fn():
+            ops.paged_attention_decode(query, keys, values, table, lengths, sinks)
+        nbytes = 2 * batch * (prior + 1) * kv_heads * dim * 2
+    else:
+        logits = normal((64, 201088), 1.0, torch.float32)
+
+        def fn():
+            ops.topk_rows(logits, 8)
+        nbytes = logits.numel() * 4
+    for _ in range(max(args.warmup, 3)):
+        fn()
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(args.steps):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    if _abi.device_status(0x1) != 0:
+        raise RuntimeError("a kernel reported a device-side error")
+    us = begin.elapsed_time(end) * 1e3 / args.steps
+    print(json.dumps({"case": args.case, "what": PROFILE_CASES[args.case], "steps": args.steps,
+                      "us_per_call": us, "algorithmic_bytes": nbytes,
+                      "gbs": nbytes / us / 1e3, "timing": "eager launches, L2-warm where it fits"}))
+
+
 def main() -> int:
     args = parse_args()
+    if args.case:
+        run_case(args)
+        return 0
     if args.impl == "reference":
         run_reference_arm(args)
     else:

@@ -25,11 +25,11 @@ bool reserve(Kernel kernel, int device, std::atomic<int> (&configured)[64]) {
   return true;
 }
 
-template <int NT, int UT, typename T, int MODE, bool FULL>
+template <int NT, int UT, int RT, typename T, int MODE, bool FULL>
 int32_t launch_variant(const Params& p, int smem_bytes, int64_t units_bound,
                        const DeviceInfo& device, cudaStream_t stream, char* message,
                        size_t capacity) {
-  auto kernel = stream_kernel<NT, UT, T, MODE, FULL>;
+  auto kernel = stream_kernel<NT, UT, RT, T, MODE, FULL>;
   static std::atomic<int> configured[64];
   if (!reserve(kernel, device.device, configured)) {
     return fail(NML_SM100_LAUNCH_FAILURE,
@@ -44,23 +44,34 @@ int32_t launch_variant(const Params& p, int smem_bytes, int64_t units_bound,
 }
 
 template <typename T, int MODE>
-int32_t launch_for_shape(const Params& p, int nt, int smem_bytes, int64_t units_bound,
+int32_t launch_for_shape(const Params& p, int nt, int rt, int smem_bytes, int64_t units_bound,
                          const DeviceInfo& device, cudaStream_t stream, char* message,
                          size_t capacity) {
-#define NML_STREAM_VARIANT(NT, UT, FULL)                                                      \
-  launch_variant<NT, UT, T, MODE, FULL>(p, smem_bytes, units_bound, device, stream, message, \
-                                        capacity)
+#define NML_STREAM_VARIANT(NT, UT, RT, FULL)                                                  \
+  launch_variant<NT, UT, RT, T, MODE, FULL>(p, smem_bytes, units_bound, device, stream,       \
+                                            message, capacity)
+#define NML_STREAM_TILE(UT, FULL)                                                             \
+  (nt == 2 ? NML_STREAM_VARIANT(2, UT, 1, FULL)                                               \
+           : (rt == 2 ? NML_STREAM_VARIANT(1, UT, 2, FULL) : NML_STREAM_VARIANT(1, UT, 1, FULL)))
   // Three variants: K units that split evenly into 3 per warp (K = 2880), evenly into 4 per
-  // warp (K = 4096), and the guarded form for every other width.
+  // warp (K = 4096), and the guarded form for every other width; each for one activation-row
+  // tile (16- or 32-row weight tiles) and for two.
   const bool even = p.compute_warps * p.units_per_warp == p.k_units;
-  if (even && p.units_per_warp == 3) {
-    return nt == 1 ? NML_STREAM_VARIANT(1, 3, true) : NML_STREAM_VARIANT(2, 3, true);
-  }
-  if (even && p.units_per_warp == 4) {
-    return nt == 1 ? NML_STREAM_VARIANT(1, 4, true) : NML_STREAM_VARIANT(2, 4, true);
-  }
-  return nt == 1 ? NML_STREAM_VARIANT(1, 4, false) : NML_STREAM_VARIANT(2, 4, false);
+  if (even && p.units_per_warp == 3) return NML_STREAM_TILE(3, true);
+  if (even && p.units_per_warp == 4) return NML_STREAM_TILE(4, true);
+  return NML_STREAM_TILE(4, false);
+#undef NML_STREAM_TILE
 #undef NML_STREAM_VARIANT
+}
+
+// 32-row tiles once every CTA walks at least this many 16-row tiles: the launch is then long
+// enough for the per-tile bookkeeping to matter and coarse enough tiles still balance.
+constexpr int64_t kLargeTileWalk = 6;
+
+// With two activation-row tiles the registers do not hold a second fragment of accumulators
+// and decodes without spilling, and the larger tile was measured slower there.
+int tile_fragments(int nt, int64_t fragments, const DeviceInfo& device) {
+  return nt == 1 && fragments >= kLargeTileWalk * device.sm_count ? 2 : 1;
 }
 
 bool aligned16(const void* pointer) { return reinterpret_cast<uintptr_t>(pointer) % 16 == 0; }
@@ -91,8 +102,14 @@ int32_t launch_linear_stream(const LinearArgs& args, const DeviceInfo& device, c
                              size_t capacity) {
   Params p = {};
   const int nt = args.rows <= 8 ? 1 : 2;
+  int64_t fragments = (args.outputs + kFragmentRows - 1) / kFragmentRows;
+  for (int i = 0; i < args.extra_projections; ++i) {
+    fragments += (args.extra[i].outputs + kFragmentRows - 1) / kFragmentRows;
+  }
+  const int rt = tile_fragments(nt, fragments * ((args.rows + 15) / 16), device);
+  const int kTileRows = kFragmentRows * rt;
   int smem_bytes = 0;
-  if (!plan_layout(args.inputs, nt, &p, &smem_bytes)) {
+  if (!plan_layout(args.inputs, nt, rt, &p, &smem_bytes)) {
     return fail(NML_SM100_INVALID_ARGUMENT,
                 "the weight-streaming linear does not support this input width", message,
                 capacity);
@@ -115,17 +132,17 @@ int32_t launch_linear_stream(const LinearArgs& args, const DeviceInfo& device, c
   const int64_t units = static_cast<int64_t>(p.groups) * tiles;
   note_linear_kernel("stream", 16);
   if (args.dtype == NML_SM100_F16) {
-    return launch_for_shape<__half, kDense>(p, nt, smem_bytes, units, device, args.stream,
+    return launch_for_shape<__half, kDense>(p, nt, rt, smem_bytes, units, device, args.stream,
                                             message, capacity);
   }
-  return launch_for_shape<__nv_bfloat16, kDense>(p, nt, smem_bytes, units, device, args.stream,
-                                                 message, capacity);
+  return launch_for_shape<__nv_bfloat16, kDense>(p, nt, rt, smem_bytes, units, device,
+                                                 args.stream, message, capacity);
 }
 
 bool experts_stream_supported(const ExpertArgs& args) {
   const int64_t rows_per_expert = args.gate_up ? 2ll * args.outputs : args.outputs;
   return !args.slot_input && args.inputs % kUnitK == 0 && args.inputs <= 4 * 16 * kUnitK &&
-         rows_per_expert % kTileRows == 0 &&
+         rows_per_expert % kFragmentRows == 0 &&
          args.experts * rows_per_expert <= std::numeric_limits<int32_t>::max() &&
          aligned16(args.payload) && aligned16(args.block_scales) && aligned16(args.input) &&
          // decode-size batches: at most one full schedule block per expert on average
@@ -138,8 +155,15 @@ int32_t launch_experts_stream(const ExpertArgs& args, const DeviceInfo& device, 
   Params p = {};
   // sparse schedule form (one route per block, nml-ir/src/lib.rs:5696-5721): slot 0 only
   const int nt = args.assignments <= args.experts ? 1 : 2;  // (the plan's form follows all routes)
+  const int rows_per_expert = args.gate_up ? 2 * args.outputs : args.outputs;
+  // blocks with work: at most one per live route and at most ceil(routes / 16) + experts
+  const int64_t live = args.live_routes > 0 ? args.live_routes : args.assignments;
+  int64_t busy_blocks = nt == 1 ? live : live / 16 + args.experts;
+  if (busy_blocks > args.schedule_blocks) busy_blocks = args.schedule_blocks;
+  const int rt = tile_fragments(nt, busy_blocks * (rows_per_expert / kFragmentRows), device);
+  const int kTileRows = kFragmentRows * rt;
   int smem_bytes = 0;
-  if (!plan_layout(args.inputs, nt, &p, &smem_bytes)) {
+  if (!plan_layout(args.inputs, nt, rt, &p, &smem_bytes)) {
     return fail(NML_SM100_INVALID_ARGUMENT,
                 "the weight-streaming expert kernel does not support this input width", message,
                 capacity);
@@ -159,16 +183,16 @@ int32_t launch_experts_stream(const ExpertArgs& args, const DeviceInfo& device, 
   p.schedule_blocks = args.schedule_blocks;
   p.experts = args.experts;
   p.top_k = args.experts_per_token;
-  p.rows_per_expert = args.gate_up ? 2 * args.outputs : args.outputs;
+  p.rows_per_expert = rows_per_expert;
   p.N = args.outputs;
   p.groups = args.schedule_blocks;
-  p.tiles_per_group = p.rows_per_expert / kTileRows;
+  p.tiles_per_group = (p.rows_per_expert + kTileRows - 1) / kTileRows;
   p.status = device.status_word;
   const int64_t units = static_cast<int64_t>(p.groups) * p.tiles_per_group;
 #define NML_STREAM_EXPERTS(T)                                                                  \
-  (args.gate_up ? launch_for_shape<T, kGateUp>(p, nt, smem_bytes, units, device, args.stream,  \
-                                               message, capacity)                              \
-                : launch_for_shape<T, kDown>(p, nt, smem_bytes, units, device, args.stream,    \
+  (args.gate_up ? launch_for_shape<T, kGateUp>(p, nt, rt, smem_bytes, units, device,          \
+                                               args.stream, message, capacity)                 \
+                : launch_for_shape<T, kDown>(p, nt, rt, smem_bytes, units, device, args.stream, \
                                              message, capacity))
   if (args.dtype == NML_SM100_F16) return NML_STREAM_EXPERTS(__half);
   return NML_STREAM_EXPERTS(__nv_bfloat16);

@@ -9,7 +9,9 @@
 // crates/nml-kernel-triton/src/nvfp4.rs:523-731 and :1421-1970); this is their sm_100a
 // counterpart, for 1..16 activation rows (or schedule slots) per group.
 //
-// Work unit: a tile of 16 weight rows over the whole K range.  The rows of a tile are
+// Work unit: a tile of 16 or 32 weight rows (RT = 1 or 2 fragments of 16; the larger tile
+// halves the per-tile bookkeeping and is used when every CTA walks many tiles) over the whole
+// K range.  The rows of a tile are
 // contiguous in the payload tensor, so the producer warp brings a tile (payload and block
 // scales) into a shared-memory ring with untiled bulk copies (cp.async.bulk); no tensor map
 // is involved.  The K range is cut into units of 64 and dealt to the W <= 16 compute
@@ -49,12 +51,12 @@ namespace stream {
 
 enum Mode : int { kDense = 0, kGateUp = 1, kDown = 2 };
 
-constexpr int kTileRows = 16;
+constexpr int kFragmentRows = 16;     // weight rows of one mma.sync A fragment
 constexpr int kUnitK = 64;            // K values of one unit: a quad of lanes reads 32 bytes per row
 constexpr int kMaxComputeWarps = 16;
 constexpr int kMaxThreads = (kMaxComputeWarps + 3) * 32;  // + reducer warp(s) + producer warp
 constexpr int kMaxStages = 4;         // weight tiles in flight per CTA (more were measured to add nothing)
-constexpr int kSlots = 4;             // partial-sum slots between compute warps and reducer
+constexpr int kMaxSlots = 4;          // partial-sum slots between compute warps and reducer
 constexpr int kSmemBudget = 227 * 1024;
 
 // One dense weight (fused Q/K/V: up to three that share the activations).
@@ -65,7 +67,7 @@ struct Segment {
   const void* bias;
   void* output;
   int outputs;     // rows of this weight = output columns
-  int tile_begin;  // first 16-row tile of the segment in the launch's tile list
+  int tile_begin;  // first tile of the segment in the launch's tile list
 };
 
 struct Params {
@@ -92,7 +94,7 @@ struct Params {
   // common
   int K;
   int groups;            // dense: ceil(M / 16); grouped: schedule_blocks (upper bound)
-  int tiles_per_group;   // 16-row weight tiles every group walks
+  int tiles_per_group;   // weight tiles every group walks
   int compute_warps;     // W
   int units_per_warp;    // consecutive 64-wide K units per compute warp (<= UT)
   int k_units;           // K / 64
@@ -103,6 +105,8 @@ struct Params {
   int scale_offset;      // offset of the scale rows inside a stage
   int stage_bytes;
   int stages;
+  int slots;             // partial-sum slots in the ring (<= kMaxSlots)
+  int second_offset;     // NT = 2: the compute warps' copies of the second activation-row tile
   int partial_offset;    // offset of the partial-sum slots
   int barrier_offset;
   int* status;
@@ -171,6 +175,7 @@ enum WaitSite : int {
 };
 
 // NT: activation-row tiles of 8 per group (1: up to 8 rows, 2: up to 16).
+// RT: 16-row fragments of weight rows per tile.
 // UT: K units a compute warp can hold activations for (registers: 8 * NT * UT).
 // FULL: every compute warp holds exactly UT units (no per-unit guards).
 template <int UT>
@@ -178,9 +183,10 @@ constexpr int max_threads() {
   return kMaxThreads;
 }
 
-template <int NT, int UT, typename T, int MODE, bool FULL>
+template <int NT, int UT, int RT, typename T, int MODE, bool FULL>
 __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Params p) {
   constexpr bool kGrouped = MODE != kDense;
+  constexpr int kTileRows = kFragmentRows * RT;
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
   extern __shared__ uint8_t stream_smem_raw[];
   uint8_t* smem = stream_smem_raw + ((128u - (smem_u32(stream_smem_raw) & 127u)) & 127u);
@@ -194,16 +200,17 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
   uint64_t* full_p = bars;                       // [kMaxStages] tile landed
   uint64_t* empty_p = full_p + kMaxStages;       // [kMaxStages] every compute warp has read it
   uint64_t* full_s = empty_p + kMaxStages;       // [kSlots] every compute warp has written
-  uint64_t* empty_s = full_s + kSlots;           // [kSlots] the reducer has read
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_s + kSlots);
-  float4* partials = reinterpret_cast<float4*>(smem + p.partial_offset);  // [slot][W][NT][32]
+  uint64_t* empty_s = full_s + kMaxSlots;        // [kSlots] the reducer has read
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_s + kMaxSlots);
+  // [slot][W][NT][RT][32]
+  float4* partials = reinterpret_cast<float4*>(smem + p.partial_offset);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kMaxStages; ++s) {
       mbar_init(&full_p[s], 1);
       mbar_init(&empty_p[s], W);
     }
-    for (int s = 0; s < kSlots; ++s) {
+    for (int s = 0; s < kMaxSlots; ++s) {
       mbar_init(&full_s[s], W);
       mbar_init(&empty_s[s], NT);
     }
@@ -282,8 +289,14 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
     // ------------------------------------------------------------------- compute
     const int units = max(0, min(p.units_per_warp, p.k_units - warp * p.units_per_warp));
     const int unit0 = warp * p.units_per_warp;  // first K unit of this warp
-    uint32_t b[UT][NT][8];   // activations of the slice: row 8 jn + g, K = 64 unit + 16 c + 2 r
+    // Activations of the slice as mma.sync B fragments: row 8 jn + g, K = 64 unit + 16 c + 2 r.
+    // The first activation-row tile stays in registers; the second one (NT = 2) would push the
+    // kernel into spills, so it lives in this warp's corner of shared memory, one 16-byte
+    // read per lane and half unit.
+    uint32_t b[UT][8];
+    uint4* b_second = reinterpret_cast<uint4*>(smem + p.second_offset) + warp * (UT * 2 * 32) + lane;
     float back[NT][2];       // inverse rescale of activation rows 8 jn + 2 c and 8 jn + 2 c + 1
+    bool second_live = false;  // NT = 2: the group has a row (slot) among its second eight
     // Loads the slice of the group's activation rows and narrows it to f16.
     auto load_activations = [&](int group) {
 #pragma unroll
@@ -300,7 +313,9 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
           const int m = group * 16 + slot;
           if (m < p.M) row = static_cast<const uint8_t*>(p.x) + static_cast<int64_t>(m) * p.K * 2;
         }
+        if (jn == 1) second_live = __any_sync(0xffffffffu, row != nullptr);
         uint32_t magnitude = 0;
+        uint32_t fresh[UT][8];
 #pragma unroll
         for (int u = 0; u < UT; ++u) {
           uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
@@ -310,13 +325,13 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
             lo = __ldg(source);
             hi = __ldg(source + 1);
           }
-          b[u][jn][0] = lo.x; b[u][jn][1] = lo.y; b[u][jn][2] = lo.z; b[u][jn][3] = lo.w;
-          b[u][jn][4] = hi.x; b[u][jn][5] = hi.y; b[u][jn][6] = hi.z; b[u][jn][7] = hi.w;
+          fresh[u][0] = lo.x; fresh[u][1] = lo.y; fresh[u][2] = lo.z; fresh[u][3] = lo.w;
+          fresh[u][4] = hi.x; fresh[u][5] = hi.y; fresh[u][6] = hi.z; fresh[u][7] = hi.w;
           if constexpr (kBf16) {
 #pragma unroll
             for (int r = 0; r < 8; ++r) {
-              magnitude = max(magnitude, b[u][jn][r] & 0x7fffu);
-              magnitude = max(magnitude, (b[u][jn][r] >> 16) & 0x7fffu);
+              magnitude = max(magnitude, fresh[u][r] & 0x7fffu);
+              magnitude = max(magnitude, (fresh[u][r] >> 16) & 0x7fffu);
             }
           }
         }
@@ -334,12 +349,26 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
           for (int u = 0; u < UT; ++u) {
 #pragma unroll
             for (int r = 0; r < 8; ++r) {
-              const uint32_t word = b[u][jn][r];
+              const uint32_t word = fresh[u][r];
               const float low = __uint_as_float(word << 16) * down;
               const float high = __uint_as_float(word & 0xffff0000u) * down;
               const __half2 narrowed = __floats2half2_rn(low, high);
-              b[u][jn][r] = *reinterpret_cast<const uint32_t*>(&narrowed);
+              fresh[u][r] = *reinterpret_cast<const uint32_t*>(&narrowed);
             }
+          }
+        }
+        if (jn == 0) {
+#pragma unroll
+          for (int u = 0; u < UT; ++u) {
+#pragma unroll
+            for (int r = 0; r < 8; ++r) b[u][r] = fresh[u][r];
+          }
+        } else {
+#pragma unroll
+          for (int u = 0; u < UT; ++u) {
+            b_second[(2 * u) * 32] = make_uint4(fresh[u][0], fresh[u][1], fresh[u][2], fresh[u][3]);
+            b_second[(2 * u + 1) * 32] =
+                make_uint4(fresh[u][4], fresh[u][5], fresh[u][6], fresh[u][7]);
           }
         }
         // the accumulator columns of this lane are activation rows 8 jn + 2 c and + 1, whose
@@ -363,46 +392,52 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
       }
       if (!wait(&full_p[ring.index], ring.phase, kSiteCompute)) break;
       const uint8_t* stage = smem + ring.index * p.stage_bytes;
-      const uint8_t* payload_g = stage + payload_offset;
-      const uint8_t* payload_h = payload_g + 8 * p.row_stride;
-      const uint8_t* scale_g = stage + scale_offset;
-      const uint8_t* scale_h = scale_g + 8 * p.scale_stride;
-      // Consecutive mma.sync into one accumulator form a dependent chain whose latency, not
-      // its throughput, would bound a tile: the instructions of a tile rotate over kChains
-      // accumulators per activation-row tile (four chains in flight either way), added in
-      // index order below.
-      constexpr int kChains = NT == 1 ? 4 : 2;
-      float acc[NT][kChains][4];
+      // The mma.sync instructions of one fragment alternate over two accumulators (added in
+      // index order below) whatever the tile shape, so that a weight row's sum is formed in
+      // the same order in every variant: a fused launch equals separate launches bit for bit.
+      constexpr int kChains = 2;
+      float acc[RT][NT][kChains][4];
+      uint32_t seen[RT][2];  // OR of the scale bytes of rows g and g + 8: bit 7 marks an invalid one
 #pragma unroll
-      for (int jn = 0; jn < NT; ++jn) {
+      for (int rt = 0; rt < RT; ++rt) {
+        seen[rt][0] = seen[rt][1] = 0;
 #pragma unroll
-        for (int q = 0; q < kChains; ++q) {
-          acc[jn][q][0] = acc[jn][q][1] = acc[jn][q][2] = acc[jn][q][3] = 0.0f;
+        for (int jn = 0; jn < NT; ++jn) {
+#pragma unroll
+          for (int q = 0; q < kChains; ++q) {
+            acc[rt][jn][q][0] = acc[rt][jn][q][1] = acc[rt][jn][q][2] = acc[rt][jn][q][3] = 0.0f;
+          }
         }
       }
-      uint32_t seen_g = 0, seen_h = 0;  // OR of the scale bytes: the sign bit marks an invalid one
 #pragma unroll
       for (int u = 0; u < UT; ++u) {
         if (FULL || u < units) {
-          const uint2 words_g = *reinterpret_cast<const uint2*>(payload_g + u * 32);
-          const uint2 words_h = *reinterpret_cast<const uint2*>(payload_h + u * 32);
-          const uint32_t byte_g = scale_g[u * 4];
-          const uint32_t byte_h = scale_h[u * 4];
-          seen_g |= byte_g;
-          seen_h |= byte_h;
-          const uint32_t pair_g = scale_pair(byte_g);
-          const uint32_t pair_h = scale_pair(byte_h);
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            uint32_t dg[4], dh[4];
-            decode8(half == 0 ? words_g.x : words_g.y, pair_g, dg);
-            decode8(half == 0 ? words_h.x : words_h.y, pair_h, dh);
+          for (int rt = 0; rt < RT; ++rt) {
+            const uint8_t* payload_g = stage + payload_offset + rt * 16 * p.row_stride + u * 32;
+            const uint8_t* scale_g = stage + scale_offset + rt * 16 * p.scale_stride + u * 4;
+            const uint2 words_g = *reinterpret_cast<const uint2*>(payload_g);
+            const uint2 words_h = *reinterpret_cast<const uint2*>(payload_g + 8 * p.row_stride);
+            const uint32_t byte_g = scale_g[0];
+            const uint32_t byte_h = scale_g[8 * p.scale_stride];
+            seen[rt][0] |= byte_g;
+            seen[rt][1] |= byte_h;
+            const uint32_t pair_g = scale_pair(byte_g);
+            const uint32_t pair_h = scale_pair(byte_h);
 #pragma unroll
-            for (int jn = 0; jn < NT; ++jn) {
-              mma_16816(acc[jn][(2 * half) % kChains], dg[0], dh[0], dg[1], dh[1],
-                        b[u][jn][4 * half], b[u][jn][4 * half + 1]);
-              mma_16816(acc[jn][(2 * half + 1) % kChains], dg[2], dh[2], dg[3], dh[3],
-                        b[u][jn][4 * half + 2], b[u][jn][4 * half + 3]);
+            for (int half = 0; half < 2; ++half) {
+              uint32_t dg[4], dh[4];
+              decode8(half == 0 ? words_g.x : words_g.y, pair_g, dg);
+              decode8(half == 0 ? words_h.x : words_h.y, pair_h, dh);
+              mma_16816(acc[rt][0][0], dg[0], dh[0], dg[1], dh[1], b[u][4 * half],
+                        b[u][4 * half + 1]);
+              mma_16816(acc[rt][0][1], dg[2], dh[2], dg[3], dh[3], b[u][4 * half + 2],
+                        b[u][4 * half + 3]);
+              if (NT == 2 && (!kGrouped || second_live)) {  // skipped for blocks of <= 8 routes
+                const uint4 second = b_second[(2 * u + half) * 32];
+                mma_16816(acc[rt][1][0], dg[0], dh[0], dg[1], dh[1], second.x, second.y);
+                mma_16816(acc[rt][1][1], dg[2], dh[2], dg[3], dh[3], second.z, second.w);
+              }
             }
           }
         }
@@ -413,40 +448,53 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
       ring.advance(p.stages);
       // invalid scale bytes seen by any lane of the quad poison the two rows (rare: one vote
       // per tile keeps the common path free of shuffles)
-      float poison_g = 0.0f, poison_h = 0.0f;
-      if (__any_sync(0xffffffffu, ((seen_g | seen_h) & 0x80u) != 0u)) {
-        seen_g |= __shfl_xor_sync(0xffffffffu, seen_g, 1);
-        seen_g |= __shfl_xor_sync(0xffffffffu, seen_g, 2);
-        seen_h |= __shfl_xor_sync(0xffffffffu, seen_h, 1);
-        seen_h |= __shfl_xor_sync(0xffffffffu, seen_h, 2);
-        if (seen_g & 0x80u) poison_g = __uint_as_float(0x7fc00000u);
-        if (seen_h & 0x80u) poison_h = __uint_as_float(0x7fc00000u);
+      float poison[RT][2];
+      uint32_t any_seen = 0;
+#pragma unroll
+      for (int rt = 0; rt < RT; ++rt) {
+        poison[rt][0] = poison[rt][1] = 0.0f;
+        any_seen |= seen[rt][0] | seen[rt][1];
+      }
+      if (__any_sync(0xffffffffu, (any_seen & 0x80u) != 0u)) {
+#pragma unroll
+        for (int rt = 0; rt < RT; ++rt) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t bits = seen[rt][h];
+            bits |= __shfl_xor_sync(0xffffffffu, bits, 1);
+            bits |= __shfl_xor_sync(0xffffffffu, bits, 2);
+            if (bits & 0x80u) poison[rt][h] = __uint_as_float(0x7fc00000u);
+          }
+        }
       }
       if (!wait(&empty_s[slots.index], slots.phase ^ 1u, kSiteSlot)) break;
-      float4* mine = partials + ((slots.index * W + warp) * NT) * 32 + lane;
+      float4* mine = partials + ((slots.index * W + warp) * NT * RT) * 32 + lane;
 #pragma unroll
       for (int jn = 0; jn < NT; ++jn) {
-        float total[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          total[i] = acc[jn][0][i];
+        for (int rt = 0; rt < RT; ++rt) {
+          float total[4];
 #pragma unroll
-          for (int q = 1; q < kChains; ++q) total[i] = __fadd_rn(total[i], acc[jn][q][i]);
+          for (int i = 0; i < 4; ++i) {
+            total[i] = acc[rt][jn][0][i];
+#pragma unroll
+            for (int q = 1; q < kChains; ++q) total[i] = __fadd_rn(total[i], acc[rt][jn][q][i]);
+          }
+          mine[(jn * RT + rt) * 32] = make_float4(total[0] * back[jn][0] + poison[rt][0],
+                                                  total[1] * back[jn][1] + poison[rt][0],
+                                                  total[2] * back[jn][0] + poison[rt][1],
+                                                  total[3] * back[jn][1] + poison[rt][1]);
         }
-        mine[jn * 32] = make_float4(total[0] * back[jn][0] + poison_g,
-                                    total[1] * back[jn][1] + poison_g,
-                                    total[2] * back[jn][0] + poison_h,
-                                    total[3] * back[jn][1] + poison_h);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&full_s[slots.index]);
-      slots.advance(kSlots);
+      slots.advance(p.slots);
     }
   } else if (warp == W + NT) {
     // ------------------------------------------------------------------ producer
     // Lane 0 owns the ring (waits, transaction counts); when rows are padded in shared memory
-    // and have to be copied one by one, payload row r is issued by lane r and scale row r by
-    // lane 16 + r.
+    // and have to be copied one by one, lane r issues payload row r and lane 16 + r scale
+    // row r (lane r both, when the tile has 32 rows).
     Ring ring;
     int issued = 0;
     auto produce = [&](const Walk& w) -> bool {
@@ -490,13 +538,14 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
         bulk_load(stage + lane * p.row_stride, from + static_cast<int64_t>(lane) * p.row_bytes,
                   static_cast<uint32_t>(p.row_bytes), &full_p[ring.index]);
       }
+      const int scale_row = RT == 1 ? lane - 16 : lane;
       if (p.scale_stride == p.scale_width) {
         if (lane == 16) {
           bulk_load(stage + p.scale_offset, scale_from,
                     static_cast<uint32_t>(valid * p.scale_width), &full_p[ring.index]);
         }
-      } else if (lane >= 16 && lane - 16 < valid) {
-        const int r = lane - 16;
+      } else if (scale_row >= 0 && scale_row < valid) {
+        const int r = scale_row;
         bulk_load(stage + p.scale_offset + r * p.scale_stride,
                   scale_from + static_cast<int64_t>(r) * p.scale_width,
                   static_cast<uint32_t>(p.scale_width), &full_p[ring.index]);
@@ -545,19 +594,27 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
         }
       }
       if (!wait(&full_s[slots.index], slots.phase, kSiteReducer)) break;
-      const float4* slot = partials + ((slots.index * W) * NT + jn) * 32 + lane;
-      float4 sum = slot[0];
+      const float4* slot = partials + ((slots.index * W) * NT + jn) * RT * 32 + lane;
+      float4 sums[RT];
+#pragma unroll
+      for (int rt = 0; rt < RT; ++rt) sums[rt] = slot[rt * 32];
 #pragma unroll 4
       for (int cw = 1; cw < W; ++cw) {  // ascending K
-        const float4 v = slot[cw * NT * 32];
-        sum.x = __fadd_rn(sum.x, v.x);
-        sum.y = __fadd_rn(sum.y, v.y);
-        sum.z = __fadd_rn(sum.z, v.z);
-        sum.w = __fadd_rn(sum.w, v.w);
+#pragma unroll
+        for (int rt = 0; rt < RT; ++rt) {
+          const float4 v = slot[(cw * NT * RT + rt) * 32];
+          sums[rt].x = __fadd_rn(sums[rt].x, v.x);
+          sums[rt].y = __fadd_rn(sums[rt].y, v.y);
+          sums[rt].z = __fadd_rn(sums[rt].z, v.z);
+          sums[rt].w = __fadd_rn(sums[rt].w, v.w);
+        }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_s[slots.index]);
-      slots.advance(kSlots);
+      slots.advance(p.slots);
+#pragma unroll
+      for (int rt = 0; rt < RT; ++rt) {
+      const float4 sum = sums[rt];
 
       if constexpr (MODE == kDense) {
         int s = 0;
@@ -567,7 +624,7 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
         const float scale = __ldg(segment.global_scale);
         T* out = static_cast<T*>(segment.output);
         const T* bias = static_cast<const T*>(segment.bias);
-        const int n0 = (w.tile - segment.tile_begin) * kTileRows + g;
+        const int n0 = (w.tile - segment.tile_begin) * kTileRows + 16 * rt + g;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {  // weight rows g and g + 8
           const int n = n0 + 8 * half;
@@ -591,7 +648,7 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
         T* out = static_cast<T*>(p.output);
         const T* bias = static_cast<const T*>(p.bias) +
                         static_cast<int64_t>(w.expert) * p.rows_per_expert;
-        const int n0 = w.tile * kTileRows + g;
+        const int n0 = w.tile * kTileRows + 16 * rt + g;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           const int n = n0 + 8 * half;  // weight row inside the expert
@@ -625,6 +682,7 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
           }
         }
       }
+      }  // rt
     }
   }
   __syncthreads();
@@ -633,7 +691,8 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
 // ---- host side ------------------------------------------------------------------------------
 
 // Shared-memory layout and warp split of a launch; false when the shape does not fit.
-inline bool plan_layout(int K, int nt, Params* p, int* smem_bytes) {
+inline bool plan_layout(int K, int nt, int rt, Params* p, int* smem_bytes) {
+  const int tile_rows = kFragmentRows * rt;
   if (K <= 0 || K % kUnitK != 0) return false;
   p->K = K;
   p->k_units = K / kUnitK;
@@ -659,16 +718,22 @@ inline bool plan_layout(int K, int nt, Params* p, int* smem_bytes) {
   const int r = p->row_bytes % 128;
   p->row_stride = p->row_bytes + ((r == 32 || r == 96) ? 0 : (32 + 128 - r) % 128);
   p->scale_stride = p->scale_width + (p->scale_width % 32 == 0 ? 16 : 0);
-  p->scale_offset = (kTileRows * p->row_stride + 127) / 128 * 128;
-  p->stage_bytes = p->scale_offset + (kTileRows * p->scale_stride + 127) / 128 * 128;
-  const int partial_bytes = kSlots * p->compute_warps * nt * 32 * 16;
-  const int fixed = partial_bytes + 256 /* barriers */ + 128 /* alignment slack */;
+  p->scale_offset = (tile_rows * p->row_stride + 127) / 128 * 128;
+  p->stage_bytes = p->scale_offset + (tile_rows * p->scale_stride + 127) / 128 * 128;
+  p->slots = rt == 1 ? kMaxSlots : 2;
+  const int partial_bytes = p->slots * p->compute_warps * nt * rt * 32 * 16;
+  // the kernel variant that serves this split holds 3 units per warp when that divides K
+  // evenly, else 4 (see launch_for_shape)
+  const int held_units = (best_w * best_u == p->k_units && best_u == 3) ? 3 : 4;
+  const int second_bytes = nt == 2 ? p->compute_warps * held_units * 2 * 32 * 16 : 0;
+  const int fixed = partial_bytes + second_bytes + 256 /* barriers */ + 128 /* alignment slack */;
   int stages = kMaxStages;
   while (stages > 1 && stages * p->stage_bytes + fixed > kSmemBudget) --stages;
   if (stages < 2) return false;
   p->stages = stages;
   p->partial_offset = stages * p->stage_bytes;
-  p->barrier_offset = p->partial_offset + partial_bytes;
+  p->second_offset = p->partial_offset + partial_bytes;
+  p->barrier_offset = p->second_offset + second_bytes;
   *smem_bytes = stages * p->stage_bytes + fixed;
   return true;
 }

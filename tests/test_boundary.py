@@ -23,6 +23,20 @@ def test_library_exports_every_declared_symbol():
     assert _abi.load().nml_nvfp4_sm100_abi_version() == 2
 
 
+def test_reference_binding_patch_names_exported_entry_points():
+    # the Rust glue a maintainer applies binds four of the header's entry points by name and
+    # registers one custom-call target per entry point
+    patch = (ROOT / "include" / "reference_sm100_binding.patch").read_text()
+    added = "\n".join(line[1:] for line in patch.splitlines()
+                      if line.startswith("+") and not line.startswith("+++"))
+    bound = set(re.findall(r"fn (nml_nvfp4_sm100_[a-z0-9_]+)\(", added))
+    assert bound == {"nml_nvfp4_sm100_linear", "nml_nvfp4_sm100_embedding",
+                     "nml_nvfp4_sm100_expert_gate_up", "nml_nvfp4_sm100_expert_down"}
+    assert bound <= set(_abi.REQUEST_ENTRY_POINTS)
+    targets = set(re.findall(r'"(nml\.nvfp4\.sm100\.[a-z_]+)"', added))
+    assert {"nml.nvfp4.sm100." + name[len("nml_nvfp4_sm100_"):] for name in bound} <= targets
+
+
 def test_struct_sizes_match_reference_prefix():
     # The reference structs (nml_nvfp4.h:18-92) on LP64: Linear 96, Embedding 88,
     # ExpertGateUp 152, ExpertDown 152 bytes; the two trailing pointers add 16.
