@@ -24,8 +24,9 @@ template <int BM, int KS, int PS, int XS, int WB, int DG, int MI, int PA, bool W
 int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* message,
                       size_t capacity) {
   using L = KernelLayout<BM, KS, PS, XS, WB, WT, AFMT, MODE, false>;
-  const int scale_buffer_bytes = WT ? ((args.inputs / 16 * kTileN + 127) / 128) * 128 : 0;
-  const int smem_bytes = L::kSmemBytes + 2 * scale_buffer_bytes;
+  const int scale_buffer_bytes = WT ? bulk_scale_buffer_bytes(args.inputs / 16) : 0;
+  const int scale_buffers = L::kSmemBytes + 2 * scale_buffer_bytes > kSmemBudget ? 1 : 2;
+  const int smem_bytes = L::kSmemBytes + scale_buffers * scale_buffer_bytes;
   if (smem_bytes > kSmemBudget) return kDoesNotFit;
   const int rows_per_expert = args.gate_up ? 2 * args.outputs : args.outputs;
   const int64_t weight_rows = static_cast<int64_t>(args.experts) * rows_per_expert;
@@ -70,6 +71,8 @@ int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* me
   p.top_k = args.experts_per_token;
   p.status = device.status_word;
   p.scale_buffer_bytes = scale_buffer_bytes;
+  p.scale_stride = bulk_scale_stride(static_cast<int>(args.inputs / 16));
+  p.scale_buffers = scale_buffers;
   p.split_k = 1;
 
   auto kernel = gemm_kernel<BM, KS, PS, XS, WB, DG, MI, PA, WT, AFMT, T, MODE, XTMA>;

@@ -22,7 +22,7 @@ template <int BM, int KS, int PS, int XS, int WB, int DG, int MI, int PA, bool W
 int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* message,
                       size_t capacity) {
   using L = KernelLayout<BM, KS, PS, XS, WB, WT, AFMT, kDense, SB>;
-  const int scale_buffer_bytes = (WT || SB) ? ((args.inputs / 16 * kTileN + 127) / 128) * 128 : 0;
+  const int scale_buffer_bytes = (WT || SB) ? bulk_scale_buffer_bytes(args.inputs / 16) : 0;
   // Few tiles and few rows (decode shapes of the 2880-class weights): cut K over a cluster so
   // that more SMs stream the weights.  One unit per cluster, at least 8 K steps per CTA.
   int total_tiles = (args.outputs + kTileN - 1) / kTileN;
@@ -37,7 +37,12 @@ int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* me
       ++split_k;
     }
   }
-  int smem_bytes = L::kSmemBytes + 2 * scale_buffer_bytes;
+  // Two scale buffers let the next unit's scales land while this one is decoded; when they do
+  // not fit (K = 4096) one buffer does: the decode of a unit's first K step then waits for the
+  // copy, once per unit, which costs far less than giving up an activation stage.
+  int scale_buffers = 2;
+  if (L::kSmemBytes + 2 * scale_buffer_bytes > kSmemBudget) scale_buffers = 1;
+  int smem_bytes = L::kSmemBytes + scale_buffers * scale_buffer_bytes;
   // rank 0 keeps the f32 partial tiles of the other ranks behind the scale buffers: step the
   // split down until they fit instead of giving it up
   while (split_k > 1 && smem_bytes + (split_k - 1) * kTileN * BM * 4 > kSmemBudget) --split_k;
@@ -84,6 +89,8 @@ int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* me
   p.output = args.output;
   p.status = device.status_word;
   p.scale_buffer_bytes = scale_buffer_bytes;
+  p.scale_stride = bulk_scale_stride(static_cast<int>(args.inputs / 16));
+  p.scale_buffers = scale_buffers;
 
   auto kernel = gemm_kernel<BM, KS, PS, XS, WB, DG, MI, PA, WT, AFMT, T, kDense, true, SB>;
   static std::atomic<int> configured[64];
@@ -232,15 +239,11 @@ int32_t launch_for_rows(const LinearArgs& args, const DeviceInfo& device, char* 
       return launch_config<128, 1, 8, 5, 5, 3, 1, 1, false, AFMT, T>(args, device, message,
                                                                      capacity);
     default: {
-      // 256-row tiles: scales by bulk copy when the two buffers fit beside three activation
-      // stages (K <= ~2900) and the copy is legal; else per-stage 4-byte copies
+      // 256-row tiles: scales by bulk copy when the copy is legal and a buffer (two up to
+      // K ~ 2900) fits beside three activation stages; else per-stage 4-byte copies
       if (bulk_scales_legal) {
         int32_t rc = launch_config<256, 1, 4, 3, 4, 3, 1, 1, false, AFMT, T, true>(
             args, device, message, capacity);
-        if (rc != kDoesNotFit) return rc;
-        // larger K (4096): the two scale buffers leave room for two activation stages
-        rc = launch_config<256, 1, 4, 2, 4, 3, 1, 1, false, AFMT, T, true>(args, device, message,
-                                                                           capacity);
         if (rc != kDoesNotFit) return rc;
       }
       return launch_config<256, 1, 6, 4, 4, 3, 1, 1, false, AFMT, T>(args, device, message,

@@ -158,7 +158,9 @@ struct Params {
   // shared memory, rank 0 adds them in rank order (ascending K) and finishes the unit.
   int split_k;  // 1: no split
   int* status;
-  int scale_buffer_bytes;  // WT: bytes of one scale buffer (128 rows x K / 16, 128-aligned)
+  int scale_buffer_bytes;  // BULK: bytes of one scale buffer (128 rows x scale_stride, 128-aligned)
+  int scale_stride;        // BULK: bytes between the scale rows of a buffer (bulk_scale_stride)
+  int scale_buffers;       // BULK: 2, or 1 when a second buffer would cost an activation stage
 };
 
 // One unit of work: a 128-row weight tile against BM activation rows / schedule slots.
@@ -471,7 +473,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
   auto scale_buffer = [&](int b) { return smem + L::kScaleBufferOffset + b * p.scale_buffer_bytes; };
   // split K, rank 0: f32 partial tiles [128 x BM] of ranks 1.. behind the scale buffers
   auto partial_tile = [&](int i) {
-    return reinterpret_cast<float*>(smem + L::kScaleBufferOffset + 2 * p.scale_buffer_bytes +
+    return reinterpret_cast<float*>(smem + L::kScaleBufferOffset +
+                                    p.scale_buffers * p.scale_buffer_bytes +
                                     i * (kTileN * BM * 4));
   };
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarrierOffset);
@@ -493,6 +496,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
   Groups* groups = reinterpret_cast<Groups*>(smem + L::kBarrierOffset + L::kBarrierBytes);
   uint64_t* x_free = kSharedEmpty ? empty_w : empty_x;
   // Per-unit weight operands: in dense mode they come from the unit's segment.
+  // the scale buffer and barrier phase of the CTA's `local`-th unit
+  auto scale_slot = [&](int local) { return p.scale_buffers == 2 ? (local & 1) : 0; };
+  auto scale_phase = [&](int local) -> uint32_t {
+    return p.scale_buffers == 2 ? ((local >> 1) & 1) : (local & 1);
+  };
   auto scale_base = [&](const Unit& u) -> const uint8_t* {
     return GROUPED ? p.block_scales : p.segment[u.expert].block_scales;
   };
@@ -612,20 +620,42 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     bool ok = true;
     for (int index = first_unit; index < units && ok; index += unit_stride, ++local) {
       const Unit u = get_unit<BM, GROUPED>(p, groups, index);
-      if constexpr (kBulk) {
-        // all block scales of the unit's weight rows: one contiguous range of the tensor
-        const int b = local & 1;
-        if (!wait(&empty_scale[b], ((local >> 1) & 1) ^ 1u, kSiteProducerScale)) break;
+      // All block scales of the unit's weight rows: one contiguous range of the tensor, copied
+      // at once, or row by row when the rows are padded apart in shared memory.  With two
+      // buffers the copy goes first; with one it has to wait for the previous unit's decode to
+      // end, so the first payload stages of this unit are put in flight before it (it must
+      // still precede the wait for a stage that only this unit's decode can free).
+      auto issue_scales = [&]() -> bool {
+        const int b = scale_slot(local);
+        if (!wait(&empty_scale[b], scale_phase(local) ^ 1u, kSiteProducerScale)) return false;
+        const int rows = min(kTileN, weight_rows(u) - u.weight_row0);
+        const uint8_t* from =
+            scale_base(u) + static_cast<int64_t>(u.weight_row0) * p.scale_width;
         if (lane == 0) {
-          const int rows = min(kTileN, weight_rows(u) - u.weight_row0);
-          const uint32_t bytes = static_cast<uint32_t>(rows * p.scale_width);
-          mbar_arrive_expect_tx(&full_scale[b], bytes);
-          bulk_load(scale_buffer(b),
-                    scale_base(u) + static_cast<int64_t>(u.weight_row0) * p.scale_width, bytes,
-                    &full_scale[b]);
+          mbar_arrive_expect_tx(&full_scale[b], static_cast<uint32_t>(rows * p.scale_width));
+          if (p.scale_stride == p.scale_width) {
+            bulk_load(scale_buffer(b), from, static_cast<uint32_t>(rows * p.scale_width),
+                      &full_scale[b]);
+          }
         }
-      }
+        if (p.scale_stride != p.scale_width) {
+          __syncwarp();
+          for (int r = lane; r < rows; r += 32) {
+            bulk_load(scale_buffer(b) + r * p.scale_stride, from + r * p.scale_width,
+                      static_cast<uint32_t>(p.scale_width), &full_scale[b]);
+          }
+          __syncwarp();
+        }
+        return true;
+      };
+      const int scales_at = p.scale_buffers == 2 ? 0 : min(PS, stages) - 1;
       for (int rs = 0; rs < stages; ++rs) {
+        if constexpr (kBulk) {
+          if (rs == scales_at && !issue_scales()) {
+            ok = false;
+            break;
+          }
+        }
         if (!wait(&empty_p[ps.index], ps.phase ^ 1u, kSiteProducerRaw)) {
           ok = false;
           break;
@@ -666,9 +696,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       if (!mbar_wait(&full_p[ps.index], ps.phase)) give_up(kSiteProducerDrain);
     }
     if constexpr (kBulk) {
-      for (int back = 1; back <= 2 && back <= local; ++back) {
+      for (int back = 1; back <= p.scale_buffers && back <= local; ++back) {
         const int unit = local - back;
-        if (!mbar_wait(&full_scale[unit & 1], (unit >> 1) & 1)) give_up(kSiteProducerDrain);
+        if (!mbar_wait(&full_scale[scale_slot(unit)], scale_phase(unit))) {
+          give_up(kSiteProducerDrain);
+        }
       }
     }
   } else if (XTMA && warp == kGatherWarp0) {
@@ -1005,8 +1037,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     for (int index = first_unit; index < units && ok; index += unit_stride, ++local) {
       const uint8_t* unit_scales = nullptr;
       if constexpr (kBulk) {
-        if (!wait(&full_scale[local & 1], (local >> 1) & 1, kSiteDecodeScale)) break;
-        unit_scales = scale_buffer(local & 1) + row * p.scale_width;
+        if (!wait(&full_scale[scale_slot(local)], scale_phase(local), kSiteDecodeScale)) break;
+        unit_scales = scale_buffer(scale_slot(local)) + row * p.scale_stride;
       }
       for (int rs = 0; rs < stages && ok; ++rs) {
         if (!wait(&full_p[ps.index], ps.phase, kSiteDecodeRaw)) {
@@ -1130,7 +1162,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       if constexpr (kBulk) {
         // this warp has read its last scale of the unit: the buffer may be refilled
         __syncwarp();
-        if (lane == 0) mbar_arrive(&empty_scale[local & 1]);
+        if (lane == 0) mbar_arrive(&empty_scale[scale_slot(local)]);
       }
     }
   } else {
@@ -1224,8 +1256,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
 
 // ---- host helpers -------------------------------------------------------------------------
 
+
 namespace nml_sm100 {
 namespace umma {
+
+// Bytes between the scale rows of a unit's shared-memory scale buffer.  Thread r of a decode
+// warp reads the 4-byte word (row r, K step s), so a row pitch of an even number of words maps
+// several lanes to one bank (all 32 at K = 4096, 256-byte rows).  Such rows are copied one by
+// one and padded apart to a pitch of 4 (mod 8) words: eight distinct banks, the best a 16-byte
+// aligned bulk-copy destination allows.  Odd word pitches (K = 2880: 45 words) stay contiguous.
+inline int bulk_scale_stride(int scale_width) {
+  if (scale_width % 16 != 0) return scale_width;
+  int stride = scale_width + 16;
+  while ((stride / 4) % 8 != 4) stride += 16;
+  return stride;
+}
+
+inline int bulk_scale_buffer_bytes(int scale_width) {
+  return (bulk_scale_stride(scale_width) * kTileN + 127) / 128 * 128;
+}
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
