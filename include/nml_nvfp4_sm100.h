@@ -44,7 +44,11 @@ typedef enum NmlSm100DType {
 #define NML_SM100_LAUNCH_FAILURE 2
 
 /* Y[rows, outputs] = X[rows, inputs] * W[outputs, inputs]^T (+ bias), f32 accumulate.
- * Field-for-field NmlNvFp4Linear (nml_nvfp4.h:18-31). */
+ * Field-for-field NmlNvFp4Linear (nml_nvfp4.h:18-31), plus one optional trailing field that is
+ * read only when struct_size covers it: `residual` [rows, outputs] is added to the narrowed
+ * result, Y = narrow(narrow(X W^T + bias) + residual), which is what the reference graph
+ * computes with a separate add after the attention output projection
+ * (products/serve/src/gpt_oss/graph.rs:534-543); `residual` may alias `output`. */
 typedef struct NmlSm100Linear {
   size_t struct_size;
   const void *activation;      /* [rows, inputs] dtype */
@@ -58,6 +62,7 @@ typedef struct NmlSm100Linear {
   int64_t outputs;
   int64_t inputs;
   int32_t dtype; /* NmlSm100DType */
+  const void *residual; /* optional: [rows, outputs] dtype, or NULL */
 } NmlSm100Linear;
 
 /* Three linears that share one activation (the Q, K and V projections), in one launch:

@@ -44,7 +44,7 @@ class Linear(ctypes.Structure):
     _fields_ = [("struct_size", _sz), ("activation", _vp), ("payload", _vp),
                 ("block_scales", _vp), ("global_scale", _vp), ("bias", _vp), ("output", _vp),
                 ("stream", _vp), ("rows", _i64), ("outputs", _i64), ("inputs", _i64),
-                ("dtype", _i32)]
+                ("dtype", _i32), ("residual", _vp)]
 
 
 class LinearQkv(ctypes.Structure):

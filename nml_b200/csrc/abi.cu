@@ -270,7 +270,7 @@ extern "C" int32_t nml_nvfp4_sm100_device_status(void* stream, int32_t clear, in
 
 extern "C" int32_t nml_nvfp4_sm100_linear(const NmlSm100Linear* request, char* error_message,
                                           size_t error_message_capacity) {
-  if (request == nullptr || request->struct_size < sizeof(NmlSm100Linear)) {
+  if (request == nullptr || request->struct_size < offsetof(NmlSm100Linear, residual)) {
     return fail(NML_SM100_INVALID_ARGUMENT, "truncated NVFP4 linear request", error_message,
                 error_message_capacity);
   }
@@ -299,6 +299,9 @@ extern "C" int32_t nml_nvfp4_sm100_linear(const NmlSm100Linear* request, char* e
   args.outputs = static_cast<int>(request->outputs);
   args.inputs = static_cast<int>(request->inputs);
   args.dtype = request->dtype;
+  args.residual = has_field(request, offsetof(NmlSm100Linear, residual), sizeof(void*))
+                      ? request->residual
+                      : nullptr;
   return dispatch_linear(args, *device, error_message, error_message_capacity);
 }
 

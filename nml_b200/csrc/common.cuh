@@ -95,6 +95,15 @@ struct Elem<__nv_bfloat16> {
   }
 };
 
+// Narrows a finished linear output; with a residual operand the narrowed value and the
+// residual are added and narrowed again, as a separate elementwise add on 16-bit tensors would.
+template <typename T>
+__device__ __forceinline__ T narrow_with_residual(float value, const T* residual, int64_t index) {
+  const T narrowed = Elem<T>::store(value);
+  if (residual == nullptr) return narrowed;
+  return Elem<T>::store(Elem<T>::load(narrowed) + Elem<T>::load(residual[index]));
+}
+
 // Clamped residual SwiGLU of the routed experts (crates/nml-kernel-nvfp4/src/lib.rs:424-429):
 // gate clamps above 7, up clamps to [-7, 7], result (up + 1) * gate * sigmoid(1.702 * gate).
 __device__ __forceinline__ float clamped_swiglu(float gate, float up) {
@@ -115,6 +124,7 @@ struct LinearArgs {
   cudaStream_t stream;
   int rows, outputs, inputs;
   int dtype;
+  const void* residual = nullptr;  // [rows, outputs], added to the narrowed result
   // Fused projections that share the activation (Q/K/V): further weights after the first.
   struct Projection {
     const uint8_t* payload;

@@ -19,7 +19,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 linear_simt_kernel(const T* __restrict__ activation, const uint8_t* __restrict__ payload,
                    const uint8_t* __restrict__ block_scales,
                    const float* __restrict__ global_scale, const T* __restrict__ bias,
-                   T* __restrict__ output, int rows, int outputs, int inputs) {
+                   const T* residual, T* output, int rows, int outputs, int inputs) {
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int64_t n = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
@@ -71,7 +71,8 @@ linear_simt_kernel(const T* __restrict__ activation, const uint8_t* __restrict__
       }
       const int row = row_base + r;
       if (lane == 0 && row < rows) {
-        output[static_cast<int64_t>(row) * outputs + n] = Elem<T>::store(sum + bias_value);
+        const int64_t index = static_cast<int64_t>(row) * outputs + n;
+        output[index] = narrow_with_residual<T>(sum + bias_value, residual, index);
       }
     }
   }
@@ -87,11 +88,13 @@ int32_t launch_linear_simt(const LinearArgs& args, const DeviceInfo&, char* mess
     linear_simt_kernel<__half><<<grid, kWarpsPerBlock * 32, 0, args.stream>>>(
         static_cast<const __half*>(args.activation), args.payload, args.block_scales,
         args.global_scale, static_cast<const __half*>(args.bias),
-        static_cast<__half*>(args.output), args.rows, args.outputs, args.inputs);
+        static_cast<const __half*>(args.residual), static_cast<__half*>(args.output), args.rows,
+        args.outputs, args.inputs);
   } else {
     linear_simt_kernel<__nv_bfloat16><<<grid, kWarpsPerBlock * 32, 0, args.stream>>>(
         static_cast<const __nv_bfloat16*>(args.activation), args.payload, args.block_scales,
         args.global_scale, static_cast<const __nv_bfloat16*>(args.bias),
+        static_cast<const __nv_bfloat16*>(args.residual),
         static_cast<__nv_bfloat16*>(args.output), args.rows, args.outputs, args.inputs);
   }
   note_linear_kernel("simt", 0);

@@ -72,12 +72,14 @@ int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* me
   p.K = args.inputs;
   p.split_k = split_k;
   p.segments = 1 + args.extra_projections;
-  p.segment[0] = {args.block_scales, args.global_scale, args.bias, args.output, args.outputs, 0};
+  p.segment[0] = {args.block_scales, args.global_scale, args.bias, args.output, args.outputs, 0,
+                  args.residual};
   p.n_tiles = (args.outputs + kTileN - 1) / kTileN;
   int64_t weight_bytes = static_cast<int64_t>(args.outputs) * (args.inputs / 2);
   for (int i = 0; i < args.extra_projections; ++i) {
     const LinearArgs::Projection& e = args.extra[i];
-    p.segment[1 + i] = {e.block_scales, e.global_scale, e.bias, e.output, e.outputs, p.n_tiles};
+    p.segment[1 + i] = {e.block_scales, e.global_scale, e.bias, e.output, e.outputs, p.n_tiles,
+                        nullptr};
     p.n_tiles += (e.outputs + kTileN - 1) / kTileN;
     weight_bytes += static_cast<int64_t>(e.outputs) * (args.inputs / 2);
   }

@@ -118,12 +118,12 @@ int32_t launch_linear_stream(const LinearArgs& args, const DeviceInfo& device, c
   p.M = args.rows;
   p.segments = 1 + args.extra_projections;
   p.segment[0] = {args.payload, args.block_scales, args.global_scale, args.bias, args.output,
-                  args.outputs, 0};
+                  args.outputs, 0, args.residual};
   int tiles = (args.outputs + kTileRows - 1) / kTileRows;
   for (int i = 0; i < args.extra_projections; ++i) {
     const LinearArgs::Projection& e = args.extra[i];
     p.segment[1 + i] = {e.payload, e.block_scales, e.global_scale, e.bias, e.output, e.outputs,
-                        tiles};
+                        tiles, nullptr};
     tiles += (e.outputs + kTileRows - 1) / kTileRows;
   }
   p.groups = (args.rows + 15) / 16;

@@ -68,6 +68,7 @@ struct Segment {
   void* output;
   int outputs;     // rows of this weight = output columns
   int tile_begin;  // first tile of the segment in the launch's tile list
+  const void* residual;  // [M, outputs] added to the narrowed result, or null
 };
 
 struct Params {
@@ -624,6 +625,7 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
         const float scale = __ldg(segment.global_scale);
         T* out = static_cast<T*>(segment.output);
         const T* bias = static_cast<const T*>(segment.bias);
+        const T* residual = static_cast<const T*>(segment.residual);
         const int n0 = (w.tile - segment.tile_begin) * kTileRows + 16 * rt + g;
 #pragma unroll
         for (int half = 0; half < 2; ++half) {  // weight rows g and g + 8
@@ -634,12 +636,12 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
             const float v1 = half == 0 ? sum.y : sum.w;
             const int m = w.group * 16 + 8 * jn + 2 * c;
             if (m < p.M) {
-              out[static_cast<int64_t>(m) * segment.outputs + n] =
-                  Elem<T>::store(fmaf(v0, scale, bias_value));
+              const int64_t index = static_cast<int64_t>(m) * segment.outputs + n;
+              out[index] = narrow_with_residual<T>(fmaf(v0, scale, bias_value), residual, index);
             }
             if (m + 1 < p.M) {
-              out[static_cast<int64_t>(m + 1) * segment.outputs + n] =
-                  Elem<T>::store(fmaf(v1, scale, bias_value));
+              const int64_t index = static_cast<int64_t>(m + 1) * segment.outputs + n;
+              out[index] = narrow_with_residual<T>(fmaf(v1, scale, bias_value), residual, index);
             }
           }
         }

@@ -150,6 +150,7 @@ struct Params {
     void* output;
     int outputs;     // rows of this weight = output columns
     int tile_begin;  // first weight tile of the segment
+    const void* residual;  // dense: [M, outputs] added to the narrowed result, or null
   };
   Segment segment[3];
   int segments;
@@ -842,6 +843,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     float g = GROUPED ? __ldg(p.global_scale) * kDecodeFactor : 0.0f;
     T* out = static_cast<T*>(p.output);
     const T* bias = static_cast<const T*>(p.bias);
+    const T* residual = nullptr;  // dense: the segment's residual operand
     int out_columns = p.N;
     const int row = quarter * 32 + lane;  // row of the weight tile this thread reads
     int local = 0;
@@ -885,6 +887,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         g = __ldg(segment.global_scale) * kDecodeFactor;
         out = static_cast<T*>(segment.output);
         bias = static_cast<const T*>(segment.bias);
+        residual = static_cast<const T*>(segment.residual);
         out_columns = segment.outputs;
       }
       const int n = u.n0 + row;  // output column (dense, down) or weight row in the expert
@@ -966,8 +969,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
             for (int j = 0; j < kChunk; ++j) {
               const int m = u.m0 + c + j;
               if (c + j < u.rows) {
-                out[static_cast<int64_t>(m) * out_columns + n] =
-                    Elem<T>::store(fmaf(__uint_as_float(v[j]), g, bias_value));
+                const int64_t index = static_cast<int64_t>(m) * out_columns + n;
+                out[index] = narrow_with_residual<T>(fmaf(__uint_as_float(v[j]), g, bias_value),
+                                                     residual, index);
               }
             }
           }

@@ -235,7 +235,7 @@ class DecodeModel:
             layer["value"][self.write_page, self.write_slot] = v.view(
                 self.batch, shape.key_value_heads, shape.head_dim)
             attention = self._attention(layer, q)
-            hidden = hidden + ops.linear(attention, layer["o"], layer["o_bias"])
+            hidden = ops.linear(attention, layer["o"], layer["o_bias"], residual=hidden)
             x = F.rms_norm(hidden, (shape.hidden,), layer["post_norm"], eps)
             hidden = hidden + self._moe(layer, x)
         x = F.rms_norm(hidden, (shape.hidden,), self.final_norm, eps)

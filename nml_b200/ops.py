@@ -99,8 +99,11 @@ class NvFp4Parameter:
 
 
 def linear(input: torch.Tensor, weight: NvFp4Parameter, bias: torch.Tensor | None = None,
-           out: torch.Tensor | None = None) -> torch.Tensor:
-    """``[..., K] x [N, K]^T (+ bias[N])`` with f32 accumulation; result in the input dtype."""
+           out: torch.Tensor | None = None, residual: torch.Tensor | None = None) -> torch.Tensor:
+    """``[..., K] x [N, K]^T (+ bias[N])`` with f32 accumulation; result in the input dtype.
+    ``residual`` (shape and dtype of the result; may be ``out`` itself) is added to the narrowed
+    result in the kernel's epilogue: bit for bit ``linear(...) + residual`` of the reference
+    graph's output projection (products/serve/src/gpt_oss/graph.rs:534-543) in one launch."""
     if input.dim() == 0:
         raise ValueError("linear input requires at least one dimension")
     if len(weight.shape) != 2:
@@ -123,11 +126,16 @@ def linear(input: torch.Tensor, weight: NvFp4Parameter, bias: torch.Tensor | Non
         out = torch.empty(result_shape, dtype=input.dtype, device=input.device)
     elif tuple(out.shape) != result_shape or out.dtype != input.dtype:
         raise ValueError("NVFP4 linear component and output shapes are inconsistent")
+    if residual is not None:
+        if tuple(residual.shape) != result_shape or residual.dtype != input.dtype or \
+                not residual.is_contiguous():
+            raise ValueError("NVFP4 linear residual must match the result's shape and dtype")
+        _require_cuda(residual)
     request = _abi.Linear(activation=_ptr(input), payload=_ptr(weight.payload),
                           block_scales=_ptr(weight.block_scales),
                           global_scale=_ptr(weight.global_scale), bias=_ptr(bias),
                           output=_ptr(out), stream=_stream(input), rows=rows, outputs=outputs,
-                          inputs=inputs, dtype=dtype)
+                          inputs=inputs, dtype=dtype, residual=_ptr(residual))
     _abi.call("nml_nvfp4_sm100_linear", request)
     return out
 
@@ -447,6 +455,22 @@ def routed_clamped_swiglu_masked(hidden: torch.Tensor, router_logits: torch.Tens
 _ATTENTION_SCRATCH: dict = {}
 
 
+def _attention_splits(pairs: int, visible_pages: int, sms: int) -> int:
+    """Splits of the visible pages per (sequence, kv head).  Six CTAs of the decode kernel are
+    resident per SM (128 threads, 80 registers), so a launch runs in waves of 6 * sms CTAs and
+    its time follows waves / splits: pick the split count that minimises it (a slight
+    preference for fewer splits, whose partial results cost a second pass), at most one split
+    per 8 pages."""
+    slots = 6 * sms
+    best, best_cost = 1, float("inf")
+    for candidate in range(1, max(1, min(64, visible_pages // 8)) + 1):
+        waves = -(-pairs * candidate // slots)
+        cost = waves / candidate + 0.004 * candidate
+        if cost < best_cost - 1e-9:
+            best, best_cost = candidate, cost
+    return best
+
+
 def paged_attention_decode(query: torch.Tensor, key_cache: torch.Tensor,
                            value_cache: torch.Tensor, page_table: torch.Tensor,
                            sequence_lengths: torch.Tensor, sinks: torch.Tensor | None = None,
@@ -475,11 +499,9 @@ def paged_attention_decode(query: torch.Tensor, key_cache: torch.Tensor,
         raise ValueError("attention sinks must be F32 [query_heads]")
     _require_cuda(query, key_cache, value_cache, page_table, sequence_lengths, sinks)
     if splits is None:
-        # enough CTAs for a few waves over the SMs, at most one split per 8 pages
         sms = torch.cuda.get_device_properties(query.device).multi_processor_count
-        wanted = -(-4 * sms // max(1, batch * kv_heads))
         visible = page_table.shape[1] if not sliding_window else -(-sliding_window // page_size) + 1
-        splits = max(1, min(wanted, max(1, visible // 8), 64))
+        splits = _attention_splits(batch * kv_heads, visible, sms)
     lib = _abi.load()
     size = lib.nml_sm100_paged_attention_decode_workspace_bytes(batch, query_heads, splits)
     key = (query.device, torch.cuda.current_stream(query.device).cuda_stream)

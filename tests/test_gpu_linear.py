@@ -255,3 +255,38 @@ def test_split_k_over_a_cluster_matches_oracle_and_unsplit_kernel(M, K, N, dtype
     expected = oracle.linear(x32, *triple, None)
     gu.assert_gemm_close(gu.device_f32(split), expected, f"split M={M} K={K} N={N}")
     gu.assert_gemm_close(gu.device_f32(unsplit), expected, f"unsplit M={M} K={K} N={N}")
+
+
+@pytest.mark.parametrize("dtype", [oracle.BF16, oracle.F16])
+@pytest.mark.parametrize("M,K,N,policy_name", [
+    (1, 4096, 2880, "POLICY_AUTO"), (16, 4096, 2880, "POLICY_AUTO"),   # weight-streaming kernel
+    (64, 4096, 2880, "POLICY_UMMA"), (300, 4096, 2880, "POLICY_AUTO"),  # tcgen05, both homes
+    (520, 2880, 2880, "POLICY_UMMA_SMEM"), (5, 48, 20, "POLICY_SIMT")])
+def test_residual_operand_equals_a_separate_add(M, K, N, policy_name, dtype):
+    # products/serve/src/gpt_oss/graph.rs:534-543: hidden + o_proj(attention).  The epilogue
+    # narrows the projection, adds the residual and narrows again, so the fused call equals the
+    # two-step evaluation bit for bit, also when the residual is the output buffer itself.
+    from nml_b200 import ops, _abi
+    import gpu_util as gu
+    triple = make_weight(1300, (N, K))
+    weight = gu.parameter("w", triple, K, dtype)
+    x_bits, _ = make_activation(1301, (M, K), dtype=dtype)
+    bias_bits, _ = make_activation(1302, (N,), std=0.5, dtype=dtype)
+    res_bits, _ = make_activation(1303, (M, N), std=2.0, dtype=dtype)
+    x, bias = gu.to_device_bits(x_bits, dtype), gu.to_device_bits(bias_bits, dtype)
+    residual = gu.to_device_bits(res_bits, dtype)
+    previous = _abi.set_kernel_policy(getattr(_abi, policy_name))
+    try:
+        plain = ops.linear(x, weight, bias)
+        fused = ops.linear(x, weight, bias, residual=residual)
+        in_place = residual.clone()
+        ops.linear(x, weight, bias, out=in_place, residual=in_place)
+        torch.cuda.synchronize()
+    finally:
+        _abi.set_kernel_policy(previous)
+    two_step = (plain.float() + residual.float()).to(plain.dtype)
+    assert torch.equal(fused.view(torch.int16), two_step.view(torch.int16))
+    assert torch.equal(in_place.view(torch.int16), two_step.view(torch.int16))
+    with pytest.raises(ValueError):
+        ops.linear(x, weight, bias, residual=residual[:, :-1])
+    assert _abi.device_status(0x1) == 0
