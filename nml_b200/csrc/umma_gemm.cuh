@@ -964,7 +964,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
               }
             }
           }
-          if (n_ok) {
+          // two copies of the store loop: the residual form costs the plain one nothing
+          if (n_ok && residual == nullptr) {
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j) {
+              const int m = u.m0 + c + j;
+              if (c + j < u.rows) {
+                out[static_cast<int64_t>(m) * out_columns + n] =
+                    Elem<T>::store(fmaf(__uint_as_float(v[j]), g, bias_value));
+              }
+            }
+          } else if (n_ok) {
 #pragma unroll
             for (int j = 0; j < kChunk; ++j) {
               const int m = u.m0 + c + j;

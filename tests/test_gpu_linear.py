@@ -103,13 +103,23 @@ def test_tensor_core_kernel_shared_memory_weight_ring(M, K, N, dtype):
                expect_kernel="umma_swapab_a")
 
 
-@pytest.mark.parametrize("M,K,N", [(200, 8192, 256), (64, 128, 130), (33, 16384, 512)])
+@pytest.mark.parametrize("M,K,N", [(64, 128, 130), (33, 16384, 512)])
 def test_tensor_core_kernel_falls_back_to_shared_memory_ring(M, K, N):
-    # two scale buffers (128 rows x K/16 bytes each) that no longer fit beside the rings, or an
-    # output count that breaks the bulk scale copy
+    # a scale buffer (128 rows x K/16 bytes, rows padded apart) that does not fit beside the
+    # rings even alone, or an output count that breaks the bulk scale copy
     from nml_b200 import _abi
     run_linear(M, K, N, oracle.BF16, _abi.POLICY_UMMA, seed=M + N + 2,
                expect_kernel="umma_swapab_abf16")
+
+
+@pytest.mark.parametrize("M,K,N", [(200, 8192, 256), (512, 4096, 2880), (40, 4096, 384),
+                                   (4096, 4096, 2880)])
+def test_tensor_core_kernel_with_one_scale_buffer(M, K, N):
+    # K >= 4096: 256- and 512-byte scale rows are copied row by row with a padded pitch, and
+    # where two such buffers do not fit the kernel runs with one (units take turns on it)
+    from nml_b200 import _abi
+    run_linear(M, K, N, oracle.BF16, _abi.POLICY_UMMA, seed=M + N + 3, with_bias=True,
+               sample_rows=48)
 
 
 CONFIG_SHAPES = [(2880, 5120), (4096, 2880), (2880, 5760), (2880, 2880)]
