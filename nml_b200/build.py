@@ -42,7 +42,7 @@ def _stale() -> bool:
 
 def build(force: bool = False, verbose: bool = False, defines=(), output: Path | None = None) -> Path:
     """Compiles every source and links the shared object.  ``defines`` adds -D flags (for
-    example NML_SM100_PROFILE, the stall-accounting build used when tuning) and ``output``
+    example a macro that switches a variant on when tuning) and ``output``
     redirects the result so that a tuning build never replaces the product library."""
     target = Path(output) if output is not None else LIB_PATH
     if output is None and not defines and not force and not _stale():

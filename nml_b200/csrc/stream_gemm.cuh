@@ -635,13 +635,26 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
             const float v0 = half == 0 ? sum.x : sum.z;
             const float v1 = half == 0 ? sum.y : sum.w;
             const int m = w.group * 16 + 8 * jn + 2 * c;
-            if (m < p.M) {
-              const int64_t index = static_cast<int64_t>(m) * segment.outputs + n;
-              out[index] = narrow_with_residual<T>(fmaf(v0, scale, bias_value), residual, index);
-            }
-            if (m + 1 < p.M) {
-              const int64_t index = static_cast<int64_t>(m + 1) * segment.outputs + n;
-              out[index] = narrow_with_residual<T>(fmaf(v1, scale, bias_value), residual, index);
+            if (residual == nullptr) {  // the plain form keeps its own, shorter store sequence
+              if (m < p.M) {
+                out[static_cast<int64_t>(m) * segment.outputs + n] =
+                    Elem<T>::store(fmaf(v0, scale, bias_value));
+              }
+              if (m + 1 < p.M) {
+                out[static_cast<int64_t>(m + 1) * segment.outputs + n] =
+                    Elem<T>::store(fmaf(v1, scale, bias_value));
+              }
+            } else {
+              if (m < p.M) {
+                const int64_t index = static_cast<int64_t>(m) * segment.outputs + n;
+                out[index] =
+                    narrow_with_residual<T>(fmaf(v0, scale, bias_value), residual, index);
+              }
+              if (m + 1 < p.M) {
+                const int64_t index = static_cast<int64_t>(m + 1) * segment.outputs + n;
+                out[index] =
+                    narrow_with_residual<T>(fmaf(v1, scale, bias_value), residual, index);
+              }
             }
           }
         }
