@@ -51,11 +51,11 @@ int32_t launch_for_shape(const Params& p, int nt, int rt, int smem_bytes, int64_
   launch_variant<NT, UT, RT, T, MODE, FULL>(p, smem_bytes, units_bound, device, stream,       \
                                             message, capacity)
 #define NML_STREAM_TILE(UT, FULL)                                                             \
-  (nt == 2 ? NML_STREAM_VARIANT(2, UT, 1, FULL)                                               \
+  (nt == 2 ? (rt == 2 ? NML_STREAM_VARIANT(2, UT, 2, FULL) : NML_STREAM_VARIANT(2, UT, 1, FULL)) \
            : (rt == 2 ? NML_STREAM_VARIANT(1, UT, 2, FULL) : NML_STREAM_VARIANT(1, UT, 1, FULL)))
   // Three variants: K units that split evenly into 3 per warp (K = 2880), evenly into 4 per
-  // warp (K = 4096), and the guarded form for every other width; each for one activation-row
-  // tile (16- or 32-row weight tiles) and for two.
+  // warp (K = 4096), and the guarded form for every other width; each for one or two
+  // activation-row tiles and 16- or 32-row weight tiles.
   const bool even = p.compute_warps * p.units_per_warp == p.k_units;
   if (even && p.units_per_warp == 3) return NML_STREAM_TILE(3, true);
   if (even && p.units_per_warp == 4) return NML_STREAM_TILE(4, true);
@@ -68,10 +68,16 @@ int32_t launch_for_shape(const Params& p, int nt, int rt, int smem_bytes, int64_
 // enough for the per-tile bookkeeping to matter and coarse enough tiles still balance.
 constexpr int64_t kLargeTileWalk = 6;
 
-// With two activation-row tiles the registers do not hold a second fragment of accumulators
-// and decodes without spilling, and the larger tile was measured slower there.
-int tile_fragments(int nt, int64_t fragments, const DeviceInfo& device) {
-  return nt == 1 && fragments >= kLargeTileWalk * device.sm_count ? 2 : 1;
+int tile_fragments(int64_t fragments, const DeviceInfo& device) {
+  return fragments >= kLargeTileWalk * device.sm_count ? 2 : 1;
+}
+
+// The layout for the preferred tile height, or for 16-row tiles when the larger one does not
+// leave two stages of shared memory (wide K with two activation-row tiles).
+bool plan_tiles(int K, int nt, int* rt, Params* p, int* smem_bytes) {
+  if (*rt == 2 && plan_layout(K, nt, 2, p, smem_bytes)) return true;
+  *rt = 1;
+  return plan_layout(K, nt, 1, p, smem_bytes);
 }
 
 bool aligned16(const void* pointer) { return reinterpret_cast<uintptr_t>(pointer) % 16 == 0; }
@@ -106,14 +112,14 @@ int32_t launch_linear_stream(const LinearArgs& args, const DeviceInfo& device, c
   for (int i = 0; i < args.extra_projections; ++i) {
     fragments += (args.extra[i].outputs + kFragmentRows - 1) / kFragmentRows;
   }
-  const int rt = tile_fragments(nt, fragments * ((args.rows + 15) / 16), device);
-  const int kTileRows = kFragmentRows * rt;
+  int rt = tile_fragments(fragments * ((args.rows + 15) / 16), device);
   int smem_bytes = 0;
-  if (!plan_layout(args.inputs, nt, rt, &p, &smem_bytes)) {
+  if (!plan_tiles(args.inputs, nt, &rt, &p, &smem_bytes)) {
     return fail(NML_SM100_INVALID_ARGUMENT,
                 "the weight-streaming linear does not support this input width", message,
                 capacity);
   }
+  const int kTileRows = kFragmentRows * rt;
   p.x = args.activation;
   p.M = args.rows;
   p.segments = 1 + args.extra_projections;
@@ -160,14 +166,14 @@ int32_t launch_experts_stream(const ExpertArgs& args, const DeviceInfo& device, 
   const int64_t live = args.live_routes > 0 ? args.live_routes : args.assignments;
   int64_t busy_blocks = nt == 1 ? live : live / 16 + args.experts;
   if (busy_blocks > args.schedule_blocks) busy_blocks = args.schedule_blocks;
-  const int rt = tile_fragments(nt, busy_blocks * (rows_per_expert / kFragmentRows), device);
-  const int kTileRows = kFragmentRows * rt;
+  int rt = tile_fragments(busy_blocks * (rows_per_expert / kFragmentRows), device);
   int smem_bytes = 0;
-  if (!plan_layout(args.inputs, nt, rt, &p, &smem_bytes)) {
+  if (!plan_tiles(args.inputs, nt, &rt, &p, &smem_bytes)) {
     return fail(NML_SM100_INVALID_ARGUMENT,
                 "the weight-streaming expert kernel does not support this input width", message,
                 capacity);
   }
+  const int kTileRows = kFragmentRows * rt;
   p.input = args.input;
   p.sorted_assignments = args.sorted_assignments;
   p.block_experts = args.block_experts;

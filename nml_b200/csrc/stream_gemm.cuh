@@ -393,10 +393,12 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
       }
       if (!wait(&full_p[ring.index], ring.phase, kSiteCompute)) break;
       const uint8_t* stage = smem + ring.index * p.stage_bytes;
-      // The mma.sync instructions of one fragment alternate over two accumulators (added in
-      // index order below) whatever the tile shape, so that a weight row's sum is formed in
-      // the same order in every variant: a fused launch equals separate launches bit for bit.
-      constexpr int kChains = 2;
+      // With one activation-row tile the mma.sync instructions of a fragment alternate over
+      // two accumulators (added in index order below); with two tiles each has one, which
+      // leaves registers for the 32-row tile.  The count depends on nothing but NT, so a
+      // weight row's sum is formed in the same order whatever the tile height: a fused launch
+      // equals separate launches bit for bit.
+      constexpr int kChains = NT == 1 ? 2 : 1;
       float acc[RT][NT][kChains][4];
       uint32_t seen[RT][2];  // OR of the scale bytes of rows g and g + 8: bit 7 marks an invalid one
 #pragma unroll
@@ -432,12 +434,13 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
               decode8(half == 0 ? words_h.x : words_h.y, pair_h, dh);
               mma_16816(acc[rt][0][0], dg[0], dh[0], dg[1], dh[1], b[u][4 * half],
                         b[u][4 * half + 1]);
-              mma_16816(acc[rt][0][1], dg[2], dh[2], dg[3], dh[3], b[u][4 * half + 2],
+              mma_16816(acc[rt][0][kChains - 1], dg[2], dh[2], dg[3], dh[3], b[u][4 * half + 2],
                         b[u][4 * half + 3]);
               if (NT == 2 && (!kGrouped || second_live)) {  // skipped for blocks of <= 8 routes
                 const uint4 second = b_second[(2 * u + half) * 32];
-                mma_16816(acc[rt][1][0], dg[0], dh[0], dg[1], dh[1], second.x, second.y);
-                mma_16816(acc[rt][1][1], dg[2], dh[2], dg[3], dh[3], second.z, second.w);
+                mma_16816(acc[rt][NT - 1][0], dg[0], dh[0], dg[1], dh[1], second.x, second.y);
+                mma_16816(acc[rt][NT - 1][kChains - 1], dg[2], dh[2], dg[3], dh[3], second.z,
+                          second.w);
               }
             }
           }
