@@ -20,11 +20,11 @@ using namespace umma;
 constexpr int32_t kDoesNotFit = -1000;  // internal: the variant's shared memory exceeds the SM's
 
 template <int BM, int KS, int PS, int XS, int WB, int DG, int MI, int PA, bool WT, int AFMT,
-          typename T, int MODE, bool XTMA>
+          typename T, int MODE, bool XTMA, bool SB = false>
 int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* message,
                       size_t capacity) {
-  using L = KernelLayout<BM, KS, PS, XS, WB, WT, AFMT, MODE, false>;
-  const int scale_buffer_bytes = WT ? bulk_scale_buffer_bytes(args.inputs / 16) : 0;
+  using L = KernelLayout<BM, KS, PS, XS, WB, WT, AFMT, MODE, SB>;
+  const int scale_buffer_bytes = (WT || SB) ? bulk_scale_buffer_bytes(args.inputs / 16) : 0;
   const int scale_buffers = L::kSmemBytes + 2 * scale_buffer_bytes > kSmemBudget ? 1 : 2;
   const int smem_bytes = L::kSmemBytes + scale_buffers * scale_buffer_bytes;
   if (smem_bytes > kSmemBudget) return kDoesNotFit;
@@ -75,9 +75,10 @@ int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* me
   p.scale_buffers = scale_buffers;
   p.split_k = 1;
 
-  auto kernel = gemm_kernel<BM, KS, PS, XS, WB, DG, MI, PA, WT, AFMT, T, MODE, XTMA>;
+  auto kernel = gemm_kernel<BM, KS, PS, XS, WB, DG, MI, PA, WT, AFMT, T, MODE, XTMA, SB>;
   static std::atomic<int> configured[64];
-  if (!reserve_smem(kernel, WT ? kSmemBudget : L::kSmemBytes, device.device, configured)) {
+  if (!reserve_smem(kernel, (WT || SB) ? kSmemBudget : L::kSmemBytes, device.device,
+                    configured)) {
     return fail(NML_SM100_LAUNCH_FAILURE, "cannot reserve shared memory for the tcgen05 experts",
                 message, capacity);
   }
@@ -155,6 +156,15 @@ int32_t launch_for_load(const ExpertArgs& args, const DeviceInfo& device, char* 
   if (average <= 160) {
     return launch_config<128, 1, 6, 5, 5, 2, 1, 1, false, AFMT, T, MODE, XTMA>(args, device,
                                                                               message, capacity);
+  }
+  if constexpr (XTMA) {
+    // slot-ordered input by TMA: no gather warps, so a third decode group fits, and the unit's
+    // block scales come by bulk copy (the form the dense 256-row tile runs in)
+    if (tmem_weights) {
+      const int32_t rc = launch_config<256, 1, 4, 3, 4, 3, 1, 1, false, AFMT, T, MODE, XTMA, true>(
+          args, device, message, capacity);
+      if (rc != kDoesNotFit) return rc;
+    }
   }
   return launch_config<256, 1, 4, 4, 4, 2, 1, 1, false, AFMT, T, MODE, XTMA>(args, device, message,
                                                                             capacity);
