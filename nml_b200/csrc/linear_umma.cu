@@ -5,8 +5,6 @@
 // between 64, 128 and 256 minimises waves x per-tile time on the device's SM count.  Small
 // tiles (decode shapes, HBM-bound) use raw stages of four K steps so that ~100 KB of packed
 // weight bytes are in flight per SM; large tiles are MMA-bound and use one K step per stage.
-#include <cstdlib>
-
 #include "umma_gemm.cuh"
 
 namespace nml_sm100 {
@@ -241,6 +239,18 @@ int32_t launch_for_rows(const LinearArgs& args, const DeviceInfo& device, char* 
       return launch_config<128, 1, 8, 5, 5, 3, 1, 1, false, AFMT, T>(args, device, message,
                                                                      capacity);
     default: {
+      // Wide K (4096): the shared-memory ring variant has room for one scale buffer only; the
+      // tensor-memory variant (one accumulator set beside eight W' tiles, byte-table decode)
+      // measured 9 % faster there, and equal or slower at K = 2880.
+      if constexpr (AFMT == kAbf16) {
+        using Ring = KernelLayout<256, 1, 4, 3, 4, false, AFMT, kDense, true>;
+        if (bulk_scales_legal && policy != NML_SM100_POLICY_UMMA_SMEM &&
+            Ring::kSmemBytes + 2 * bulk_scale_buffer_bytes(args.inputs / 16) > kSmemBudget) {
+          const int32_t rc = launch_config<256, 1, 4, 4, 8, 3, 1, 1, true, kAbf16Lut, T>(
+              args, device, message, capacity);
+          if (rc != kDoesNotFit) return rc;
+        }
+      }
       // 256-row tiles: scales by bulk copy when the copy is legal and a buffer (two up to
       // K ~ 2900) fits beside three activation stages; else per-stage 4-byte copies
       if (bulk_scales_legal) {

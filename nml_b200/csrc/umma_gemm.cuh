@@ -452,8 +452,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
   constexpr bool kBulk = WT || SB;  // block scales of a unit by one bulk copy
   constexpr bool kLut = AFMT == kAbf16Lut;
   using L = KernelLayout<BM, KS, PS, XS, WB, WT, AFMT, MODE, SB>;
-  constexpr int kAccColumns = PA * L::kTmemColumns;   // two accumulator sets of PA partials
   constexpr int kWColumns = kTileK / 2;                // one decoded K step: 64 x 16 bit per row
+  // Two accumulator sets of PA partials overlap a unit's epilogue with the next unit's MMAs.
+  // Where they do not fit beside the W' tiles in tensor memory (256 activation rows) there is
+  // one set: the MMA warp then waits for the epilogue, while the decode warps run ahead into
+  // the W' ring.
+  constexpr int kAccSets = (WT && PA * L::kTmemColumns + WB * kWColumns > 512) ? 1 : 2;
+  constexpr int kAccColumns = kAccSets * PA * (L::kTmemColumns / 2);
   constexpr int kTmemNeeded = kAccColumns + (WT ? WB * kWColumns : 0);
   constexpr int kTmemColumns = kTmemNeeded <= 32    ? 32
                                : kTmemNeeded <= 64  ? 64
@@ -777,8 +782,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         // After a timeout anywhere in the CTA nothing further is issued: the waits below have
         // become no-ops and the operands would not be ready.
         if (__shfl_sync(0xffffffffu, *abort_flag, 0) != 0) break;
-        const int acc = local & 1;
-        const uint32_t acc_phase = (local >> 1) & 1;
+        const int acc = kAccSets == 2 ? (local & 1) : 0;
+        const uint32_t acc_phase = kAccSets == 2 ? ((local >> 1) & 1) : (local & 1);
         mbar_wait_or_abort(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, p.status,
                            kSiteMmaAccumulator);
         tcgen05_fence_after_sync();
@@ -849,8 +854,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     int local = 0;
     for (int index = first_unit; index < units; index += unit_stride, ++local) {
       const Unit u = get_unit<BM, GROUPED>(p, groups, index);
-      const int acc = local & 1;
-      const uint32_t acc_phase = (local >> 1) & 1;
+      const int acc = kAccSets == 2 ? (local & 1) : 0;
+      const uint32_t acc_phase = kAccSets == 2 ? ((local >> 1) & 1) : (local & 1);
       if (!wait(&tmem_full[acc], acc_phase, kSiteEpilogue)) break;
       tcgen05_fence_after_sync();
       // Grouped modes that address the output by assignment keep the unit's slot -> (assignment,
