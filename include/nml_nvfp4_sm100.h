@@ -168,6 +168,12 @@ typedef struct NmlSm100ExpertDown {
   int32_t dtype;
   const int32_t *active_blocks;
   const int32_t *expert_offset;
+  /* Optional (read when struct_size covers it): [assignments] device pointers; when set, the
+   * result row of assignment a is stored at row_targets[a] (hidden_size values) instead of
+   * weighted + a * hidden_size.  An expert-parallel owner points them into the senders'
+   * return buffers (nml_nvfp4_sm100_ep_receive_meta fills the table), so the projection's
+   * epilogue is also the return trip.  NULL entries are skipped. */
+  void *const *row_targets;
 } NmlSm100ExpertDown;
 
 /* Top-k routing from f32 router logits: softmax over all experts, top-k by
@@ -269,6 +275,10 @@ typedef struct NmlSm100RoutedSwiglu {
    * rows of masked tokens are then left untouched instead of being zeroed.  For callers that
    * never read those rows (an expert-parallel owner returning rows to their senders). */
   int32_t flags;
+  /* Optional, with NML_SM100_ROUTED_LEAVE_MASKED_ROWS and experts_per_token == 1:
+   * [tokens] device pointers, the destination of every token's result row (see
+   * NmlSm100ExpertDown::row_targets); `output` is then not written. */
+  void *const *row_targets;
 } NmlSm100RoutedSwiglu;
 #define NML_SM100_ROUTED_LEAVE_MASKED_ROWS 1
 
@@ -422,11 +432,16 @@ typedef struct NmlSm100EpReceiveMeta {
   void *stream;
   int64_t wait_limit;
   int32_t dtype;
+  /* Optional (read when struct_size covers it): [ranks * region_rows] device pointers, set to
+   * where row i's result goes in its sender's return buffer (NULL where no row arrived). */
+  void **row_targets;
 } NmlSm100EpReceiveMeta;
 
 typedef struct NmlSm100EpReturnRows {
   size_t struct_size;
-  const void *computed;            /* [ranks * region_rows, width] dtype: results in receive order */
+  const void *computed;            /* [ranks * region_rows, width] dtype: results in receive order;
+                                      NULL when the projection stored them through row_targets:
+                                      the call then only publishes the return flags */
   NmlSm100EpExchange exchange;
   void *stream;
   int32_t dtype;

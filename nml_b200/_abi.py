@@ -79,7 +79,7 @@ class ExpertDown(ctypes.Structure):
                 ("schedule_positions", _i64), ("schedule_blocks", _i64),
                 ("intermediate_size", _i64), ("hidden_size", _i64), ("experts", _i64),
                 ("experts_per_token", _i64), ("block_size", _i32), ("dtype", _i32),
-                ("active_blocks", _vp), ("expert_offset", _vp)]
+                ("active_blocks", _vp), ("expert_offset", _vp), ("row_targets", _vp)]
 
 
 class Route(ctypes.Structure):
@@ -111,7 +111,7 @@ class RoutedSwiglu(ctypes.Structure):
                 ("workspace", _vp), ("workspace_bytes", _sz), ("stream", _vp), ("tokens", _i64),
                 ("hidden_size", _i64), ("intermediate_size", _i64), ("experts", _i64),
                 ("experts_per_token", _i64), ("expert_offset", _i32), ("dtype", _i32),
-                ("live_routes_hint", _i64), ("flags", _i32)]
+                ("live_routes_hint", _i64), ("flags", _i32), ("row_targets", _vp)]
 
 
 class EpDispatchPlan(ctypes.Structure):
@@ -181,7 +181,7 @@ class EpPushRows(ctypes.Structure):
 class EpReceiveMeta(ctypes.Structure):
     _fields_ = [("struct_size", _sz), ("exchange", EpExchange), ("expert_ids", _vp),
                 ("routing_weights", _vp), ("received", _vp), ("stream", _vp),
-                ("wait_limit", _i64), ("dtype", _i32)]
+                ("wait_limit", _i64), ("dtype", _i32), ("row_targets", _vp)]
 
 
 class EpReturnRows(ctypes.Structure):

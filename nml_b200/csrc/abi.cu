@@ -506,6 +506,9 @@ extern "C" int32_t nml_nvfp4_sm100_expert_down(const NmlSm100ExpertDown* request
       has_field(request, offsetof(NmlSm100ExpertDown, expert_offset), sizeof(void*))
           ? request->expert_offset
           : nullptr;
+  args.row_targets = has_field(request, offsetof(NmlSm100ExpertDown, row_targets), sizeof(void*))
+                         ? request->row_targets
+                         : nullptr;
   args.stream = static_cast<cudaStream_t>(request->stream);
   args.assignments = static_cast<int>(request->assignments);
   args.schedule_blocks = static_cast<int>(request->schedule_blocks);
@@ -764,7 +767,12 @@ extern "C" int32_t nml_nvfp4_sm100_routed_swiglu(const NmlSm100RoutedSwiglu* req
       request->experts_per_token == 1 &&
       has_field(request, offsetof(NmlSm100RoutedSwiglu, flags), sizeof(int32_t)) &&
       (request->flags & NML_SM100_ROUTED_LEAVE_MASKED_ROWS) != 0;
-  if (rows_are_routes) args.output = request->output;  // assignment a is token a
+  if (rows_are_routes) {
+    args.output = request->output;  // assignment a is token a
+    if (has_field(request, offsetof(NmlSm100RoutedSwiglu, row_targets), sizeof(void*))) {
+      args.row_targets = request->row_targets;
+    }
+  }
   status = dispatch_experts(args, *device, error_message, error_message_capacity);
   if (status != NML_SM100_OK || rows_are_routes) return status;
 
@@ -998,7 +1006,8 @@ extern "C" int32_t nml_nvfp4_sm100_ep_push_rows(const NmlSm100EpPushRows* reques
 extern "C" int32_t nml_nvfp4_sm100_ep_receive_meta(const NmlSm100EpReceiveMeta* request,
                                                    char* error_message,
                                                    size_t error_message_capacity) {
-  if (request == nullptr || request->struct_size < sizeof(NmlSm100EpReceiveMeta)) {
+  if (request == nullptr ||
+      request->struct_size < offsetof(NmlSm100EpReceiveMeta, row_targets)) {
     return fail(NML_SM100_INVALID_ARGUMENT, "truncated NVFP4 receive meta request", error_message,
                 error_message_capacity);
   }
@@ -1020,8 +1029,8 @@ extern "C" int32_t nml_nvfp4_sm100_ep_return_rows(const NmlSm100EpReturnRows* re
     return fail(NML_SM100_INVALID_ARGUMENT, "truncated NVFP4 row return request", error_message,
                 error_message_capacity);
   }
-  if (request->computed == nullptr || request->stream == nullptr ||
-      !valid_exchange(request->exchange) || !valid_dtype(request->dtype) ||
+  if (request->stream == nullptr || !valid_exchange(request->exchange) ||
+      !valid_dtype(request->dtype) ||
       reinterpret_cast<uintptr_t>(request->computed) % 16 != 0) {
     return fail(NML_SM100_INVALID_ARGUMENT, "invalid NVFP4 row return request", error_message,
                 error_message_capacity);

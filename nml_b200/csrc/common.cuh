@@ -189,6 +189,9 @@ struct ExpertArgs {
   bool slot_input = false;
   // Routes expected to be live (kernel selection only); 0: all of `assignments`.
   int live_routes = 0;
+  // Down only: where each assignment's result row goes instead of output + a * outputs (null
+  // entries are skipped); null table: the plain layout.
+  void* const* row_targets = nullptr;
 };
 
 int32_t launch_experts_simt(const ExpertArgs& args, const DeviceInfo& device, char* message,

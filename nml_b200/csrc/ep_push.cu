@@ -183,7 +183,8 @@ ep_push_rows_kernel(const T* __restrict__ source, const int32_t* __restrict__ se
 template <typename T>
 __global__ void __launch_bounds__(256)
 ep_receive_meta_kernel(Exchange x, int32_t* __restrict__ expert_ids, T* __restrict__ weights,
-                       int32_t* __restrict__ received, int64_t wait_limit, int* status) {
+                       int32_t* __restrict__ received, void** __restrict__ row_targets,
+                       int64_t wait_limit, int* status) {
   const int epoch = x.local_state[kEpochWord];
   const int32_t* sync = x.sync[x.rank];
   const unsigned missing = wait_for_epoch(sync + kArrivedWords, x.ranks, epoch, wait_limit, status);
@@ -200,18 +201,28 @@ ep_receive_meta_kernel(Exchange x, int32_t* __restrict__ expert_ids, T* __restri
   const int sender = i / x.region_rows;
   const int position = i - sender * x.region_rows;
   const bool live = !(missing >> sender & 1u) && position < sync[kCountWords + sender];
+  void* target = nullptr;
   if (live) {
     const int4 m = reinterpret_cast<const int4*>(x.meta[x.rank])[i];
     expert_ids[i] = m.x;
     reinterpret_cast<uint16_t*>(weights)[i] = static_cast<uint16_t>(m.y);
+    if (m.z >= 0 && m.z < x.region_rows) {
+      // where this row's result goes: row m.z of the sender's return buffer
+      target = reinterpret_cast<uint4*>(x.back[sender]) + static_cast<int64_t>(m.z) * x.vectors;
+    } else if (row_targets != nullptr) {
+      atomicOr(status, NML_SM100_STATUS_INDEX_RANGE);
+    }
   } else {
     expert_ids[i] = -1;
     reinterpret_cast<uint16_t*>(weights)[i] = 0;
   }
+  if (row_targets != nullptr) row_targets[i] = target;
 }
 
 // One warp per received row: computed[i] of region r goes to row meta[i].z of rank r's return
-// buffer.  The last block raises this rank's return flag on every rank.
+// buffer.  The last block raises this rank's return flag on every rank.  With computed == null
+// the rows were already stored by the kernel before this one (a down projection that wrote
+// through row targets): the launch is a single block that fences and raises the flags.
 template <typename T>
 __global__ void __launch_bounds__(kRowsPerBlock * 32)
 ep_return_rows_kernel(const T* __restrict__ computed, Exchange x, int* status) {
@@ -220,7 +231,8 @@ ep_return_rows_kernel(const T* __restrict__ computed, Exchange x, int* status) {
   const int sender = i / x.region_rows;
   const int position = i - sender * x.region_rows;
   const int32_t* sync = x.sync[x.rank];
-  if (sender < x.ranks && position < min(sync[kCountWords + sender], x.region_rows)) {
+  if (computed != nullptr && sender < x.ranks &&
+      position < min(sync[kCountWords + sender], x.region_rows)) {
     const int4 m = reinterpret_cast<const int4*>(x.meta[x.rank])[i];
     if (m.z < 0 || m.z >= x.region_rows) {
       if (lane == 0) atomicOr(status, NML_SM100_STATUS_INDEX_RANGE);
@@ -298,14 +310,17 @@ int32_t launch_ep_receive_meta(const NmlSm100EpReceiveMeta& q, const DeviceInfo&
   const int64_t rows = q.exchange.ranks * q.exchange.region_rows;
   const unsigned grid = static_cast<unsigned>((rows + 255) / 256);
   const int64_t limit = effective_limit(q.wait_limit);
+  void** targets = q.struct_size >= offsetof(NmlSm100EpReceiveMeta, row_targets) + sizeof(void*)
+                       ? q.row_targets
+                       : nullptr;
   if (q.dtype == NML_SM100_F16) {
     ep_receive_meta_kernel<__half><<<grid, 256, 0, stream>>>(
-        x, q.expert_ids, static_cast<__half*>(q.routing_weights), q.received, limit,
+        x, q.expert_ids, static_cast<__half*>(q.routing_weights), q.received, targets, limit,
         device.status_word);
   } else {
     ep_receive_meta_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
-        x, q.expert_ids, static_cast<__nv_bfloat16*>(q.routing_weights), q.received, limit,
-        device.status_word);
+        x, q.expert_ids, static_cast<__nv_bfloat16*>(q.routing_weights), q.received, targets,
+        limit, device.status_word);
   }
   return launch_result(message, capacity);
 }
@@ -314,8 +329,11 @@ int32_t launch_ep_return_rows(const NmlSm100EpReturnRows& q, const DeviceInfo& d
                               char* message, size_t capacity) {
   const Exchange x = make_exchange(q.exchange);
   cudaStream_t stream = static_cast<cudaStream_t>(q.stream);
-  const unsigned grid = static_cast<unsigned>(
-      (q.exchange.ranks * q.exchange.region_rows + kRowsPerBlock - 1) / kRowsPerBlock);
+  const unsigned grid =
+      q.computed == nullptr
+          ? 1u
+          : static_cast<unsigned>(
+                (q.exchange.ranks * q.exchange.region_rows + kRowsPerBlock - 1) / kRowsPerBlock);
   constexpr int kBlock = kRowsPerBlock * 32;
   if (q.dtype == NML_SM100_F16) {
     ep_return_rows_kernel<__half><<<grid, kBlock, 0, stream>>>(

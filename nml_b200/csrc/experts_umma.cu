@@ -65,6 +65,7 @@ int32_t launch_config(const ExpertArgs& args, const DeviceInfo& device, char* me
   p.active_blocks = args.active_blocks;
   p.expert_offset = args.expert_offset;
   p.routing_weights = args.routing_weights;
+  p.row_targets = args.row_targets;
   p.assignments = args.assignments;
   p.schedule_blocks = args.schedule_blocks;
   p.experts = args.experts;

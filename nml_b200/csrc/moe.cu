@@ -327,6 +327,7 @@ experts_simt_kernel(const T* __restrict__ input, const int32_t* __restrict__ sor
                     const uint8_t* __restrict__ payload, const uint8_t* __restrict__ block_scales,
                     const float* __restrict__ global_scale, const T* __restrict__ bias,
                     const T* __restrict__ routing_weights, T* __restrict__ output,
+                    void* const* __restrict__ row_targets,
                     const int32_t* __restrict__ active_blocks,
                     const int32_t* __restrict__ expert_offset, int assignments, int inputs,
                     int outputs, int experts, int top_k) {
@@ -418,7 +419,10 @@ experts_simt_kernel(const T* __restrict__ input, const int32_t* __restrict__ sor
         const float value =
             (sums[0] + Elem<T>::load(bias[static_cast<int64_t>(expert) * outputs + column])) *
             Elem<T>::load(routing_weights[a]);
-        output[static_cast<int64_t>(a) * outputs + column] = Elem<T>::store(value);
+        T* destination = row_targets != nullptr
+                             ? static_cast<T*>(row_targets[a])
+                             : output + static_cast<int64_t>(a) * outputs;
+        if (destination != nullptr) destination[column] = Elem<T>::store(value);
       }
     }
   }
@@ -437,14 +441,15 @@ int32_t launch_experts_simt_typed(const ExpertArgs& args, char* message, size_t 
     experts_simt_kernel<T, true><<<grid, kExpertWarps * 32, 0, args.stream>>>(
         static_cast<const T*>(args.input), args.sorted_assignments, args.block_experts,
         args.payload, args.block_scales, args.global_scale, static_cast<const T*>(args.bias),
-        nullptr, static_cast<T*>(args.output), args.active_blocks, args.expert_offset,
+        nullptr, static_cast<T*>(args.output), nullptr, args.active_blocks, args.expert_offset,
         args.assignments, args.inputs, args.outputs, args.experts, args.experts_per_token);
   } else {
     experts_simt_kernel<T, false><<<grid, kExpertWarps * 32, 0, args.stream>>>(
         static_cast<const T*>(args.input), args.sorted_assignments, args.block_experts,
         args.payload, args.block_scales, args.global_scale, static_cast<const T*>(args.bias),
         static_cast<const T*>(args.routing_weights), static_cast<T*>(args.output),
-        args.active_blocks, args.expert_offset, args.assignments, args.inputs, args.outputs,
+        args.row_targets, args.active_blocks, args.expert_offset, args.assignments, args.inputs,
+        args.outputs,
         args.experts, args.experts_per_token);
   }
   return launch_result(message, capacity);

@@ -180,6 +180,7 @@ int32_t launch_experts_stream(const ExpertArgs& args, const DeviceInfo& device, 
   p.active_blocks = args.active_blocks;
   p.expert_offset = args.expert_offset;
   p.routing_weights = args.routing_weights;
+  p.row_targets = args.row_targets;
   p.payload = args.payload;
   p.block_scales = args.block_scales;
   p.global_scale = args.global_scale;

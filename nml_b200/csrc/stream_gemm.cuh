@@ -84,6 +84,7 @@ struct Params {
   const int32_t* active_blocks;       // may be null
   const int32_t* expert_offset;       // may be null
   const void* routing_weights;        // down: [A]
+  void* const* row_targets;           // down: optional [A] destinations of the result rows
   const uint8_t* payload;
   const uint8_t* block_scales;
   const float* global_scale;
@@ -581,6 +582,7 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
     // grouped: the assignment (output row) and routing weight of this lane's columns
     int32_t target[2];
     float route_weight[2];
+    T* down_row[2] = {nullptr, nullptr};  // down: where this lane's two result rows go
     for (Walk w = walk_begin(); w.unit < last; walk_next(w)) {
       if constexpr (kGrouped) {
         if (loaded_group != w.group) {
@@ -590,8 +592,16 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
             const bool valid = a >= 0 && a < p.assignments;
             target[i] = valid ? a : -1;
             route_weight[i] = 0.0f;
-            if (MODE == kDown && valid) {
-              route_weight[i] = Elem<T>::load(static_cast<const T*>(p.routing_weights)[a]);
+            if (MODE == kDown) {
+              down_row[i] = nullptr;
+              if (valid) {
+                route_weight[i] = Elem<T>::load(static_cast<const T*>(p.routing_weights)[a]);
+                // row a of the output, or wherever the caller's table sends it (an
+                // expert-parallel owner: the sender's return buffer, over NVLink)
+                down_row[i] = p.row_targets != nullptr
+                                  ? static_cast<T*>(p.row_targets[a])
+                                  : static_cast<T*>(p.output) + static_cast<int64_t>(a) * p.N;
+              }
             }
           }
           loaded_group = w.group;
@@ -692,9 +702,8 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
           } else {
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
-              if (n_ok && target[i] >= 0) {
-                out[static_cast<int64_t>(target[i]) * p.N + n] =
-                    Elem<T>::store(v[i] * route_weight[i]);
+              if (n_ok && down_row[i] != nullptr) {
+                down_row[i][n] = Elem<T>::store(v[i] * route_weight[i]);
               }
             }
           }

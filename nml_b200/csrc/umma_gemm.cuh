@@ -139,6 +139,7 @@ struct Params {
   const int32_t* block_experts;
   const int32_t* active_blocks;
   const int32_t* expert_offset;
+  void* const* row_targets;       // down: optional destination of each assignment's row
   const void* routing_weights;
   int assignments, schedule_blocks, experts, top_k;
   // dense: up to three weights that share the activation operand (fused Q/K/V); a plain
@@ -991,13 +992,30 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
             }
           }
         } else if constexpr (MODE == kDown) {
+          if (p.row_targets == nullptr) {
 #pragma unroll
-          for (int j = 0; j < kChunk; ++j) {
-            const int a = slot_assignment[c + j];
-            if (n_ok && a >= 0) {
-              const float weight = Elem<T>::from_bits(slot_weight[c + j]);
-              out[static_cast<int64_t>(a) * p.N + n] =
-                  Elem<T>::store(fmaf(__uint_as_float(v[j]), g, bias_value) * weight);
+            for (int j = 0; j < kChunk; ++j) {
+              const int a = slot_assignment[c + j];
+              if (n_ok && a >= 0) {
+                const float weight = Elem<T>::from_bits(slot_weight[c + j]);
+                out[static_cast<int64_t>(a) * p.N + n] =
+                    Elem<T>::store(fmaf(__uint_as_float(v[j]), g, bias_value) * weight);
+              }
+            }
+          } else {
+            // the caller's table says where each assignment's row goes (an expert-parallel
+            // owner: straight into the sender's return buffer, over NVLink)
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j) {
+              const int a = slot_assignment[c + j];
+              if (n_ok && a >= 0) {
+                T* destination = static_cast<T*>(p.row_targets[a]);
+                if (destination != nullptr) {
+                  const float weight = Elem<T>::from_bits(slot_weight[c + j]);
+                  destination[n] =
+                      Elem<T>::store(fmaf(__uint_as_float(v[j]), g, bias_value) * weight);
+                }
+              }
             }
           }
         } else {

@@ -100,23 +100,33 @@ class CudaBackend:
             experts_per_token=top_k, dtype=ops._code(hidden.dtype))
         _abi.call("nml_nvfp4_sm100_ep_push_rows", request)
 
-    def receive_meta(self, exchange, dtype, wait_limit=0):
+    def receive_meta(self, exchange, dtype, wait_limit=0, with_targets=False):
+        """Expert ids, routing weights and count of the rows that arrived; with
+        ``with_targets`` also the address of every row's place in its sender's return buffer
+        (the table the down projection stores through)."""
         rows = exchange.ranks * exchange.region_rows
         device = exchange.rows.device
         ids = torch.empty((rows, 1), dtype=torch.int32, device=device)
         weights = torch.empty((rows, 1), dtype=dtype, device=device)
         received = torch.empty(1, dtype=torch.int32, device=device)
+        targets = torch.empty(rows, dtype=torch.int64, device=device) if with_targets else None
         request = _abi.EpReceiveMeta(
             exchange=exchange.descriptor(), expert_ids=ids.data_ptr(),
             routing_weights=weights.data_ptr(), received=received.data_ptr(),
-            stream=ops._stream(ids), wait_limit=wait_limit, dtype=ops._code(dtype))
+            stream=ops._stream(ids), wait_limit=wait_limit, dtype=ops._code(dtype),
+            row_targets=None if targets is None else targets.data_ptr())
         _abi.call("nml_nvfp4_sm100_ep_receive_meta", request)
+        if with_targets:
+            return ids, weights, received, targets
         return ids, weights, received
 
     def return_rows(self, computed, exchange):
-        request = _abi.EpReturnRows(computed=computed.data_ptr(),
-                                    exchange=exchange.descriptor(),
-                                    stream=ops._stream(computed), dtype=ops._code(computed.dtype))
+        """Copies the computed rows to their senders and raises the return flags; with
+        ``computed`` None (rows already stored through row targets) only the flags."""
+        request = _abi.EpReturnRows(
+            computed=None if computed is None else computed.data_ptr(),
+            exchange=exchange.descriptor(), stream=ops._stream(exchange.rows),
+            dtype=ops._code(exchange.rows.dtype))
         _abi.call("nml_nvfp4_sm100_ep_return_rows", request)
 
     def wait_returns(self, exchange, wait_limit=0):
@@ -125,11 +135,11 @@ class CudaBackend:
         _abi.call("nml_nvfp4_sm100_ep_wait_returns", request)
 
     def routed_experts(self, hidden, expert_ids, routing_weights, layer, expert_offset=0,
-                       live_routes=0, leave_masked_rows=False):
+                       live_routes=0, leave_masked_rows=False, row_targets=None):
         return ops.routed_experts(hidden, expert_ids, routing_weights, layer.gate_up,
                                   layer.gate_up_bias, layer.down, layer.down_bias,
                                   expert_offset=expert_offset, live_routes=live_routes,
-                                  leave_masked_rows=leave_masked_rows)
+                                  leave_masked_rows=leave_masked_rows, row_targets=row_targets)
 
     def linear(self, hidden, weight, bias=None):
         return ops.linear(hidden, weight, bias)
@@ -258,7 +268,7 @@ class ExpertParallelMoE:
 
     def __init__(self, layer: LocalExperts, experts_per_token: int, group=None,
                  schedule: str = "alltoall", backend=None, exchange: PeerExchange | None = None,
-                 wait_limit: int = 0):
+                 wait_limit: int = 0, fused_return: bool = True):
         if schedule not in ("alltoall", "allreduce", "push"):
             raise ValueError("schedule must be 'alltoall', 'push' or 'allreduce'")
         # push schedule: mapped buffers, shared between layers when passed in, else allocated
@@ -266,6 +276,9 @@ class ExpertParallelMoE:
         # collective, done only after every rank has drained its stream)
         self.exchange = exchange
         self.wait_limit = wait_limit
+        # push schedule: the down projection stores its rows into the senders' return buffers
+        # itself (False: a separate copy kernel after the layer)
+        self.fused_return = fused_return
         self.layer = layer
         self.top_k = experts_per_token
         self.group = group
@@ -347,11 +360,22 @@ class ExpertParallelMoE:
         order, local_expert, slot_of, counts = backend.dispatch_plan(
             ids.reshape(-1), self.world, self.layer.experts_local)
         backend.push_rows(hidden, order, local_expert, weights.reshape(-1), counts, exchange, k)
-        recv_ids, recv_weights, _ = backend.receive_meta(exchange, hidden.dtype, self.wait_limit)
         # of the world * region_rows rows an owner's buffer holds, about `assignments` are live
-        computed = backend.routed_experts(exchange.rows, recv_ids, recv_weights, self.layer,
-                                          live_routes=assignments, leave_masked_rows=True)
-        backend.return_rows(computed, exchange)
+        if self.fused_return:
+            # the down projection's epilogue stores every result row straight into its
+            # sender's return buffer; what is left of the return trip is raising the flags
+            recv_ids, recv_weights, _, targets = backend.receive_meta(
+                exchange, hidden.dtype, self.wait_limit, with_targets=True)
+            backend.routed_experts(exchange.rows, recv_ids, recv_weights, self.layer,
+                                   live_routes=assignments, leave_masked_rows=True,
+                                   row_targets=targets)
+            backend.return_rows(None, exchange)
+        else:
+            recv_ids, recv_weights, _ = backend.receive_meta(exchange, hidden.dtype,
+                                                             self.wait_limit)
+            computed = backend.routed_experts(exchange.rows, recv_ids, recv_weights, self.layer,
+                                              live_routes=assignments, leave_masked_rows=True)
+            backend.return_rows(computed, exchange)
         backend.wait_returns(exchange, self.wait_limit)
         return backend.combine_rows(exchange.back, slot_of, tokens, k)
 

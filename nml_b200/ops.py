@@ -370,14 +370,18 @@ def routed_experts(hidden: torch.Tensor, expert_ids: torch.Tensor,
                    gate_up_bias: torch.Tensor, down: NvFp4Parameter, down_bias: torch.Tensor,
                    expert_offset: int = 0, out: torch.Tensor | None = None,
                    workspace: torch.Tensor | None = None, live_routes: int = 0,
-                   leave_masked_rows: bool = False) -> torch.Tensor:
+                   leave_masked_rows: bool = False,
+                   row_targets: torch.Tensor | None = None) -> torch.Tensor:
     """The routed layer from given routes, one C-ABI call (plan, gate/up + SwiGLU, down,
     k-way sum); the unit of the reference's CPU target ``nml.nvfp4.routed_swiglu``
     (crates/nml-kernel-nvfp4/src/ffi.rs:228-428).  ``workspace`` (u8, 256-byte aligned, at
     least ``nml_nvfp4_sm100_routed_swiglu_workspace_bytes``) replaces the cached scratch
     buffer, e.g. to inspect the intermediates afterwards.  ``live_routes`` (optional) tells
     the kernel selection how many routes are expected not to be masked.  ``leave_masked_rows``
-    (one route per token only) skips the k-way sum pass: rows of masked tokens stay untouched."""
+    (one route per token only) skips the k-way sum pass: rows of masked tokens stay untouched;
+    with it, ``row_targets`` (I64 ``[tokens]`` device addresses, 0 to skip a row) sends every
+    token's result row to its address instead of ``out`` (an expert-parallel owner: into the
+    senders' return buffers)."""
     if hidden.dim() != 2 or expert_ids.dim() != 2 or \
             tuple(routing_weights.shape) != tuple(expert_ids.shape) or \
             expert_ids.shape[0] != hidden.shape[0]:
@@ -403,8 +407,15 @@ def routed_experts(hidden: torch.Tensor, expert_ids: torch.Tensor,
     elif workspace.dtype != torch.uint8 or workspace.numel() < size or not workspace.is_cuda:
         raise ValueError("the routed-layer workspace must be a device U8 buffer of at least "
                          f"{size} bytes")
+    if row_targets is not None:
+        if not (leave_masked_rows and top_k == 1):
+            raise ValueError("row targets need one route per token and leave_masked_rows")
+        if row_targets.dtype != torch.int64 or tuple(row_targets.shape) != (tokens,) or \
+                not row_targets.is_contiguous():
+            raise ValueError("row targets must be I64 [tokens] device addresses")
+        _require_cuda(row_targets)
     if out is None:
-        out = torch.empty_like(hidden)
+        out = torch.empty_like(hidden) if row_targets is None else hidden  # not written
     request = _abi.RoutedSwiglu(
         hidden=_ptr(hidden), expert_ids=_ptr(expert_ids), routing_weights=_ptr(routing_weights),
         gate_payload=_ptr(gate_up.payload), gate_scales=_ptr(gate_up.block_scales),
@@ -415,7 +426,8 @@ def routed_experts(hidden: torch.Tensor, expert_ids: torch.Tensor,
         tokens=tokens, hidden_size=hidden_size, intermediate_size=intermediate, experts=experts,
         experts_per_token=top_k, expert_offset=expert_offset, dtype=_code(hidden.dtype),
         live_routes_hint=live_routes,
-        flags=_abi.ROUTED_LEAVE_MASKED_ROWS if leave_masked_rows and top_k == 1 else 0)
+        flags=_abi.ROUTED_LEAVE_MASKED_ROWS if leave_masked_rows and top_k == 1 else 0,
+        row_targets=_ptr(row_targets))
     _abi.call("nml_nvfp4_sm100_routed_swiglu", request)
     return out
 

@@ -74,14 +74,18 @@ def test_dispatch_plan_gather_and_combine_kernels_against_numpy():
         tensor_to_bits(reference.combine_rows(rows, slot, tokens, k)))
 
 
+@pytest.mark.parametrize("fused_return", [True, False])
 @pytest.mark.parametrize("ranks,experts,tokens", [(2, 8, 96), (4, 8, 40), (8, 32, 64),
                                                   (8, 8, 512)])
-def test_push_schedule_with_several_ranks_emulated_on_one_device(ranks, experts, tokens):
+def test_push_schedule_with_several_ranks_emulated_on_one_device(ranks, experts, tokens,
+                                                                 fused_return):
     # No kernel of the peer-push schedule waits for a flag that an earlier launch has not
     # raised when the stages are replayed stage by stage over all ranks, so G ranks can run on
     # one device with every "peer" buffer local.  This exercises the whole protocol (regions,
     # counts, arrival and return flags, epochs over two consecutive layers) and compares every
-    # rank's output with the oracle's evaluation of the layer.
+    # rank's output with the oracle's evaluation of the layer.  With `fused_return` the down
+    # projection stores its rows into the senders' return buffers itself (through the row
+    # targets that receive_meta fills) and return_rows only raises the flags.
     from ep_common import OracleBackend, build_problem, tensor_to_bits
     from nml_b200 import _abi, expert_parallel as ep
     import gpu_util as gu
@@ -105,11 +109,21 @@ def test_push_schedule_with_several_ranks_emulated_on_one_device(ranks, experts,
             plans.append((ids, weights, slot_of))
         computed = []
         for r in range(ranks):
-            recv_ids, recv_weights, received = backend.receive_meta(exchanges[r], torch.bfloat16)
+            if fused_return:
+                recv_ids, recv_weights, received, targets = backend.receive_meta(
+                    exchanges[r], torch.bfloat16, with_targets=True)
+                assert int((targets != 0).sum().item()) == int(received.item())
+                backend.routed_experts(exchanges[r].rows, recv_ids, recv_weights, layers[r],
+                                       live_routes=per_rank * k, leave_masked_rows=True,
+                                       row_targets=targets)
+                computed.append(None)
+            else:
+                recv_ids, recv_weights, received = backend.receive_meta(exchanges[r],
+                                                                        torch.bfloat16)
+                computed.append(backend.routed_experts(exchanges[r].rows, recv_ids, recv_weights,
+                                                       layers[r], live_routes=per_rank * k,
+                                                       leave_masked_rows=True))
             assert int(received.item()) == int((recv_ids >= 0).sum().item())
-            computed.append(backend.routed_experts(exchanges[r].rows, recv_ids, recv_weights,
-                                                   layers[r], live_routes=per_rank * k,
-                                                   leave_masked_rows=True))
         for r in range(ranks):
             backend.return_rows(computed[r], exchanges[r])
         for r in range(ranks):
