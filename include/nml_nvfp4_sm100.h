@@ -452,6 +452,14 @@ typedef struct NmlSm100EpWaitReturns {
   NmlSm100EpExchange exchange;
   void *stream;
   int64_t wait_limit;
+  /* Optional (read when struct_size covers them; output != NULL): do the combine over this
+   * rank's return buffer in the same launch, every block after its own wait:
+   * output[t, :] = sum over routes of back[row_index[t * experts_per_token + route], :]. */
+  const int32_t *row_index;        /* [tokens * experts_per_token], -1 = no row */
+  void *output;                    /* [tokens, width] dtype */
+  int64_t tokens;
+  int64_t experts_per_token;
+  int32_t dtype;
 } NmlSm100EpWaitReturns;
 
 int32_t nml_nvfp4_sm100_ep_push_rows(const NmlSm100EpPushRows *request, char *error_message,

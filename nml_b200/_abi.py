@@ -191,7 +191,8 @@ class EpReturnRows(ctypes.Structure):
 
 class EpWaitReturns(ctypes.Structure):
     _fields_ = [("struct_size", _sz), ("exchange", EpExchange), ("stream", _vp),
-                ("wait_limit", _i64)]
+                ("wait_limit", _i64), ("row_index", _vp), ("output", _vp), ("tokens", _i64),
+                ("experts_per_token", _i64), ("dtype", _i32)]
 
 
 # name -> request structure, for the entry points of the form fn(const Request*, char*, size_t)

@@ -1043,7 +1043,8 @@ extern "C" int32_t nml_nvfp4_sm100_ep_return_rows(const NmlSm100EpReturnRows* re
 extern "C" int32_t nml_nvfp4_sm100_ep_wait_returns(const NmlSm100EpWaitReturns* request,
                                                    char* error_message,
                                                    size_t error_message_capacity) {
-  if (request == nullptr || request->struct_size < sizeof(NmlSm100EpWaitReturns)) {
+  if (request == nullptr ||
+      request->struct_size < offsetof(NmlSm100EpWaitReturns, row_index)) {
     return fail(NML_SM100_INVALID_ARGUMENT, "truncated NVFP4 return wait request", error_message,
                 error_message_capacity);
   }
@@ -1051,6 +1052,14 @@ extern "C" int32_t nml_nvfp4_sm100_ep_wait_returns(const NmlSm100EpWaitReturns* 
       !valid_exchange(request->exchange)) {
     return fail(NML_SM100_INVALID_ARGUMENT, "invalid NVFP4 return wait request", error_message,
                 error_message_capacity);
+  }
+  if (request->struct_size >= sizeof(NmlSm100EpWaitReturns) && request->output != nullptr &&
+      (request->row_index == nullptr || request->tokens <= 0 || !fits_i32(request->tokens) ||
+       request->experts_per_token <= 0 || !fits_i32(request->experts_per_token) ||
+       !valid_dtype(request->dtype) ||
+       reinterpret_cast<uintptr_t>(request->output) % 16 != 0)) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "invalid NVFP4 return combine request",
+                error_message, error_message_capacity);
   }
   const DeviceInfo* device = current_device(error_message, error_message_capacity);
   if (device == nullptr) return NML_SM100_LAUNCH_FAILURE;

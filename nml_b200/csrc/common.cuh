@@ -104,6 +104,37 @@ __device__ __forceinline__ T narrow_with_residual(float value, const T* residual
   return Elem<T>::store(Elem<T>::load(narrowed) + Elem<T>::load(residual[index]));
 }
 
+// One 16-byte item of an indexed k-way sum: output[token, vector] = sum over routes, in route
+// order, of rows[row_index[token * k + route], vector] (f32, one narrowing); routes with an
+// index outside [0, row_count) are skipped.
+template <typename T>
+__device__ __forceinline__ void combine_rows_item(const T* __restrict__ rows,
+                                                  const int32_t* __restrict__ row_index,
+                                                  T* __restrict__ output, int64_t item,
+                                                  int top_k, int vectors, int64_t row_count) {
+  const int token = static_cast<int>(item / vectors);
+  const int vector = static_cast<int>(item - static_cast<int64_t>(token) * vectors);
+  float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int route = 0; route < top_k; ++route) {
+    const int32_t index = row_index[static_cast<int64_t>(token) * top_k + route];
+    if (index < 0 || index >= row_count) continue;
+    const uint4 v =
+        reinterpret_cast<const uint4*>(rows)[static_cast<int64_t>(index) * vectors + vector];
+    const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      sum[2 * i] += Elem<T>::from_bits(words[i] & 0xffffu);
+      sum[2 * i + 1] += Elem<T>::from_bits(words[i] >> 16);
+    }
+  }
+  uint4 out;
+  out.x = Elem<T>::pack2(sum[0], sum[1]);
+  out.y = Elem<T>::pack2(sum[2], sum[3]);
+  out.z = Elem<T>::pack2(sum[4], sum[5]);
+  out.w = Elem<T>::pack2(sum[6], sum[7]);
+  reinterpret_cast<uint4*>(output)[item] = out;
+}
+
 // Clamped residual SwiGLU of the routed experts (crates/nml-kernel-nvfp4/src/lib.rs:424-429):
 // gate clamps above 7, up clamps to [-7, 7], result (up + 1) * gate * sigmoid(1.702 * gate).
 __device__ __forceinline__ float clamped_swiglu(float gate, float up) {

@@ -116,26 +116,7 @@ combine_rows_kernel(const T* __restrict__ rows, const int32_t* __restrict__ row_
                     int64_t row_count) {
   const int64_t item = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (item >= static_cast<int64_t>(tokens) * vectors) return;
-  const int token = static_cast<int>(item / vectors);
-  const int vector = static_cast<int>(item - static_cast<int64_t>(token) * vectors);
-  float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  for (int route = 0; route < top_k; ++route) {
-    const int32_t index = row_index[static_cast<int64_t>(token) * top_k + route];
-    if (index < 0 || index >= row_count) continue;
-    const uint4 v = reinterpret_cast<const uint4*>(rows)[static_cast<int64_t>(index) * vectors + vector];
-    const uint32_t words[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      sum[2 * i] += Elem<T>::from_bits(words[i] & 0xffffu);
-      sum[2 * i + 1] += Elem<T>::from_bits(words[i] >> 16);
-    }
-  }
-  uint4 out;
-  out.x = Elem<T>::pack2(sum[0], sum[1]);
-  out.y = Elem<T>::pack2(sum[2], sum[3]);
-  out.z = Elem<T>::pack2(sum[4], sum[5]);
-  out.w = Elem<T>::pack2(sum[6], sum[7]);
-  reinterpret_cast<uint4*>(output)[item] = out;
+  combine_rows_item<T>(rows, row_index, output, item, top_k, vectors, row_count);
 }
 
 }  // namespace

@@ -78,6 +78,27 @@ __device__ __forceinline__ int32_t load_acquire_system(const int32_t* address) {
   return value;
 }
 
+// A warp copies one row of `vectors` 16-byte words.  The loads of a pass are issued before its
+// stores so that up to eight are in flight per lane: a row is a few hundred words, and a
+// load-store loop would pay the memory latency once per 32 of them.
+__device__ __forceinline__ void copy_row(uint4* __restrict__ to, const uint4* __restrict__ from,
+                                         int vectors, int lane) {
+  constexpr int kInFlight = 8;
+  for (int base = lane; base < vectors; base += 32 * kInFlight) {
+    uint4 held[kInFlight];
+#pragma unroll
+    for (int j = 0; j < kInFlight; ++j) {
+      const int v = base + 32 * j;
+      if (v < vectors) held[j] = from[v];
+    }
+#pragma unroll
+    for (int j = 0; j < kInFlight; ++j) {
+      const int v = base + 32 * j;
+      if (v < vectors) to[v] = held[j];
+    }
+  }
+}
+
 // Counts this block on `counter`; true in exactly one block, the one that counted last, and
 // only after every other block's earlier stores are ordered before whatever it does next.
 __device__ __forceinline__ bool last_block_done(int32_t* counter) {
@@ -153,7 +174,7 @@ ep_push_rows_kernel(const T* __restrict__ source, const int32_t* __restrict__ se
       const uint4* from = reinterpret_cast<const uint4*>(source) +
                           static_cast<int64_t>(source_row) * x.vectors;
       uint4* to = reinterpret_cast<uint4*>(x.rows[destination]) + row * x.vectors;
-      for (int v = lane; v < x.vectors; v += 32) to[v] = from[v];
+      copy_row(to, from, x.vectors, lane);
       if (lane == 0) {
         int4 meta;
         meta.x = local_expert[slot];
@@ -222,7 +243,8 @@ ep_receive_meta_kernel(Exchange x, int32_t* __restrict__ expert_ids, T* __restri
 // One warp per received row: computed[i] of region r goes to row meta[i].z of rank r's return
 // buffer.  The last block raises this rank's return flag on every rank.  With computed == null
 // the rows were already stored by the kernel before this one (a down projection that wrote
-// through row targets): the launch is a single block that fences and raises the flags.
+// through row targets and whose writers fenced their stores at system scope): the launch is a
+// single block that raises the flags.
 template <typename T>
 __global__ void __launch_bounds__(kRowsPerBlock * 32)
 ep_return_rows_kernel(const T* __restrict__ computed, Exchange x, int* status) {
@@ -241,7 +263,7 @@ ep_return_rows_kernel(const T* __restrict__ computed, Exchange x, int* status) {
                           static_cast<int64_t>(i) * x.vectors;
       uint4* to = reinterpret_cast<uint4*>(x.back[sender]) +
                   static_cast<int64_t>(m.z) * x.vectors;
-      for (int v = lane; v < x.vectors; v += 32) to[v] = from[v];
+      copy_row(to, from, x.vectors, lane);
     }
   }
   if (last_block_done(x.local_state + kReturnDoneWord)) {
@@ -257,6 +279,21 @@ __global__ void __launch_bounds__(32)
 ep_wait_returns_kernel(Exchange x, int64_t wait_limit, int* status) {
   const int epoch = x.local_state[kEpochWord];
   wait_for_epoch(x.sync[x.rank] + kReturnedWords, x.ranks, epoch, wait_limit, status);
+}
+
+// The same wait in every block of the combine over this rank's return buffer: the k-way sum of
+// a token's rows starts as soon as the owners' flags are in, without a launch in between.
+template <typename T>
+__global__ void __launch_bounds__(256)
+ep_combine_returns_kernel(Exchange x, const int32_t* __restrict__ row_index,
+                          T* __restrict__ output, int tokens, int top_k, int64_t wait_limit,
+                          int* status) {
+  const int epoch = x.local_state[kEpochWord];
+  wait_for_epoch(x.sync[x.rank] + kReturnedWords, x.ranks, epoch, wait_limit, status);
+  const int64_t item = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (item >= static_cast<int64_t>(tokens) * x.vectors) return;
+  combine_rows_item<T>(static_cast<const T*>(x.back[x.rank]), row_index, output, item, top_k,
+                       x.vectors, x.region_rows);
 }
 
 int64_t effective_limit(int64_t requested) {
@@ -348,8 +385,27 @@ int32_t launch_ep_return_rows(const NmlSm100EpReturnRows& q, const DeviceInfo& d
 int32_t launch_ep_wait_returns(const NmlSm100EpWaitReturns& q, const DeviceInfo& device,
                                char* message, size_t capacity) {
   const Exchange x = make_exchange(q.exchange);
-  ep_wait_returns_kernel<<<1, 32, 0, static_cast<cudaStream_t>(q.stream)>>>(
-      x, effective_limit(q.wait_limit), device.status_word);
+  cudaStream_t stream = static_cast<cudaStream_t>(q.stream);
+  const bool combine = q.struct_size >= offsetof(NmlSm100EpWaitReturns, dtype) + sizeof(int32_t) &&
+                       q.output != nullptr;
+  if (!combine) {
+    ep_wait_returns_kernel<<<1, 32, 0, stream>>>(x, effective_limit(q.wait_limit),
+                                                 device.status_word);
+    return launch_result(message, capacity);
+  }
+  const int64_t items = q.tokens * x.vectors;
+  const unsigned grid = static_cast<unsigned>((items + 255) / 256);
+  if (q.dtype == NML_SM100_F16) {
+    ep_combine_returns_kernel<__half><<<grid, 256, 0, stream>>>(
+        x, q.row_index, static_cast<__half*>(q.output), static_cast<int>(q.tokens),
+        static_cast<int>(q.experts_per_token), effective_limit(q.wait_limit),
+        device.status_word);
+  } else {
+    ep_combine_returns_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
+        x, q.row_index, static_cast<__nv_bfloat16*>(q.output), static_cast<int>(q.tokens),
+        static_cast<int>(q.experts_per_token), effective_limit(q.wait_limit),
+        device.status_word);
+  }
   return launch_result(message, capacity);
 }
 

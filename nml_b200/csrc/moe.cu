@@ -423,6 +423,9 @@ experts_simt_kernel(const T* __restrict__ input, const int32_t* __restrict__ sor
                              ? static_cast<T*>(row_targets[a])
                              : output + static_cast<int64_t>(a) * outputs;
         if (destination != nullptr) destination[column] = Elem<T>::store(value);
+        // a destination in another GPU's memory is announced by a later launch: the writer
+        // orders its own store at system scope
+        if (row_targets != nullptr) __threadfence_system();
       }
     }
   }

@@ -711,6 +711,11 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
       }
       }  // rt
     }
+    if constexpr (MODE == kDown) {
+      // stores through the caller's table may go to another GPU, whose flag a later launch
+      // raises: each writer orders its own stores at system scope before the kernel ends
+      if (p.row_targets != nullptr) __threadfence_system();
+    }
   }
   __syncthreads();
 }

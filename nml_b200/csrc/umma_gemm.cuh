@@ -1058,6 +1058,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         }
       }
     }
+    if constexpr (MODE == kDown) {
+      // Rows stored through the caller's table may sit in another GPU's memory, and the flag
+      // that announces them is raised by a later launch: every writer orders its own stores
+      // at system scope before the kernel ends (a fence by another thread, or the end of the
+      // grid, does not wait for posted peer writes).
+      if (p.row_targets != nullptr) __threadfence_system();
+    }
   } else if (warp < kGatherWarp0) {
     // -------------------------------------------------------------------- decode
     const int dt = threadIdx.x - kDecodeWarp0 * 32;

@@ -127,8 +127,11 @@ def test_push_schedule_with_several_ranks_emulated_on_one_device(ranks, experts,
         for r in range(ranks):
             backend.return_rows(computed[r], exchanges[r])
         for r in range(ranks):
-            backend.wait_returns(exchanges[r])
-            outputs.append(backend.combine_rows(exchanges[r].back, plans[r][2], per_rank, k))
+            if fused_return:  # the wait folded into the combine launch
+                outputs.append(backend.combine_returns(exchanges[r], plans[r][2], per_rank, k))
+            else:
+                backend.wait_returns(exchanges[r])
+                outputs.append(backend.combine_rows(exchanges[r].back, plans[r][2], per_rank, k))
         torch.cuda.synchronize()
         assert _abi.device_status(0x1) == 0
         total = sum(int((p[0] >= 0).sum().item()) for p in plans)
