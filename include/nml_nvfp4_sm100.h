@@ -384,7 +384,11 @@ int32_t nml_nvfp4_sm100_routed_swiglu(const NmlSm100RoutedSwiglu *request, char 
  * (waits for every rank's arrival flag, then writes the expert ids and routing weights of the
  * received rows); the routed layer over the receive buffer (k = 1); ep_return_rows (stores
  * result rows into the senders' return buffers, then raises the return flag);
- * ep_wait_returns; combine_rows over the return buffer.
+ * ep_wait_returns; combine_rows over the return buffer.  Optional fusions: with the
+ * row_targets that ep_receive_meta fills, the routed layer's down projection stores its rows
+ * into the senders' return buffers itself (its writers fence at system scope) and
+ * ep_return_rows without `computed` only raises the flag; ep_wait_returns with its combine
+ * fields does the k-way sum in the same launch.
  *
  * Every rank's receive buffer holds one region of `region_rows` rows per sender; sender r
  * writes its rows for a destination into region r in its send order, so placement needs no
