@@ -14,10 +14,12 @@
 // [16 tokens x 8 query heads of the group] = K_page [16 x 64] . Q_group^T, four
 // mma.sync.m16n8k16 with the page's keys loaded straight into A fragments (16-byte loads; the
 // K index order inside an instruction is free as long as Q uses the same order).  Softmax is
-// online per warp (running maximum and sum per head), probabilities pass through a 512-byte
-// shared-memory tile, and P.V runs on FMA lanes: lane l owns dimensions 2l and 2l + 1 of all
-// eight heads.  Warps merge in shared memory, splits through a caller-provided f32 scratch
-// that a second small kernel reduces (applying the sink) into the 16-bit output.
+// online per warp (running maximum and sum per head); the probabilities, narrowed to the
+// cache's 16-bit type, pass through a small shared-memory tile into B fragments, and P.V is
+// four more mma.sync: out^T [64 dimensions x 8 heads] += V_page^T [64 x 16] . P [16 x 8], the
+// value page staged in shared memory by cp.async one page ahead and read transposed with
+// ldmatrix.  Warps merge in shared memory, splits through a caller-provided f32 scratch that a
+// second small kernel reduces (applying the sink) into the 16-bit output.
 #include <type_traits>
 
 #include "common.cuh"
@@ -66,16 +68,45 @@ struct DecodeParams {
 // partial layout per (batch, kv head, split, head of the group)
 constexpr int kPartialWidth = kHeadDim + 2;
 
+// Four 8x8 16-bit matrices from shared memory, transposed: with the rows of a value tile
+// [token][dimension] as matrix rows, lane (g, c) receives (V[2c][g], V[2c + 1][g]) of each
+// matrix, which is the A fragment of mma.sync for a [dimension x token] operand.
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* row_address) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(row_address))));
+}
+
+// 16-byte asynchronous copy into shared memory; zeros instead when `valid` is false.
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool valid) {
+  const uint32_t size = valid ? 16u : 0u;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
+                   static_cast<uint32_t>(__cvta_generic_to_shared(dst))),
+               "l"(src), "r"(size)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+constexpr int kValueStride = kHeadDim + 8;  // elements per token row of a staged value page
+constexpr int kProbabilityStride = 24;      // 16 tokens + padding: conflict-free fragment reads
+
 template <typename T>
 __global__ void __launch_bounds__(kWarps * 32)
 attention_decode_kernel(const DecodeParams p) {
+  constexpr bool kHalf = std::is_same<T, __half>::value;
   const int head = blockIdx.x;   // kv head
   const int b = blockIdx.y;
   const int split = blockIdx.z;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
-  __shared__ float probability[kWarps][kPage][kGroup];          // per warp: one page of P
+  // per warp: two staged value pages and one page of probabilities [head][token] (16 bit)
+  __shared__ __align__(16) T values[kWarps][2][kPage][kValueStride];
+  __shared__ __align__(16) T probability[kWarps][kGroup][kProbabilityStride];
   __shared__ float merged[kWarps][kGroup][kPartialWidth];       // per warp results
 
   const int length = p.lengths[b];
@@ -98,38 +129,66 @@ attention_decode_kernel(const DecodeParams p) {
     q[0][0] = lo.x; q[0][1] = lo.y; q[1][0] = lo.z; q[1][1] = lo.w;
     q[2][0] = hi.x; q[2][1] = hi.y; q[3][0] = hi.z; q[3][1] = hi.w;
   }
-  // running state: this lane keeps heads 2 c and 2 c + 1 statistics (replicated over g) and
-  // the output of dimensions 2 lane, 2 lane + 1 for all eight heads
+  // Running state of this lane: statistics of heads 2 c and 2 c + 1 (replicated over g), and
+  // the output as mma.sync accumulators [dimension x head]: block i holds dimensions
+  // 16 i + g (registers 0, 1) and 16 i + g + 8 (registers 2, 3) of heads 2 c and 2 c + 1.
   float running_max[2] = {-INFINITY, -INFINITY};
   float running_sum[2] = {0.0f, 0.0f};
-  float out[kGroup][2];
+  float out[4][4];
 #pragma unroll
-  for (int h = 0; h < kGroup; ++h) out[h][0] = out[h][1] = 0.0f;
+  for (int i = 0; i < 4; ++i) out[i][0] = out[i][1] = out[i][2] = out[i][3] = 0.0f;
 
   const int64_t token_stride = static_cast<int64_t>(p.kv_heads) * kHeadDim;  // elements
-  for (int page = page_begin + warp; page < page_end; page += kWarps) {
+  // physical page of a logical one; a bad entry is reported and replaced by page 0, whose
+  // scores are then computed like any other (the table is the caller's to keep valid)
+  auto page_base_of = [&](int page) -> int64_t {
     int32_t physical = p.page_table[static_cast<int64_t>(b) * p.table_width + page];
     if (physical < 0 || physical >= p.physical_pages) {
       if (lane == 0) atomicOr(p.status, NML_SM100_STATUS_INDEX_RANGE);
-      physical = 0;  // the page still reads valid memory; its scores are masked below
+      physical = 0;
     }
-    const int64_t page_base = (static_cast<int64_t>(physical) * kPage) * token_stride +
-                              static_cast<int64_t>(head) * kHeadDim;
+    return (static_cast<int64_t>(physical) * kPage) * token_stride +
+           static_cast<int64_t>(head) * kHeadDim;
+  };
+  // Stage the values of a page: 16 token rows of 128 bytes, four 16-byte pieces per lane.
+  // Rows of tokens outside the visible range become zeros: their probabilities are zero, but
+  // whatever an unwritten cache slot holds (a NaN pattern, say) must not meet the product.
+  auto stage_values = [&](int buffer, int logical_page, int64_t page_base) {
+    const T* value = static_cast<const T*>(p.value_cache) + page_base;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int piece = lane + 32 * i;
+      const int token = piece >> 3, part = piece & 7;
+      const int position = logical_page * kPage + token;
+      cp_async_16(&values[warp][buffer][token][8 * part], value + token * token_stride + 8 * part,
+                  position >= first_token && position < length);
+    }
+    cp_async_commit();
+  };
+
+  int buffer = 0;
+  int page = page_begin + warp;
+  int64_t page_base = 0;
+  if (page < page_end) {
+    page_base = page_base_of(page);
+    stage_values(0, page, page_base);
+  }
+  for (; page < page_end; page += kWarps, buffer ^= 1) {
     // keys of tokens g and g + 8, dimensions 16 c .. 16 c + 15
     const T* key = static_cast<const T*>(p.key_cache) + page_base + 16 * c;
     const uint4 k_lo_g = *reinterpret_cast<const uint4*>(key + g * token_stride);
     const uint4 k_hi_g = *reinterpret_cast<const uint4*>(key + g * token_stride + 8);
     const uint4 k_lo_h = *reinterpret_cast<const uint4*>(key + (g + 8) * token_stride);
     const uint4 k_hi_h = *reinterpret_cast<const uint4*>(key + (g + 8) * token_stride + 8);
-    // values: lane owns dimensions 2 lane, 2 lane + 1 of every token of the page
-    const T* value = static_cast<const T*>(p.value_cache) + page_base + 2 * lane;
-    uint32_t v[kPage];
-#pragma unroll
-    for (int t = 0; t < kPage; ++t) {
-      v[t] = *reinterpret_cast<const uint32_t*>(value + t * token_stride);
+    // the next page's values start moving before this page is worked on
+    const int next = page + kWarps;
+    int64_t next_base = 0;
+    if (next < page_end) {
+      next_base = page_base_of(next);
+      stage_values(buffer ^ 1, next, next_base);
     }
     float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // tokens g (s0, s1) and g + 8 (s2, s3), heads 2c, 2c+1
-    if constexpr (std::is_same<T, __half>::value) {
+    if constexpr (kHalf) {
       mma_f16(s, k_lo_g.x, k_lo_h.x, k_lo_g.y, k_lo_h.y, q[0][0], q[0][1]);
       mma_f16(s, k_lo_g.z, k_lo_h.z, k_lo_g.w, k_lo_h.w, q[1][0], q[1][1]);
       mma_f16(s, k_hi_g.x, k_hi_h.x, k_hi_g.y, k_hi_h.y, q[2][0], q[2][1]);
@@ -164,9 +223,12 @@ attention_decode_kernel(const DecodeParams p) {
     }
     const float base0 = new_max[0] == -INFINITY ? 0.0f : new_max[0];
     const float base1 = new_max[1] == -INFINITY ? 0.0f : new_max[1];
-    const float p0 = exp2f(s[0] - base0), p1 = exp2f(s[1] - base1);
-    const float p2 = exp2f(s[2] - base0), p3 = exp2f(s[3] - base1);
-    float page_sum[2] = {p0 + p2, p1 + p3};
+    // probabilities are narrowed to the cache's 16-bit type for the second product; the
+    // running sum adds the narrowed values, so numerator and denominator stay consistent
+    const T n0 = Elem<T>::store(exp2f(s[0] - base0)), n1 = Elem<T>::store(exp2f(s[1] - base1));
+    const T n2 = Elem<T>::store(exp2f(s[2] - base0)), n3 = Elem<T>::store(exp2f(s[3] - base1));
+    float page_sum[2] = {Elem<T>::load(n0) + Elem<T>::load(n2),
+                         Elem<T>::load(n1) + Elem<T>::load(n3)};
 #pragma unroll
     for (int offset = 4; offset < 32; offset <<= 1) {
       page_sum[0] += __shfl_xor_sync(0xffffffffu, page_sum[0], offset);
@@ -177,43 +239,47 @@ attention_decode_kernel(const DecodeParams p) {
       running_sum[i] = running_sum[i] * rescale[i] + page_sum[i];
       running_max[i] = new_max[i];
     }
-    __syncwarp();
-    probability[warp][g][2 * c] = p0;
-    probability[warp][g][2 * c + 1] = p1;
-    probability[warp][g + 8][2 * c] = p2;
-    probability[warp][g + 8][2 * c + 1] = p3;
-    // every lane needs the rescale factors of all eight heads: head h lives in lanes c = h / 2
-    float factor[kGroup];
-#pragma unroll
-    for (int h = 0; h < kGroup; ++h) {
-      factor[h] = __shfl_sync(0xffffffffu, rescale[h & 1], h >> 1);
+    __syncwarp();  // the previous page's fragment reads are done
+    probability[warp][2 * c][g] = n0;
+    probability[warp][2 * c + 1][g] = n1;
+    probability[warp][2 * c][g + 8] = n2;
+    probability[warp][2 * c + 1][g + 8] = n3;
+    // this page's values have landed (the next page's copy may still be in flight)
+    if (next < page_end) {
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
     __syncwarp();
+    // out[dimension, head] = rescale * out + V^T [dimension x token] . P [token x head]
+    const uint32_t p_lo = *reinterpret_cast<const uint32_t*>(&probability[warp][g][2 * c]);
+    const uint32_t p_hi = *reinterpret_cast<const uint32_t*>(&probability[warp][g][2 * c + 8]);
+    const int matrix = lane >> 3, matrix_row = lane & 7;
+    const T* tile_row = &values[warp][buffer][(matrix >> 1) * 8 + matrix_row][(matrix & 1) * 8];
 #pragma unroll
-    for (int h = 0; h < kGroup; ++h) {
-      out[h][0] *= factor[h];
-      out[h][1] *= factor[h];
-    }
-#pragma unroll
-    for (int t = 0; t < kPage; ++t) {
-      const float v0 = Elem<T>::from_bits(v[t] & 0xffffu);
-      const float v1 = Elem<T>::from_bits(v[t] >> 16);
-      const float4 pa = *reinterpret_cast<const float4*>(&probability[warp][t][0]);
-      const float4 pb = *reinterpret_cast<const float4*>(&probability[warp][t][4]);
-      const float weights[kGroup] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
-#pragma unroll
-      for (int h = 0; h < kGroup; ++h) {
-        out[h][0] = fmaf(weights[h], v0, out[h][0]);
-        out[h][1] = fmaf(weights[h], v1, out[h][1]);
+    for (int i = 0; i < 4; ++i) {
+      out[i][0] *= rescale[0];
+      out[i][1] *= rescale[1];
+      out[i][2] *= rescale[0];
+      out[i][3] *= rescale[1];
+      uint32_t a[4];
+      ldmatrix_x4_trans(a, tile_row + 16 * i);
+      if constexpr (kHalf) {
+        mma_f16(out[i], a[0], a[1], a[2], a[3], p_lo, p_hi);
+      } else {
+        mma_bf16(out[i], a[0], a[1], a[2], a[3], p_lo, p_hi);
       }
     }
+    page_base = next_base;
   }
 
   // ---- merge the four warps, then write this split's partial result -----------------------
 #pragma unroll
-  for (int h = 0; h < kGroup; ++h) {
-    merged[warp][h][2 * lane] = out[h][0];
-    merged[warp][h][2 * lane + 1] = out[h][1];
+  for (int i = 0; i < 4; ++i) {
+    merged[warp][2 * c][16 * i + g] = out[i][0];
+    merged[warp][2 * c + 1][16 * i + g] = out[i][1];
+    merged[warp][2 * c][16 * i + g + 8] = out[i][2];
+    merged[warp][2 * c + 1][16 * i + g + 8] = out[i][3];
   }
   if (g == 0) {  // lanes 0..3 hold the statistics of heads 2 c, 2 c + 1
     merged[warp][2 * c][kHeadDim] = running_max[0];
