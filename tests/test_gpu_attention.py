@@ -1,10 +1,12 @@
 """Paged-attention decode through the C ABI against a plain PyTorch fp32 evaluation of the
 same operator (softmax over the visible tokens plus the sink column, f32 throughout).
 
-Tolerance: the kernel multiplies 16-bit keys and queries exactly and accumulates in f32, the
-probabilities stay f32; what differs from the f32 evaluation is the order of the sums and
-the final narrowing to the 16-bit output, so |a - e| <= 2^-7 |e| + 2e-3 (one output ulp of
-bf16 plus accumulation noise on values of order one)."""
+Tolerance: the kernel multiplies 16-bit keys and queries exactly and accumulates in f32; the
+probabilities are narrowed to the cache's 16-bit type for the second product (numerator and
+denominator use the same narrowed values); what else differs from the f32 evaluation is the
+order of the sums and the final narrowing to the 16-bit output, so
+|a - e| <= 2^-7 |e| + 2e-3 (one output ulp of bf16 plus accumulation noise on values of
+order one)."""
 import numpy as np
 import pytest
 import torch
