@@ -54,6 +54,9 @@ PROFILE_CASES = {
     "embedding": "packed embedding gather, 8192 rows of the 201088 x 2880 table",
     "attention": "paged-attention decode, batch 64, 4096 prior tokens, 64 query / 8 kv heads",
     "topk": "row-wise top-8 of 64 x 201088 f32 logits",
+    "split_k": "2880->5760 linear at M=32; with --kernel-policy 2 the tcgen05 tile with K cut "
+               "over a cluster of CTAs (by default the weight-streaming kernel takes it)",
+    "ep_rows": "token permute and indexed k-way combine of 16384 routed rows of 2880 (T=4096)",
 }
 
 
@@ -873,6 +876,8 @@ def run_case(args) -> None:
         raise RuntimeError("bench.py needs a CUDA device: the NVFP4 path has no CPU fallback")
     device = torch.device("cuda", 0)
     _abi.load()
+    if args.kernel_policy:
+        _abi.set_kernel_policy(args.kernel_policy)
     generator = torch.Generator(device=device).manual_seed(5)
 
     def normal(shape, std=0.02, dtype=torch.bfloat16):
@@ -912,6 +917,26 @@ def run_case(args) -> None:
         def fn():
             ops.paged_attention_decode(query, keys, values, table, lengths, sinks)
         nbytes = 2 * batch * (prior + 1) * kv_heads * dim * 2
+    elif args.case == "split_k":
+        weight = quantize.quantize_parameter("w", normal((5760, hidden)))
+        x = normal((32, hidden), 1.0)
+        out = torch.empty((32, 5760), dtype=torch.bfloat16, device=device)
+
+        def fn():
+            ops.linear(x, weight, out=out)
+        nbytes = linear_bytes(32, hidden, 5760)
+    elif args.case == "ep_rows":
+        from nml_b200 import expert_parallel as ep
+        backend = ep.CudaBackend()
+        tokens = 4096
+        x = normal((tokens, hidden), 1.0)
+        order = torch.randperm(tokens * top_k, device=device, generator=generator).to(torch.int32)
+        rows_holder = {}
+
+        def fn():
+            rows_holder["rows"] = backend.gather_rows(x, order, top_k)
+            backend.combine_rows(rows_holder["rows"], order.view(tokens, top_k), tokens, top_k)
+        nbytes = 2 * tokens * top_k * hidden * 2 + tokens * top_k * hidden * 2 + tokens * hidden * 2
     else:
         logits = normal((64, 201088), 1.0, torch.float32)
 
