@@ -219,7 +219,6 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
     *abort_flag = 0;
     mbar_fence_init();
   }
-  __syncthreads();
 
   // ---- the walk every role makes: units [first, last) of (group, tile) pairs -------------
   int groups = p.groups;
@@ -228,8 +227,6 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
   }
   const int tiles = p.tiles_per_group;
   const int64_t total = static_cast<int64_t>(groups) * tiles;
-  const int first = static_cast<int>(total * blockIdx.x / gridDim.x);
-  const int last = static_cast<int>(total * (blockIdx.x + 1) / gridDim.x);
   const int expert_base = (kGrouped && p.expert_offset != nullptr) ? p.expert_offset[0] : 0;
   // grouped: local expert of a schedule block, -1 when the block has no work here
   auto group_expert = [&](int group) -> int {
@@ -241,6 +238,73 @@ __global__ void __launch_bounds__(max_threads<UT>(), 1) stream_kernel(const Para
       return 0;
     }
   };
+  // The units are dealt to the CTAs in contiguous ranges.  Grouped launches weigh them first:
+  // a block without work here costs nothing, a block with routes in its second eight slots
+  // costs about a third more than one without (its tiles issue twice the mma.sync), and equal
+  // shares of units would leave the CTAs that drew the heavy blocks running long after the
+  // others.  Warp 0 weighs the blocks (lane l takes a contiguous chunk), scans, and finds the
+  // two units where this CTA's share of the weight begins and ends.
+  constexpr int kWeighedGroups = 256;
+  // behind the barriers and the abort flag in the launch's shared memory (plan_layout)
+  int* range = reinterpret_cast<int*>(smem + p.barrier_offset + 136);
+  uint8_t* group_weight = smem + p.barrier_offset + 256;
+  bool weighed = false;
+  if constexpr (kGrouped) {
+    weighed = NT == 2 && groups <= kWeighedGroups && groups > 0;  // NT = 1: all blocks alike
+    if (weighed && warp == 0) {
+      const int chunk = (groups + 31) / 32;
+      const int begin = min(groups, lane * chunk), end = min(groups, begin + chunk);
+      int mine = 0;
+      for (int group = begin; group < end; ++group) {
+        int weight = 0;
+        if (group_expert(group) >= 0) {
+          weight = 3;
+          if constexpr (NT == 2) {
+            // slots fill in order, so the ninth slot tells whether the second tile is live
+            const int32_t ninth = p.sorted_assignments[group * 16 + 8];
+            if (ninth >= 0 && ninth < p.assignments) weight = 4;
+          }
+        }
+        group_weight[group] = static_cast<uint8_t>(weight);
+        mine += weight;
+      }
+      int before = mine;  // inclusive scan over the lanes' chunk sums
+#pragma unroll
+      for (int offset = 1; offset < 32; offset <<= 1) {
+        const int other = __shfl_up_sync(0xffffffffu, before, offset);
+        if (lane >= offset) before += other;
+      }
+      const int64_t all = static_cast<int64_t>(__shfl_sync(0xffffffffu, before, 31)) * tiles;
+      before -= mine;  // weight of the groups before this lane's chunk
+      if (lane == 0 && all == 0) range[0] = range[1] = 0;
+      if (all > 0) {
+#pragma unroll
+        for (int side = 0; side < 2; ++side) {
+          // the unit at which the weight all * (block + side) / grid is reached
+          const int64_t target = all * (blockIdx.x + side) / gridDim.x;
+          if (side == 1 && blockIdx.x + 1 == gridDim.x) {
+            if (lane == 0) range[1] = static_cast<int>(total);
+            continue;
+          }
+          int64_t reached = static_cast<int64_t>(before) * tiles;
+          if (target >= reached && target < reached + static_cast<int64_t>(mine) * tiles) {
+            for (int group = begin; group < end; ++group) {
+              const int64_t span = static_cast<int64_t>(group_weight[group]) * tiles;
+              if (target < reached + span) {
+                range[side] = group * tiles +
+                              static_cast<int>((target - reached) / group_weight[group]);
+                break;
+              }
+              reached += span;
+            }
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  const int first = weighed ? range[0] : static_cast<int>(total * blockIdx.x / gridDim.x);
+  const int last = weighed ? range[1] : static_cast<int>(total * (blockIdx.x + 1) / gridDim.x);
   // A position of the walk; always at a unit with work, or at `last`.
   struct Walk {
     int unit, group, tile, expert;
@@ -758,7 +822,8 @@ inline bool plan_layout(int K, int nt, int rt, Params* p, int* smem_bytes) {
   // evenly, else 4 (see launch_for_shape)
   const int held_units = (best_w * best_u == p->k_units && best_u == 3) ? 3 : 4;
   const int second_bytes = nt == 2 ? p->compute_warps * held_units * 2 * 32 * 16 : 0;
-  const int fixed = partial_bytes + second_bytes + 256 /* barriers */ + 128 /* alignment slack */;
+  const int fixed = partial_bytes + second_bytes +
+                    512 /* barriers, unit range, block weights */ + 128 /* alignment slack */;
   int stages = kMaxStages;
   while (stages > 1 && stages * p->stage_bytes + fixed > kSmemBudget) --stages;
   if (stages < 2) return false;
