@@ -786,9 +786,9 @@ def sharded_extras(args, rank, world, device, barrier, head, peaks) -> dict:
             check = layer_check(result[sample], expected,
                                 6e-3 if schedule == "allreduce" and world > 1 else 2e-3)
             if world > 1:
-                verdict = torch.tensor([1.0 if check["ok"] else 0.0], device=device)
-                dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
-                check["ok"] = bool(verdict.item() == 1.0)
+                agreed = torch.tensor([1.0 if check["ok"] else 0.0], device=device)
+                dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+                check["ok"] = bool(agreed.item() == 1.0)
             if not check["ok"]:
                 record["schedules"][schedule] = {"unavailable": "output check failed", **check}
                 continue
