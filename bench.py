@@ -53,7 +53,7 @@ PROFILE_CASES = {
     "moe_t4096": "routed layer, 4096 tokens, 32 experts, top-4 (tcgen05 grouped kernels)",
     "embedding": "packed embedding gather, 8192 rows of the 201088 x 2880 table",
     "attention": "paged-attention decode, batch 64, 4096 prior tokens, 64 query / 8 kv heads",
-    "topk": "row-wise top-8 of 64 x 201088 f32 logits",
+    "topk": "row-wise top-8 of 1024 x 201088 bf16 logits",
     "split_k": "2880->5760 linear at M=32; with --kernel-policy 2 the tcgen05 tile with K cut "
                "over a cluster of CTAs (by default the weight-streaming kernel takes it)",
     "ep_rows": "token permute and indexed k-way combine of 16384 routed rows of 2880 (T=4096)",
@@ -938,11 +938,11 @@ def run_case(args) -> None:
             backend.combine_rows(rows_holder["rows"], order.view(tokens, top_k), tokens, top_k)
         nbytes = 2 * tokens * top_k * hidden * 2 + tokens * top_k * hidden * 2 + tokens * hidden * 2
     else:
-        logits = normal((64, 201088), 1.0, torch.float32)
+        logits = normal((1024, 201088), 1.0)
 
         def fn():
             ops.topk_rows(logits, 8)
-        nbytes = logits.numel() * 4
+        nbytes = logits.numel() * 2
     for _ in range(max(args.warmup, 3)):
         fn()
     torch.cuda.synchronize()

@@ -5,8 +5,9 @@
 // lower index, so the result does not depend on how columns are cut into chunks or shards.
 //
 // Pass 1: one CTA per (row, chunk of 8192 columns); every thread holds 32 logits in registers
-// and the CTA runs k rounds of arg-max (warp shuffles, then one shared-memory step across the
-// warps); the winner's owner retires it.  Pass 2: one warp per row does the same k rounds over
+// and the best of them; the CTA runs k rounds of arg-max over the threads' bests (warp
+// shuffles, then one shared-memory step across the warps), and the winner's owner retires it
+// and finds its next best.  Pass 2: one warp per row does the same k rounds over
 // the chunks' candidates.  Integer/compare work on top of one read of the logits.
 #include "common.cuh"
 
@@ -77,18 +78,24 @@ topk_chunk_kernel(const T* __restrict__ logits, Candidate* __restrict__ partial,
   for (int i = 0; i < kPerThread; ++i) {
     if (!(held[i] == held[i])) held[i] = -INFINITY;  // NaN never wins
   }
-  for (int round = 0; round < k; ++round) {
-    Candidate mine = {-INFINITY, kNoIndex};
+  // Every thread keeps the best of its own 32 values; a round reduces those over the CTA, and
+  // only the thread that owned the winner retires it and looks through its values again.
+  auto best_held = [&]() {
+    Candidate best = {-INFINITY, kNoIndex};
 #pragma unroll
     for (int i = 0; i < kPerThread; ++i) {
       const int column = chunk * kChunk + 8 * (threadIdx.x + kThreads * (i / 8)) + (i % 8);
-      if (column < columns && better(held[i], column, mine.value, mine.index)) {
-        mine.value = held[i];
-        mine.index = column;
+      if (column < columns && better(held[i], column, best.value, best.index)) {
+        best.value = held[i];
+        best.index = column;
       }
     }
-    mine = warp_best(mine);
-    if (lane == 0) warp_winner[warp] = mine;
+    return best;
+  };
+  Candidate mine = best_held();
+  for (int round = 0; round < k; ++round) {
+    const Candidate in_warp = warp_best(mine);
+    if (lane == 0) warp_winner[warp] = in_warp;
     __syncthreads();
     if (warp == 0) {
       Candidate best = lane < kThreads / 32 ? warp_winner[lane] : Candidate{-INFINITY, kNoIndex};
@@ -100,11 +107,14 @@ topk_chunk_kernel(const T* __restrict__ logits, Candidate* __restrict__ partial,
     }
     __syncthreads();
     const int taken = winner.index;
-    // retire the winner: its owner marks it NaN, which loses every later comparison
+    if (taken != kNoIndex && taken == mine.index) {
+      // retire the winner: NaN loses every later comparison
 #pragma unroll
-    for (int i = 0; i < kPerThread; ++i) {
-      const int column = chunk * kChunk + 8 * (threadIdx.x + kThreads * (i / 8)) + (i % 8);
-      if (column == taken) held[i] = __int_as_float(0xffc00000);
+      for (int i = 0; i < kPerThread; ++i) {
+        const int column = chunk * kChunk + 8 * (threadIdx.x + kThreads * (i / 8)) + (i % 8);
+        if (column == taken) held[i] = __int_as_float(0xffc00000);
+      }
+      mine = best_held();
     }
   }
 }
