@@ -300,7 +300,11 @@ def run_ours(args) -> None:
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        # a rank that fails in the sharded extras must not hold the others for NCCL's default
+        # ten minutes
+        import datetime
+        dist.init_process_group("nccl", device_id=device,
+                                timeout=datetime.timedelta(minutes=4))
     _abi.load()
     if args.kernel_policy:
         _abi.set_kernel_policy(args.kernel_policy)
@@ -451,7 +455,11 @@ def run_ours(args) -> None:
         head = weights.pop("unembed")
         weights.clear()
         torch.cuda.empty_cache()
-        sharded = sharded_extras(args, rank, world, device, barrier, head, peaks)
+        try:
+            sharded = sharded_extras(args, rank, world, device, barrier, head, peaks)
+        except Exception as error:  # noqa: BLE001 -- the sweep's line must still be printed
+            sharded = {"n_gpus": world,
+                       "unavailable": f"{type(error).__name__}: {error}"[:300]}
         del head
         torch.cuda.empty_cache()
         if not args.no_decode_step:
