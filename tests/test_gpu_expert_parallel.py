@@ -75,9 +75,10 @@ def test_dispatch_plan_gather_and_combine_kernels_against_numpy():
 
 
 @pytest.mark.parametrize("fused_return", [True, False])
-@pytest.mark.parametrize("ranks,experts,tokens", [(2, 8, 96), (4, 8, 40), (8, 32, 64),
-                                                  (8, 8, 512)])
-def test_push_schedule_with_several_ranks_emulated_on_one_device(ranks, experts, tokens,
+@pytest.mark.parametrize("ranks,experts,tokens,skewed", [
+    (2, 8, 96, False), (4, 8, 40, False), (8, 32, 64, False), (8, 8, 512, False),
+    (8, 32, 64, True), (4, 8, 40, True)])
+def test_push_schedule_with_several_ranks_emulated_on_one_device(ranks, experts, tokens, skewed,
                                                                  fused_return):
     # No kernel of the peer-push schedule waits for a flag that an earlier launch has not
     # raised when the stages are replayed stage by stage over all ranks, so G ranks can run on
@@ -85,7 +86,10 @@ def test_push_schedule_with_several_ranks_emulated_on_one_device(ranks, experts,
     # counts, arrival and return flags, epochs over two consecutive layers) and compares every
     # rank's output with the oracle's evaluation of the layer.  With `fused_return` the down
     # projection stores its rows into the senders' return buffers itself (through the row
-    # targets that receive_meta fills) and return_rows only raises the flags.
+    # targets that receive_meta fills) and return_rows only raises the flags.  `skewed`: a
+    # router that sends every route of every rank to the first four experts, i.e. to one or two
+    # owners, which then receive each sender's whole region (regions hold a sender's full
+    # assignment count, so no routing can overflow them).
     from ep_common import OracleBackend, build_problem, tensor_to_bits
     from nml_b200 import _abi, expert_parallel as ep
     import gpu_util as gu
@@ -94,6 +98,9 @@ def test_push_schedule_with_several_ranks_emulated_on_one_device(ranks, experts,
     per_rank = tokens
     gate, gb, down, db, x, logits, active = build_problem(per_rank * ranks, experts, hidden,
                                                           inter, seed=31 + ranks, device="cuda")
+    if skewed:
+        logits = logits.clone()
+        logits[:, :k] += 50.0
     backend = ep.CudaBackend()
     exchanges = ep.PeerExchange.emulated(ranks, per_rank * k, hidden, torch.bfloat16, "cuda")
     layers = [ep.LocalExperts.shard(gate, gb, down, db, r, ranks) for r in range(ranks)]
