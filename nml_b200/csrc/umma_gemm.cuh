@@ -772,7 +772,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     {
       constexpr uint32_t a_format = AFMT == kAf16 ? kUmmaF16 : kUmmaBF16;
       constexpr uint32_t b_format = std::is_same<T, __half>::value ? kUmmaF16 : kUmmaBF16;
-      constexpr uint32_t idesc = umma_idesc_f16(a_format, b_format, kTileN, BM);
+      // Tall tiles issue only as many activation rows (the MMA's N) as the unit has, rounded
+      // up to 16: an expert's last slot tile, or the last rows of a dense operand, then costs
+      // its share of the tensor pipe and of the operand reads instead of a full tile's.
+      constexpr bool kDynamicRows = BM >= 64;
       constexpr uint64_t desc_hi = static_cast<uint64_t>(kUmmaDescHiSw128) << 32;
       RingState xs, wb;
       int local = 0;
@@ -788,6 +791,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
         mbar_wait_or_abort(&tmem_empty[acc], acc_phase ^ 1u, abort_flag, p.status,
                            kSiteMmaAccumulator);
         tcgen05_fence_after_sync();
+        uint32_t issued_rows = BM;
+        if constexpr (kDynamicRows) {
+          const Unit u = get_unit<BM, GROUPED>(p, groups, index);
+          issued_rows = static_cast<uint32_t>(min(BM, max(16, (u.rows + 15) & ~15)));
+        }
+        const uint32_t idesc = umma_idesc_f16(a_format, b_format, kTileN, issued_rows);
         const uint32_t d_base = tmem_base + acc * PA * BM;
         int step = 0;  // K step inside the unit
         for (int rs = 0; rs < stages; ++rs) {
@@ -906,6 +915,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       constexpr int kChunk = BM >= 32 ? 32 : 16;
 #pragma unroll 1
       for (int c = 0; c < BM; c += kChunk) {
+        if (BM >= 64 && c >= u.rows) break;  // columns the MMAs of this unit did not write
         const uint32_t address =
             tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * PA * BM + c;
         uint32_t v[kChunk];
