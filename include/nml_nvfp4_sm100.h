@@ -506,6 +506,27 @@ int32_t nml_nvfp4_sm100_topk_rows(const NmlSm100TopkRows *request, char *error_m
                                   size_t error_message_capacity);
 size_t nml_nvfp4_sm100_topk_rows_workspace_bytes(int64_t rows, int64_t columns, int64_t k);
 
+/* The other half: merges the candidates of `parts` shards (or ranks) into the k best of every
+ * row, with the same order as nml_nvfp4_sm100_topk_rows (larger value first, equal values to
+ * the lower index), so the result equals a top-k over the unsharded row.  Candidate j of part p
+ * and row r is values[(p * rows + r) * pitch + j] / indices[(p * rows + r) * pitch + j] for
+ * j < k (an all-gather of every rank's [rows, pitch] block gives exactly this layout);
+ * indices < 0 mark empty candidates.  parts * k <= 512. */
+typedef struct NmlSm100TopkMerge {
+  size_t struct_size;
+  const float *values;     /* [parts, rows, pitch] */
+  const int32_t *indices;  /* [parts, rows, pitch] */
+  float *out_values;       /* [rows, k] */
+  int32_t *out_indices;    /* [rows, k] */
+  void *stream;
+  int64_t parts;
+  int64_t rows;
+  int64_t pitch;
+  int64_t k;
+} NmlSm100TopkMerge;
+int32_t nml_nvfp4_sm100_topk_merge(const NmlSm100TopkMerge *request, char *error_message,
+                                   size_t error_message_capacity);
+
 /* Paged-attention decode: one query token per sequence over a paged K/V cache, grouped-query
  * heads, causal, optional sliding window and learned per-head sinks.  Not part of the
  * reference's NVFP4 kernel ABI: it is the operator next to it in the product graph

@@ -195,8 +195,15 @@ class EpWaitReturns(ctypes.Structure):
                 ("experts_per_token", _i64), ("dtype", _i32)]
 
 
+class TopkMerge(ctypes.Structure):
+    _fields_ = [("struct_size", _sz), ("values", _vp), ("indices", _vp), ("out_values", _vp),
+                ("out_indices", _vp), ("stream", _vp), ("parts", _i64), ("rows", _i64),
+                ("pitch", _i64), ("k", _i64)]
+
+
 # name -> request structure, for the entry points of the form fn(const Request*, char*, size_t)
 REQUEST_ENTRY_POINTS = {
+    "nml_nvfp4_sm100_topk_merge": TopkMerge,
     "nml_nvfp4_sm100_ep_push_rows": EpPushRows,
     "nml_nvfp4_sm100_ep_receive_meta": EpReceiveMeta,
     "nml_nvfp4_sm100_ep_return_rows": EpReturnRows,

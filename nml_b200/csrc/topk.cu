@@ -157,10 +157,79 @@ topk_merge_kernel(const Candidate* __restrict__ partial, float* __restrict__ val
   }
 }
 
+// One warp per row: the k best of the parts' candidates, same order as above.
+__global__ void __launch_bounds__(32)
+topk_merge_parts_kernel(const float* __restrict__ values, const int32_t* __restrict__ indices,
+                        float* __restrict__ out_values, int32_t* __restrict__ out_indices,
+                        int parts, int rows, int64_t pitch, int k) {
+  const int row = blockIdx.x;
+  const int lane = threadIdx.x;
+  const int total = parts * k;
+  constexpr int kHeld = 16;  // up to 512 candidates per row
+  Candidate held[kHeld];
+#pragma unroll
+  for (int i = 0; i < kHeld; ++i) {
+    const int at = lane + 32 * i;
+    held[i] = Candidate{-INFINITY, kNoIndex};
+    if (at < total) {
+      const int part = at / k, j = at - part * k;
+      const int64_t from = (static_cast<int64_t>(part) * rows + row) * pitch + j;
+      const int32_t index = indices[from];
+      const float value = values[from];
+      if (index >= 0 && value == value) held[i] = Candidate{value, index};
+    }
+  }
+  for (int round = 0; round < k; ++round) {
+    Candidate best = {-INFINITY, kNoIndex};
+    int slot = -1;
+#pragma unroll
+    for (int i = 0; i < kHeld; ++i) {
+      if (held[i].index != kNoIndex && better(held[i].value, held[i].index, best.value, best.index)) {
+        best = held[i];
+        slot = i;
+      }
+    }
+    const Candidate winner = warp_best(best);
+#pragma unroll
+    for (int i = 0; i < kHeld; ++i) {
+      if (i == slot && best.index == winner.index) held[i].index = kNoIndex;  // retired
+    }
+    if (lane == 0) {
+      out_values[static_cast<int64_t>(row) * k + round] = winner.value;
+      out_indices[static_cast<int64_t>(row) * k + round] =
+          winner.index == kNoIndex ? -1 : winner.index;
+    }
+  }
+}
+
 }  // namespace
 }  // namespace nml_sm100
 
 using namespace nml_sm100;
+
+extern "C" int32_t nml_nvfp4_sm100_topk_merge(const NmlSm100TopkMerge* request,
+                                              char* error_message,
+                                              size_t error_message_capacity) {
+  if (request == nullptr || request->struct_size < sizeof(NmlSm100TopkMerge)) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "truncated top-k merge request", error_message,
+                error_message_capacity);
+  }
+  const NmlSm100TopkMerge& r = *request;
+  if (r.values == nullptr || r.indices == nullptr || r.out_values == nullptr ||
+      r.out_indices == nullptr || r.stream == nullptr || r.parts <= 0 || !fits_i32(r.rows) ||
+      r.rows > 0x7fffffff || r.k <= 0 || r.k > kMaxK || r.pitch < r.k || r.parts * r.k > 512) {
+    return fail(NML_SM100_INVALID_ARGUMENT, "invalid top-k merge request", error_message,
+                error_message_capacity);
+  }
+  if (current_device(error_message, error_message_capacity) == nullptr) {
+    return NML_SM100_LAUNCH_FAILURE;
+  }
+  topk_merge_parts_kernel<<<static_cast<unsigned>(r.rows), 32, 0,
+                            static_cast<cudaStream_t>(r.stream)>>>(
+      r.values, r.indices, r.out_values, r.out_indices, static_cast<int>(r.parts),
+      static_cast<int>(r.rows), r.pitch, static_cast<int>(r.k));
+  return launch_result(error_message, error_message_capacity);
+}
 
 extern "C" size_t nml_nvfp4_sm100_topk_rows_workspace_bytes(int64_t rows, int64_t columns,
                                                             int64_t k) {

@@ -157,8 +157,10 @@ class CudaBackend:
         return ops.linear(hidden, weight, bias)
 
     def topk(self, logits, k, index_offset):
-        values, indices = ops.topk_rows(logits, k, index_offset)
-        return values, indices.long()
+        return ops.topk_rows(logits, k, index_offset)
+
+    def topk_merge(self, values, indices, k):
+        return ops.topk_merge(values, indices, k)
 
 
 @dataclass
@@ -489,27 +491,19 @@ class ShardedUnembedding:
         local = self.backend.linear(self._all_rows(hidden, gather_rows), self.weight)
         values, indices = self.backend.topk(local, k, self.column_offset)
         if self.world == 1:
-            return values, indices
+            return values, indices.long()
         rows = local.shape[0]
-        packed = torch.cat((values, indices.float()), dim=1) \
-            if self.columns_total < (1 << 24) else None
-        if packed is not None:  # indices below 2^24 are exact in f32: one collective
-            gathered = torch.empty((self.world, rows, 2 * k), dtype=torch.float32,
-                                   device=local.device)
-            dist.all_gather_into_tensor(gathered.view(self.world * rows, 2 * k), packed,
-                                        group=self.group)
-            all_values = gathered[:, :, :k].permute(1, 0, 2).reshape(rows, self.world * k)
-            all_indices = gathered[:, :, k:].permute(1, 0, 2).reshape(rows, self.world * k).long()
-        else:
-            gv = torch.empty((self.world * rows, k), dtype=torch.float32, device=local.device)
-            gi = torch.empty((self.world * rows, k), dtype=torch.int64, device=local.device)
-            dist.all_gather_into_tensor(gv, values.contiguous(), group=self.group)
-            dist.all_gather_into_tensor(gi, indices.contiguous(), group=self.group)
-            all_values = gv.view(self.world, rows, k).permute(1, 0, 2).reshape(rows, -1)
-            all_indices = gi.view(self.world, rows, k).permute(1, 0, 2).reshape(rows, -1)
-        # candidates are ordered by rank, i.e. by vocabulary index inside equal values
-        best, position = torch.topk(all_values, k, dim=1)
-        return best, torch.gather(all_indices, 1, position)
+        # one collective: every rank's [rows, 2 k] block of value bits and indices; the merge
+        # keeps the order of the per-shard selection (larger value, then lower index), so the
+        # result is the top-k of the unsharded row whatever the ties
+        packed = torch.cat((values.contiguous().view(torch.int32), indices), dim=1)
+        gathered = torch.empty((self.world, rows, 2 * k), dtype=torch.int32,
+                               device=local.device)
+        dist.all_gather_into_tensor(gathered.view(self.world * rows, 2 * k), packed,
+                                    group=self.group)
+        best, position = self.backend.topk_merge(gathered.view(torch.float32)[:, :, :k],
+                                                 gathered[:, :, k:], k)
+        return best, position.long()
 
     def argmax(self, hidden: torch.Tensor, gather_rows: bool = True) -> torch.Tensor:
         """Greedy pick for this rank's rows of ``hidden`` (i64 [rows])."""

@@ -550,3 +550,29 @@ def topk_rows(logits: torch.Tensor, k: int, index_offset: int = 0):
                             dtype=_code(logits.dtype))
     _abi.call("nml_nvfp4_sm100_topk_rows", request)
     return values, indices
+
+
+def topk_merge(values: torch.Tensor, indices: torch.Tensor, k: int):
+    """(values f32 [rows, k], indices i32 [rows, k]): the k best of every row among the
+    candidates of several parts (shards or ranks), ``values`` f32 and ``indices`` i32 of shape
+    ``[parts, rows, >= k]`` with the same strides (views into one gathered block are fine);
+    larger value first, equal values to the lower index, negative indices are empty
+    (``nml_nvfp4_sm100_topk_merge``)."""
+    if values.dim() != 3 or values.shape != indices.shape or values.stride() != indices.stride():
+        raise ValueError("top-k merge expects values and indices of one shape and layout")
+    if values.dtype != torch.float32 or indices.dtype != torch.int32:
+        raise ValueError("top-k merge takes F32 values and I32 indices")
+    parts, rows, width = values.shape
+    pitch = values.stride(1)
+    if values.stride(2) != 1 or values.stride(0) != rows * pitch or not 0 < k <= min(16, width) \
+            or parts * k > 512:
+        raise ValueError("top-k merge: candidates must be row-contiguous, k <= 16, parts * k <= 512")
+    if not values.is_cuda or not indices.is_cuda:
+        raise RuntimeError("NVFP4 operators run on a CUDA device only (no CPU fallback)")
+    out_values = torch.empty((rows, k), dtype=torch.float32, device=values.device)
+    out_indices = torch.empty((rows, k), dtype=torch.int32, device=values.device)
+    request = _abi.TopkMerge(values=values.data_ptr(), indices=indices.data_ptr(),
+                             out_values=_ptr(out_values), out_indices=_ptr(out_indices),
+                             stream=_stream(values), parts=parts, rows=rows, pitch=pitch, k=k)
+    _abi.call("nml_nvfp4_sm100_topk_merge", request)
+    return out_values, out_indices

@@ -49,6 +49,19 @@ class OracleBackend:
         return (torch.from_numpy(send_order), torch.from_numpy(local), torch.from_numpy(slot_of),
                 torch.from_numpy(counts))
 
+    def topk_merge(self, values, indices, k):
+        v, i = values.numpy(), indices.numpy()
+        parts, rows, _ = v.shape
+        out_v = np.full((rows, k), -np.inf, np.float32)
+        out_i = np.full((rows, k), -1, np.int32)
+        for r in range(rows):
+            cv, ci = v[:, r, :k].reshape(-1), i[:, r, :k].reshape(-1)
+            keep = ci >= 0
+            order = np.lexsort((ci[keep], -cv[keep]))[:k]  # larger value, then lower index
+            out_v[r, :order.size] = cv[keep][order]
+            out_i[r, :order.size] = ci[keep][order]
+        return torch.from_numpy(out_v), torch.from_numpy(out_i)
+
     def gather_rows(self, source, row_index, divisor):
         index = row_index.numpy()
         bits = tensor_to_bits(source)
@@ -87,7 +100,7 @@ class OracleBackend:
     def topk(self, logits, k, index_offset):
         # descending, equal values to the lower index (a stable sort keeps index order)
         values, order = torch.sort(logits.float(), dim=1, descending=True, stable=True)
-        return values[:, :k].contiguous(), (order[:, :k] + index_offset).contiguous()
+        return values[:, :k].contiguous(), (order[:, :k] + index_offset).to(torch.int32).contiguous()
 
     def layer_f32(self, hidden, expert_ids, routing_weights, layer):
         """The routed layer with the device path's narrowing of the two intermediates, as f32

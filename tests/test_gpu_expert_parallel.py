@@ -216,7 +216,15 @@ def nccl_worker(rank, world, port, results):
         table = ops.NvFp4Parameter("t", (experts * 2 * inter, hidden), gate.dtype,
                                    gate.payload.reshape(-1, hidden // 2),
                                    gate.block_scales.reshape(-1, hidden // 16), gate.global_scale)
-        logits_out = ep.ShardedUnembedding(table)(mine[0])
+        head = ep.ShardedUnembedding(table)
+        logits_out = head(mine[0])
+        # the sampler's view: per-shard candidates merged across ranks must be the top-k of
+        # the gathered logits (stable order: larger value, then lower vocabulary index)
+        merged_values, merged_indices = head.topk(mine[0], 8)
+        order = torch.sort(logits_out.float(), dim=1, descending=True, stable=True)
+        outcome["topk"] = (bool(torch.equal(merged_values, order.values[:, :8])),
+                           bool(torch.equal(merged_indices, order.indices[:, :8])),
+                           bool(torch.equal(head.argmax(mine[0]), order.indices[lo:hi, 0])))
         import oracle
         unembed_expected = oracle.linear(  # the sharded head gathers the rows of every rank
             oracle.to_f32(tensor_to_bits(x), oracle.BF16), table.payload.cpu().numpy(),
@@ -240,6 +248,7 @@ def test_nccl_ranks_match_single_device_evaluation():
     import gpu_util as gu
     for rank in range(world):
         outcome = results[rank]
+        assert outcome["topk"] == (True, True, True), f"rank {rank}: {outcome['topk']}"
         for schedule in ("alltoall", "allreduce", "push", "unembed"):
             out, expected = outcome[schedule]
             what = f"{schedule} rank {rank} of {world}"
