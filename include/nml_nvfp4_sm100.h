@@ -63,7 +63,29 @@ typedef struct NmlSm100Linear {
   int64_t inputs;
   int32_t dtype; /* NmlSm100DType */
   const void *residual; /* optional: [rows, outputs] dtype, or NULL */
+  /* Optional scratch (read when struct_size covers both fields), 256-byte aligned: with at
+   * least nml_nvfp4_sm100_linear_workspace_bytes(...) bytes, a BF16 call on a wide weight
+   * first narrows the activations to F16, every tile of 256 rows times one power of two that
+   * puts the tile's largest magnitude into [2^14, 2^15), so that the weights decode with the
+   * hardware FP4/FP8 conversions; the inverse power multiplies the tile's f32 sums.  Elements
+   * down to 2^-28 of the tile's largest stay exact, smaller ones round at 2^-39 of it.  The
+   * device checks the input first: when a row's largest magnitude is more than 2^8 below its
+   * tile's, or a tile holds an infinity, a NaN or nothing above 2^-111, the BF16-operand
+   * kernel produces the output instead (it is launched behind the narrowed one; each of the
+   * two returns at once when the other is meant) and the word at
+   * nml_nvfp4_sm100_linear_workspace_verdict_offset(...) of the scratch reads nonzero.
+   * Without scratch the call decodes to BF16, several per cent slower. */
+  void *workspace;
+  size_t workspace_bytes;
 } NmlSm100Linear;
+
+/* Scratch bytes nml_nvfp4_sm100_linear can use for this call; 0 when it would not use any. */
+size_t nml_nvfp4_sm100_linear_workspace_bytes(int64_t rows, int64_t outputs, int64_t inputs,
+                                              int32_t dtype);
+/* Byte offset, in that scratch, of the uint32 the call leaves at 0 when the F16-operand kernel
+ * produced the output and at 1 when the BF16-operand kernel did. */
+size_t nml_nvfp4_sm100_linear_workspace_verdict_offset(int64_t rows, int64_t outputs,
+                                                       int64_t inputs, int32_t dtype);
 
 /* Three linears that share one activation (the Q, K and V projections), in one launch:
  * output[i][rows, outputs[i]] = X * W_i^T (+ bias[i]).  The reference fuses them only for

@@ -44,7 +44,8 @@ class Linear(ctypes.Structure):
     _fields_ = [("struct_size", _sz), ("activation", _vp), ("payload", _vp),
                 ("block_scales", _vp), ("global_scale", _vp), ("bias", _vp), ("output", _vp),
                 ("stream", _vp), ("rows", _i64), ("outputs", _i64), ("inputs", _i64),
-                ("dtype", _i32), ("residual", _vp)]
+                ("dtype", _i32), ("residual", _vp), ("workspace", _vp),
+                ("workspace_bytes", _sz)]
 
 
 class LinearQkv(ctypes.Structure):
@@ -226,6 +227,8 @@ REQUEST_ENTRY_POINTS = {
 }
 
 OTHER_ENTRY_POINTS = [
+    "nml_nvfp4_sm100_linear_workspace_bytes",
+    "nml_nvfp4_sm100_linear_workspace_verdict_offset",
     "nml_nvfp4_sm100_routed_swiglu_workspace_bytes",
     "nml_nvfp4_sm100_routed_swiglu_workspace_layout",
     "nml_nvfp4_sm100_plan_capacity",
@@ -265,6 +268,10 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.restype = _i32
         fn.argtypes = [ctypes.POINTER(struct), ctypes.c_char_p, _sz]
+    lib.nml_nvfp4_sm100_linear_workspace_bytes.restype = _sz
+    lib.nml_nvfp4_sm100_linear_workspace_bytes.argtypes = [_i64, _i64, _i64, _i32]
+    lib.nml_nvfp4_sm100_linear_workspace_verdict_offset.restype = _sz
+    lib.nml_nvfp4_sm100_linear_workspace_verdict_offset.argtypes = [_i64, _i64, _i64, _i32]
     lib.nml_nvfp4_sm100_routed_swiglu_workspace_bytes.restype = _sz
     lib.nml_nvfp4_sm100_routed_swiglu_workspace_bytes.argtypes = [_i64] * 5
     lib.nml_nvfp4_sm100_routed_swiglu_workspace_layout.restype = _i32

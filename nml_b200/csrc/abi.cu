@@ -302,7 +302,27 @@ extern "C" int32_t nml_nvfp4_sm100_linear(const NmlSm100Linear* request, char* e
   args.residual = has_field(request, offsetof(NmlSm100Linear, residual), sizeof(void*))
                       ? request->residual
                       : nullptr;
+  if (has_field(request, offsetof(NmlSm100Linear, workspace_bytes), sizeof(size_t))) {
+    args.workspace = request->workspace;
+    args.workspace_bytes = request->workspace != nullptr ? request->workspace_bytes : 0;
+  }
   return dispatch_linear(args, *device, error_message, error_message_capacity);
+}
+
+extern "C" size_t nml_nvfp4_sm100_linear_workspace_bytes(int64_t rows, int64_t outputs,
+                                                         int64_t inputs, int32_t dtype) {
+  if (rows <= 0 || outputs <= 0 || inputs <= 0 || !fits_i32(rows) || !fits_i32(outputs) ||
+      !fits_i32(inputs) || !valid_dtype(dtype)) {
+    return 0;
+  }
+  return linear_umma_workspace_bytes(rows, outputs, inputs, dtype);
+}
+
+extern "C" size_t nml_nvfp4_sm100_linear_workspace_verdict_offset(int64_t rows, int64_t outputs,
+                                                                  int64_t inputs,
+                                                                  int32_t dtype) {
+  if (nml_nvfp4_sm100_linear_workspace_bytes(rows, outputs, inputs, dtype) == 0) return 0;
+  return linear_umma_workspace_verdict_offset(rows, inputs);
 }
 
 extern "C" int32_t nml_nvfp4_sm100_linear_qkv(const NmlSm100LinearQkv* request,

@@ -156,6 +156,12 @@ struct LinearArgs {
   int rows, outputs, inputs;
   int dtype;
   const void* residual = nullptr;  // [rows, outputs], added to the narrowed result
+  void* workspace = nullptr;       // optional scratch of the caller
+  size_t workspace_bytes = 0;
+  // internal (the narrowed-operand form of the tcgen05 linear)
+  const float* tile_scale = nullptr;  // factor of the f32 sums of every 256-row tile
+  const uint32_t* gate = nullptr;     // the launch runs only if (*gate != 0) == gate_when
+  int gate_when = 0;
   // Fused projections that share the activation (Q/K/V): further weights after the first.
   struct Projection {
     const uint8_t* payload;
@@ -175,6 +181,9 @@ int32_t launch_linear_simt(const LinearArgs& args, const DeviceInfo& device, cha
 bool linear_umma_supported(const LinearArgs& args);
 int32_t launch_linear_umma(const LinearArgs& args, const DeviceInfo& device, char* message,
                            size_t capacity);
+// Scratch the tcgen05 linear can use (F16 copy of BF16 activations for wide weights), else 0.
+size_t linear_umma_workspace_bytes(int64_t rows, int64_t outputs, int64_t inputs, int32_t dtype);
+size_t linear_umma_workspace_verdict_offset(int64_t rows, int64_t inputs);
 // The weight-streaming kernel: few activation rows, K a multiple of 64 up to 4096.
 bool linear_stream_supported(const LinearArgs& args);
 int32_t launch_linear_stream(const LinearArgs& args, const DeviceInfo& device, char* message,

@@ -69,6 +69,9 @@ int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* me
   p.N = args.outputs;
   p.K = args.inputs;
   p.split_k = split_k;
+  p.tile_scale = args.tile_scale;
+  p.gate = args.gate;
+  p.gate_when = args.gate_when;
   p.segments = 1 + args.extra_projections;
   p.segment[0] = {args.block_scales, args.global_scale, args.bias, args.output, args.outputs, 0,
                   args.residual};
@@ -121,9 +124,11 @@ int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* me
     kernel<<<grid, launch_threads<DG, MI, true>(), smem_bytes, args.stream>>>(
         tmap_payload, tmap_x, p, tmap_extra[0], tmap_extra[1]);
   }
+  if (args.gate != nullptr && args.gate_when != 0) return launch_result(message, capacity);
   note_linear_kernel(WT ? (AFMT == kAf16      ? "umma_tmem_weights_af16"
                            : AFMT == kAbf16Lut ? "umma_tmem_weights_abf16_lut"
                                                : "umma_tmem_weights_abf16")
+                        : args.tile_scale != nullptr ? "umma_swapab_narrowed_af16"
                         : (AFMT == kAf16 ? "umma_swapab_af16" : "umma_swapab_abf16"), BM);
   return launch_result(message, capacity);
 }
@@ -154,6 +159,122 @@ int choose_tile_rows(int rows, int outputs, int sm_count, bool wide) {
     }
   }
   return best;
+}
+
+// BF16 activations of a wide weight, narrowed once per call to F16 so that the weights decode
+// with cvt.rn.f16x2.e2m1x2 / e4m3x2 instead of the integer sequences of the BF16 decode (the
+// decode warps bound the 256-row tile).  Every tile of 256 rows is multiplied by one power of
+// two that puts its largest magnitude into [2^14, 2^15); the inverse power multiplies the
+// tile's f32 sums.  F16 then holds every element down to 2^-28 of the tile's largest exactly
+// and rounds smaller ones at 2^-39 of it.  The narrowed kernel is used only when that is far
+// below the rounding of the f32 sums for every row: each row's largest magnitude must lie
+// within 2^8 of its tile's (rows of zeros aside), the tile must be finite and not tiny.  If
+// any row fails, the verdict word is raised and the BF16-operand kernel, launched behind the
+// narrowed one, produces the output instead; each of the two returns at once when the word
+// names the other.
+constexpr int kNarrowTileRows = 256;
+
+// largest 15-bit magnitude of every row; block 0 clears the verdict
+__global__ void __launch_bounds__(256)
+row_magnitude_kernel(const __nv_bfloat16* __restrict__ x, uint32_t* __restrict__ row_magnitude,
+                     uint32_t* __restrict__ verdict, int inputs) {
+  const int64_t row = blockIdx.x;
+  const uint4* source = reinterpret_cast<const uint4*>(x + row * inputs);
+  __shared__ uint32_t warp_max[8];
+  uint32_t magnitude = 0;
+  for (int i = threadIdx.x; i < inputs / 8; i += blockDim.x) {
+    const uint4 q = __ldg(source + i);
+    const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      magnitude = max(magnitude, max(words[w] & 0x7fffu, (words[w] >> 16) & 0x7fffu));
+    }
+  }
+#pragma unroll
+  for (int offset = 16; offset != 0; offset >>= 1) {
+    magnitude = max(magnitude, __shfl_xor_sync(0xffffffffu, magnitude, offset));
+  }
+  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = magnitude;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    magnitude = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) magnitude = max(magnitude, warp_max[w]);
+    row_magnitude[row] = magnitude;
+    if (row == 0) *verdict = 0u;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+narrow_rows_kernel(const __nv_bfloat16* __restrict__ x, const uint32_t* __restrict__ row_magnitude,
+                   __half* __restrict__ narrowed, float* __restrict__ tile_scale,
+                   uint32_t* __restrict__ verdict, int rows, int inputs) {
+  const int row = blockIdx.x;
+  const int tile = row / kNarrowTileRows;
+  __shared__ uint32_t warp_max[8];
+  const int peer = tile * kNarrowTileRows + static_cast<int>(threadIdx.x);
+  uint32_t magnitude = peer < rows ? row_magnitude[peer] : 0u;
+#pragma unroll
+  for (int offset = 16; offset != 0; offset >>= 1) {
+    magnitude = max(magnitude, __shfl_xor_sync(0xffffffffu, magnitude, offset));
+  }
+  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = magnitude;
+  __syncthreads();
+  magnitude = 0;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) magnitude = max(magnitude, warp_max[w]);
+  const int tile_exponent = static_cast<int>(magnitude >> 7);  // biased, 0..255
+  const int shift = tile_exponent - 127 - 14;                  // tile's largest -> [2^14, 2^15)
+  if (threadIdx.x == 0) {
+    const uint32_t own = row_magnitude[row];
+    const int own_exponent = static_cast<int>(own >> 7);
+    const bool tile_ok = magnitude == 0u || (tile_exponent != 255 && tile_exponent >= 16);
+    const bool row_ok = own == 0u || own_exponent >= tile_exponent - 8;
+    if (!tile_ok || !row_ok) atomicOr(verdict, 1u);
+    if (row % kNarrowTileRows == 0) {
+      tile_scale[tile] = magnitude == 0u || !tile_ok
+                             ? 1.0f
+                             : __uint_as_float(static_cast<uint32_t>(127 + shift) << 23);
+    }
+  }
+  if (magnitude != 0u && (tile_exponent == 255 || tile_exponent < 16)) return;  // verdict raised
+  // (a tile of zeros is written as zeros)
+  const float down =
+      magnitude == 0u ? 1.0f : __uint_as_float(static_cast<uint32_t>(127 - shift) << 23);
+  const uint4* source = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(row) * inputs);
+  uint4* target = reinterpret_cast<uint4*>(narrowed + static_cast<int64_t>(row) * inputs);
+  for (int i = threadIdx.x; i < inputs / 8; i += blockDim.x) {
+    const uint4 q = __ldg(source + i);
+    const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+    uint32_t packed[4];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const __half2 h = __floats2half2_rn(__uint_as_float(words[w] << 16) * down,
+                                          __uint_as_float(words[w] & 0xffff0000u) * down);
+      packed[w] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    target[i] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  }
+}
+
+// Rows and outputs from which the narrowing passes pay: they move 6 bytes per activation
+// element, the projection 2 * outputs flops.
+constexpr int64_t kNarrowMinRows = 512;
+constexpr int64_t kNarrowMinOutputs = 16384;
+
+struct NarrowWorkspace {
+  size_t magnitudes, tile_scales, verdict, total;
+};
+
+NarrowWorkspace narrow_workspace(int64_t rows, int64_t inputs) {
+  auto align = [](size_t v) { return (v + 255) / 256 * 256; };
+  NarrowWorkspace w;
+  w.magnitudes = align(static_cast<size_t>(rows) * inputs * 2);
+  w.tile_scales = w.magnitudes + align(static_cast<size_t>(rows) * 4);
+  w.verdict = w.tile_scales +
+              align(static_cast<size_t>((rows + kNarrowTileRows - 1) / kNarrowTileRows) * 4);
+  w.total = w.verdict + 256;
+  return w;
 }
 
 template <int AFMT, typename T>
@@ -239,6 +360,42 @@ int32_t launch_for_rows(const LinearArgs& args, const DeviceInfo& device, char* 
       return launch_config<128, 1, 8, 5, 5, 3, 1, 1, false, AFMT, T>(args, device, message,
                                                                      capacity);
     default: {
+      LinearArgs plain = args;
+      if constexpr (AFMT == kAbf16) {
+        // wide weight, many rows, scratch given: F16 operands, with the BF16-operand kernel
+        // behind it for inputs the narrowing does not hold (see narrow_rows_kernel)
+        const size_t wanted = linear_umma_workspace_bytes(args.rows, args.outputs, args.inputs,
+                                                          args.dtype);
+        if (wanted != 0 && args.workspace_bytes >= wanted && bulk_scales_legal &&
+            policy == NML_SM100_POLICY_AUTO && args.extra_projections == 0 &&
+            reinterpret_cast<uintptr_t>(args.workspace) % 256 == 0 &&
+            KernelLayout<256, 1, 4, 3, 4, false, kAf16, kDense, true>::kSmemBytes +
+                    2 * bulk_scale_buffer_bytes(args.inputs / 16) <= kSmemBudget) {
+          const NarrowWorkspace w = narrow_workspace(args.rows, args.inputs);
+          uint8_t* base = static_cast<uint8_t*>(args.workspace);
+          __half* narrowed = reinterpret_cast<__half*>(base);
+          uint32_t* magnitudes = reinterpret_cast<uint32_t*>(base + w.magnitudes);
+          float* tile_scales = reinterpret_cast<float*>(base + w.tile_scales);
+          uint32_t* verdict = reinterpret_cast<uint32_t*>(base + w.verdict);
+          const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(args.activation);
+          row_magnitude_kernel<<<static_cast<unsigned>(args.rows), 256, 0, args.stream>>>(
+              x, magnitudes, verdict, args.inputs);
+          narrow_rows_kernel<<<static_cast<unsigned>(args.rows), 256, 0, args.stream>>>(
+              x, magnitudes, narrowed, tile_scales, verdict, args.rows, args.inputs);
+          LinearArgs narrowed_args = args;
+          narrowed_args.activation = narrowed;
+          narrowed_args.tile_scale = tile_scales;
+          narrowed_args.gate = verdict;
+          narrowed_args.gate_when = 0;
+          const int32_t rc = launch_config<256, 1, 4, 3, 4, 3, 1, 1, false, kAf16, T, true>(
+              narrowed_args, device, message, capacity);
+          if (rc != NML_SM100_OK && rc != kDoesNotFit) return rc;
+          if (rc == NML_SM100_OK) {
+            plain.gate = verdict;
+            plain.gate_when = 1;
+          }
+        }
+      }
       // Wide K (4096): the shared-memory ring variant has room for one scale buffer only; the
       // tensor-memory variant (one accumulator set beside eight W' tiles, byte-table decode)
       // measured 9 % faster there, and equal or slower at K = 2880.
@@ -247,7 +404,7 @@ int32_t launch_for_rows(const LinearArgs& args, const DeviceInfo& device, char* 
         if (bulk_scales_legal && policy != NML_SM100_POLICY_UMMA_SMEM &&
             Ring::kSmemBytes + 2 * bulk_scale_buffer_bytes(args.inputs / 16) > kSmemBudget) {
           const int32_t rc = launch_config<256, 1, 4, 4, 8, 3, 1, 1, true, kAbf16Lut, T>(
-              args, device, message, capacity);
+              plain, device, message, capacity);
           if (rc != kDoesNotFit) return rc;
         }
       }
@@ -255,10 +412,10 @@ int32_t launch_for_rows(const LinearArgs& args, const DeviceInfo& device, char* 
       // K ~ 2900) fits beside three activation stages; else per-stage 4-byte copies
       if (bulk_scales_legal) {
         int32_t rc = launch_config<256, 1, 4, 3, 4, 3, 1, 1, false, AFMT, T, true>(
-            args, device, message, capacity);
+            plain, device, message, capacity);
         if (rc != kDoesNotFit) return rc;
       }
-      return launch_config<256, 1, 6, 4, 4, 3, 1, 1, false, AFMT, T>(args, device, message,
+      return launch_config<256, 1, 6, 4, 4, 3, 1, 1, false, AFMT, T>(plain, device, message,
                                                                      capacity);
     }
   }
@@ -275,6 +432,19 @@ bool linear_umma_supported(const LinearArgs& args) {
          reinterpret_cast<uintptr_t>(args.extra[i].block_scales) % 4 == 0;
   }
   return ok;
+}
+
+size_t linear_umma_workspace_bytes(int64_t rows, int64_t outputs, int64_t inputs,
+                                   int32_t dtype) {
+  if (dtype != NML_SM100_BF16 || rows < kNarrowMinRows || outputs < kNarrowMinOutputs ||
+      inputs % kTileK != 0) {
+    return 0;
+  }
+  return narrow_workspace(rows, inputs).total;
+}
+
+size_t linear_umma_workspace_verdict_offset(int64_t rows, int64_t inputs) {
+  return narrow_workspace(rows, inputs).verdict;
 }
 
 int32_t launch_linear_umma(const LinearArgs& args, const DeviceInfo& device, char* message,

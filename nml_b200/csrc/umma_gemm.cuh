@@ -140,6 +140,9 @@ struct Params {
   const int32_t* active_blocks;
   const int32_t* expert_offset;
   void* const* row_targets;       // down: optional destination of each assignment's row
+  const float* tile_scale;        // dense: optional factor of the sums of every BM-row tile
+  const uint32_t* gate;           // optional: the launch does nothing unless (*gate != 0) == gate_when
+  int gate_when;
   const void* routing_weights;
   int assignments, schedule_blocks, experts, top_k;
   // dense: up to three weights that share the activation operand (fused Q/K/V); a plain
@@ -442,6 +445,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
             const __grid_constant__ CUtensorMap tmap_x, const Params p,
             const __grid_constant__ CUtensorMap tmap_payload1,
             const __grid_constant__ CUtensorMap tmap_payload2) {
+  // Two launches share one decision made on the device (see narrow_rows_kernel): each reads
+  // the word and the one it does not name returns before it touches anything.
+  if (p.gate != nullptr && (__ldg(p.gate) != 0u) != (p.gate_when != 0)) return;
   constexpr bool GROUPED = MODE != kDense;
   constexpr int kGatherWarp0 = Roles<DG>::kGatherWarp0;  // first warp of the X side
   constexpr int kMmaWarpB = XTMA ? kGatherWarp0 + 1 : kGatherWarp0 + kGatherWarps;
@@ -771,7 +777,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
     // nothing (see mbar_wait_or_abort), so a timeout does not make the control flow divergent.
     {
       constexpr uint32_t a_format = AFMT == kAf16 ? kUmmaF16 : kUmmaBF16;
-      constexpr uint32_t b_format = std::is_same<T, __half>::value ? kUmmaF16 : kUmmaBF16;
+      // the activation tile holds F16 also when a BF16 call narrowed its rows beforehand
+      constexpr uint32_t b_format =
+          (std::is_same<T, __half>::value || AFMT == kAf16) ? kUmmaF16 : kUmmaBF16;
       // Tall tiles issue only as many activation rows (the MMA's N) as the unit has, rounded
       // up to 16: an expert's last slot tile, or the last rows of a dense operand, then costs
       // its share of the tensor pipe and of the operand reads instead of a full tile's.
@@ -900,6 +908,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
       if constexpr (!GROUPED) {
         const Params::Segment& segment = p.segment[u.expert];
         g = __ldg(segment.global_scale) * kDecodeFactor;
+        if (p.tile_scale != nullptr) g *= __ldg(p.tile_scale + u.m0 / BM);  // a power of two
         out = static_cast<T*>(segment.output);
         bias = static_cast<const T*>(segment.bias);
         residual = static_cast<const T*>(segment.residual);
@@ -996,8 +1005,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_payload,
               const int m = u.m0 + c + j;
               if (c + j < u.rows) {
                 const int64_t index = static_cast<int64_t>(m) * out_columns + n;
-                out[index] = narrow_with_residual<T>(fmaf(__uint_as_float(v[j]), g, bias_value),
-                                                     residual, index);
+                out[index] = narrow_with_residual<T>(
+                    fmaf(__uint_as_float(v[j]), g, bias_value), residual, index);
               }
             }
           }

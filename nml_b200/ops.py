@@ -98,6 +98,9 @@ class NvFp4Parameter:
                               self.block_scales[start:stop].contiguous(), self.global_scale)
 
 
+_LINEAR_SCRATCH: dict = {}
+
+
 def linear(input: torch.Tensor, weight: NvFp4Parameter, bias: torch.Tensor | None = None,
            out: torch.Tensor | None = None, residual: torch.Tensor | None = None) -> torch.Tensor:
     """``[..., K] x [N, K]^T (+ bias[N])`` with f32 accumulation; result in the input dtype.
@@ -131,11 +134,22 @@ def linear(input: torch.Tensor, weight: NvFp4Parameter, bias: torch.Tensor | Non
                 not residual.is_contiguous():
             raise ValueError("NVFP4 linear residual must match the result's shape and dtype")
         _require_cuda(residual)
+    # scratch for the F16 copy of the activations that wide weights decode fastest against
+    scratch = None
+    size = _abi.load().nml_nvfp4_sm100_linear_workspace_bytes(rows, outputs, inputs, dtype)
+    if size:
+        key = (input.device, torch.cuda.current_stream(input.device).cuda_stream)
+        scratch = _LINEAR_SCRATCH.get(key)
+        if scratch is None or scratch.numel() < size:
+            scratch = torch.empty(size, dtype=torch.uint8, device=input.device)
+            _LINEAR_SCRATCH[key] = scratch
     request = _abi.Linear(activation=_ptr(input), payload=_ptr(weight.payload),
                           block_scales=_ptr(weight.block_scales),
                           global_scale=_ptr(weight.global_scale), bias=_ptr(bias),
                           output=_ptr(out), stream=_stream(input), rows=rows, outputs=outputs,
-                          inputs=inputs, dtype=dtype, residual=_ptr(residual))
+                          inputs=inputs, dtype=dtype, residual=_ptr(residual),
+                          workspace=_ptr(scratch),
+                          workspace_bytes=0 if scratch is None else scratch.numel())
     _abi.call("nml_nvfp4_sm100_linear", request)
     return out
 

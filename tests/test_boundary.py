@@ -41,7 +41,9 @@ def test_struct_sizes_match_reference_prefix():
     # The reference structs (nml_nvfp4.h:18-92) on LP64: Linear 96, Embedding 88,
     # ExpertGateUp 152, ExpertDown 152 bytes; the two trailing pointers add 16.
     assert _abi.Linear.residual.offset == 96  # the reference struct ends here
-    assert ctypes.sizeof(_abi.Linear) == 104
+    assert _abi.Linear.workspace.offset == 104
+    assert _abi.Linear.workspace_bytes.offset == 112
+    assert ctypes.sizeof(_abi.Linear) == 120
     assert ctypes.sizeof(_abi.Embedding) == 88
     assert _abi.ExpertGateUp.active_blocks.offset == 152
     assert _abi.ExpertDown.active_blocks.offset == 152

@@ -183,6 +183,94 @@ def test_unembedding_shape(M):
     gu.assert_gemm_close(actual, expected, f"unembedding M={M}")
 
 
+def _plain_linear(x, weight, outputs):
+    """The same call without scratch: BF16 operands."""
+    from nml_b200 import ops, _abi
+    plain = torch.empty((x.shape[0], outputs), dtype=x.dtype, device=x.device)
+    request = _abi.Linear(activation=x.data_ptr(), payload=weight.payload.data_ptr(),
+                          block_scales=weight.block_scales.data_ptr(),
+                          global_scale=weight.global_scale.data_ptr(), bias=None,
+                          output=plain.data_ptr(), stream=ops._stream(x), rows=x.shape[0],
+                          outputs=outputs, inputs=x.shape[1], dtype=_abi.BF16)
+    _abi.call("nml_nvfp4_sm100_linear", request)
+    torch.cuda.synchronize()
+    assert _abi.last_linear_kernel().startswith("umma_swapab_abf16")
+    return plain
+
+
+def _verdict(M):
+    from nml_b200 import ops, _abi
+    lib = _abi.load()
+    assert lib.nml_nvfp4_sm100_linear_workspace_bytes(M, 201088, 2880, _abi.BF16) > 0
+    offset = lib.nml_nvfp4_sm100_linear_workspace_verdict_offset(M, 201088, 2880, _abi.BF16)
+    (scratch,) = [t for t in ops._LINEAR_SCRATCH.values()]
+    return int(scratch[offset:offset + 4].view(torch.int32).item())
+
+
+@pytest.mark.parametrize("M", [512, 700])
+def test_wide_weight_runs_on_narrowed_f16_operands(M):
+    # BF16 rows of a wide weight run as F16 operands, one power of two per 256-row tile, when
+    # the request carries scratch and every row lies within 2^8 of its tile's largest; tiles
+    # may differ by any factor, rows of zeros pass, the last tile is partial at M = 700
+    from nml_b200 import ops, _abi
+    import gpu_util as gu
+    triple = unembedding_weight()
+    if "weight" not in _UNEMBEDDING:
+        _UNEMBEDDING["weight"] = gu.parameter("head", triple, 2880, oracle.BF16)
+    weight = _UNEMBEDDING["weight"]
+    _, x32 = make_activation(777 + M, (M, 2880))
+    exponents = rng(778).integers(-3, 4, size=M)
+    exponents[256:512] += 50
+    exponents[512:] -= 60
+    x32 = x32 * np.exp2(exponents)[:, None].astype(np.float32)
+    x32[5] = 0.0
+    x = torch.from_numpy(x32).to(torch.bfloat16).cuda()
+    x32 = x.float().cpu().numpy()
+    y = ops.linear(x, weight)
+    torch.cuda.synchronize()
+    assert _abi.device_status(0x1) == 0
+    assert _abi.last_linear_kernel().startswith("umma_swapab_narrowed_af16")
+    assert _verdict(M) == 0
+    plain = _plain_linear(x, weight, 201088)
+    assert torch.isfinite(y).all()
+    assert (y[5] == 0).all()
+    # the same operands in another 16-bit format: a rounding step apart, up to cancellation
+    difference = (y.float() - plain.float()).abs()
+    slack = 1e-3 * plain.float().abs().amax(dim=1, keepdim=True)
+    assert (difference <= 2.0 ** -7 * plain.float().abs() + slack).all()
+    rows = np.array([0, 5, 300, M - 1])
+    expected = oracle.linear(x32[rows], *triple, None)
+    gu.assert_gemm_close(y[torch.from_numpy(rows).cuda()].float().cpu().numpy(), expected,
+                         "narrowed rows")
+
+
+@pytest.mark.parametrize("case", ["row_far_below_its_tile", "infinity", "tiny_tile"])
+def test_wide_weight_keeps_bf16_operands_where_narrowing_would_lose_bits(case):
+    # the device decides: the verdict word is raised and the BF16-operand kernel writes the
+    # output, bit for bit what the call gives without scratch
+    from nml_b200 import ops, _abi
+    import gpu_util as gu
+    triple = unembedding_weight()
+    if "weight" not in _UNEMBEDDING:
+        _UNEMBEDDING["weight"] = gu.parameter("head", triple, 2880, oracle.BF16)
+    weight = _UNEMBEDDING["weight"]
+    M = 512
+    _, x32 = make_activation(779, (M, 2880))
+    if case == "row_far_below_its_tile":
+        x32[300] *= 2.0 ** -20
+    elif case == "infinity":
+        x32[17, 100] = np.inf
+    else:
+        x32[256:] *= 2.0 ** -120
+    x = torch.from_numpy(x32).to(torch.bfloat16).cuda()
+    y = ops.linear(x, weight)
+    torch.cuda.synchronize()
+    assert _abi.device_status(0x1) == 0
+    assert _verdict(M) == 1
+    plain = _plain_linear(x, weight, 201088)
+    assert torch.equal(y.view(torch.int16), plain.view(torch.int16))
+
+
 def test_single_linear_of_the_cpu_runnable_configuration():
     # X bf16 [16, 2880], W [5760, 2880]
     from nml_b200 import _abi
