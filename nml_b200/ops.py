@@ -106,7 +106,10 @@ def linear(input: torch.Tensor, weight: NvFp4Parameter, bias: torch.Tensor | Non
     """``[..., K] x [N, K]^T (+ bias[N])`` with f32 accumulation; result in the input dtype.
     ``residual`` (shape and dtype of the result; may be ``out`` itself) is added to the narrowed
     result in the kernel's epilogue: bit for bit ``linear(...) + residual`` of the reference
-    graph's output projection (products/serve/src/gpt_oss/graph.rs:534-543) in one launch."""
+    graph's output projection (products/serve/src/gpt_oss/graph.rs:534-543) in one launch.
+    Calls the library can run faster with scratch (BF16 rows >= 512 on weights with >= 16384
+    outputs) get a buffer cached per device and stream; the library decides on the device
+    whether the faster kernel may write the output."""
     if input.dim() == 0:
         raise ValueError("linear input requires at least one dimension")
     if len(weight.shape) != 2:

@@ -203,7 +203,8 @@ def _verdict(M):
     lib = _abi.load()
     assert lib.nml_nvfp4_sm100_linear_workspace_bytes(M, 201088, 2880, _abi.BF16) > 0
     offset = lib.nml_nvfp4_sm100_linear_workspace_verdict_offset(M, 201088, 2880, _abi.BF16)
-    (scratch,) = [t for t in ops._LINEAR_SCRATCH.values()]
+    device = torch.device("cuda", torch.cuda.current_device())
+    scratch = ops._LINEAR_SCRATCH[(device, torch.cuda.current_stream(device).cuda_stream)]
     return int(scratch[offset:offset + 4].view(torch.int32).item())
 
 
