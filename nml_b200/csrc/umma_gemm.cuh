@@ -132,6 +132,7 @@ struct Params {
   // problem
   int M, N, K;            // dense: rows, outputs, inputs; grouped: N = output columns per expert
   int n_tiles, m_tiles, k_steps, n_fastest;
+  int m_block;            // dense, m fastest: row tiles per block (0: all row tiles in one)
   void* output;
   // grouped
   const void* input;  // hidden [tokens, K] (gate/up) or activated [assignments, K] (down)
@@ -384,6 +385,15 @@ __device__ __forceinline__ Unit get_unit(const Params& p, const Groups* groups, 
     if (p.n_fastest) {
       m_tile = index / p.n_tiles;
       n_tile = index - m_tile * p.n_tiles;
+    } else if (p.m_block > 0) {
+      // m fastest inside blocks of m_block row tiles: the block's activations stay in L2 while
+      // every weight tile passes over them; the weights stream once per block
+      const int block_units = p.m_block * p.n_tiles;
+      const int block = min(index / block_units, (p.m_tiles - 1) / p.m_block);
+      const int block_tiles = min(p.m_block, p.m_tiles - block * p.m_block);
+      const int inside = index - block * block_units;
+      n_tile = inside / block_tiles;
+      m_tile = block * p.m_block + (inside - n_tile * block_tiles);
     } else {
       n_tile = index / p.m_tiles;
       m_tile = index - n_tile * p.m_tiles;

@@ -272,6 +272,31 @@ def test_wide_weight_keeps_bf16_operands_where_narrowing_would_lose_bits(case):
     assert torch.equal(y.view(torch.int16), plain.view(torch.int16))
 
 
+@pytest.mark.parametrize("M", [4352, 16384])
+def test_unembedding_visits_every_tile_once_when_rows_are_walked_in_blocks(M):
+    # more activations than the L2 keeps: the row tiles are walked in blocks (17 tiles at
+    # M = 4352: one full block and a block of one).  Equal input rows must give equal output
+    # rows, and no element of a poisoned output may survive.
+    from nml_b200 import ops
+    import gpu_util as gu
+    triple = unembedding_weight()
+    if "weight" not in _UNEMBEDDING:
+        _UNEMBEDDING["weight"] = gu.parameter("head", triple, 2880, oracle.BF16)
+    weight = _UNEMBEDDING["weight"]
+    x_bits, x32 = make_activation(31, (1, 2880))
+    x = gu.to_device_bits(x_bits, oracle.BF16).expand(M, 2880).contiguous()
+    out = torch.full((M, 201088), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.linear(x, weight, out=out)
+    torch.cuda.synchronize()
+    first = out[0].clone()
+    assert torch.isfinite(first).all()
+    for start in range(0, M, 1024):  # chunks bound the temporaries
+        block = out[start:start + 1024]
+        assert torch.equal(block.view(torch.int16), first.view(torch.int16).expand_as(block))
+    expected = oracle.linear(x32, *triple, None)
+    gu.assert_gemm_close(first.float().cpu().numpy()[None], expected, "blocked walk")
+
+
 def test_single_linear_of_the_cpu_runnable_configuration():
     # X bf16 [16, 2880], W [5760, 2880]
     from nml_b200 import _abi
