@@ -89,14 +89,16 @@ int32_t launch_config(const LinearArgs& args, const DeviceInfo& device, char* me
   // Walk n fastest when the packed weights stay L2-resident (activations stream once);
   // otherwise walk m fastest so the large weight tensor streams once.
   p.n_fastest = weight_bytes <= (32ll << 20) ? 1 : 0;
-  // m fastest over more activations than stay in L2 beside the weight stream (measured: the
-  // vocabulary projection runs 20 % slower at 94 MB of activations than at 24 MB): walk them
-  // in blocks of about 24 MB; the weights then stream once per block, which costs little
-  // (0.33 GB per block against 17 ms of arithmetic at M = 16384).
+  // m fastest over more activations than stay in L2 beside the weight stream: walk them in
+  // blocks; the weights then stream once per block, which costs little (0.33 GB per block
+  // against 16 ms of arithmetic at M = 16384).  Measured on the vocabulary projection: up to
+  // 24 MB of activations (M = 4096) one block is fastest (1271-1339 TFLOP/s against 1235-1263
+  // in blocks of 12 MB); at 94 MB (M = 16384) blocks of 12 MB give 1232-1324, of 24 MB
+  // 1145-1262, of 6 MB 1203-1315, of 3 MB 1194-1256, one block about 1085.
   const int64_t tile_bytes = static_cast<int64_t>(BM) * args.inputs * 2;
-  int m_block = 1;  // the largest power of two of row tiles within 24 MB
-  while (2 * m_block * tile_bytes <= (24ll << 20)) m_block *= 2;
-  p.m_block = (!p.n_fastest && p.m_tiles > m_block && split_k == 1) ? m_block : 0;
+  int m_block = 1;  // the largest power of two of row tiles within 12 MB
+  while (2 * m_block * tile_bytes <= (12ll << 20)) m_block *= 2;
+  p.m_block = (!p.n_fastest && p.m_tiles * tile_bytes > (24ll << 20) && split_k == 1) ? m_block : 0;
   p.output = args.output;
   p.status = device.status_word;
   p.scale_buffer_bytes = scale_buffer_bytes;

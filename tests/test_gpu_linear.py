@@ -272,10 +272,10 @@ def test_wide_weight_keeps_bf16_operands_where_narrowing_would_lose_bits(case):
     assert torch.equal(y.view(torch.int16), plain.view(torch.int16))
 
 
-@pytest.mark.parametrize("M", [4352, 16384])
+@pytest.mark.parametrize("M", [4500, 16384])
 def test_unembedding_visits_every_tile_once_when_rows_are_walked_in_blocks(M):
-    # more activations than the L2 keeps: the row tiles are walked in blocks (17 tiles at
-    # M = 4352: one full block and a block of one).  Equal input rows must give equal output
+    # more than 24 MB of activations: the row tiles are walked in blocks of 8 (18 tiles at
+    # M = 4500: two full blocks and a block of two, the last tile partial).  Equal input rows must give equal output
     # rows, and no element of a poisoned output may survive.
     from nml_b200 import ops
     import gpu_util as gu
