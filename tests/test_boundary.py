@@ -141,6 +141,26 @@ def test_workspace_size_is_monotone_and_aligned():
     assert size(0, 2880, 2880, 32, 4) == 0
 
 
+def test_linear_scratch_is_offered_only_where_the_narrowed_operands_pay():
+    lib = _abi.load()
+    size = lib.nml_nvfp4_sm100_linear_workspace_bytes
+    verdict = lib.nml_nvfp4_sm100_linear_workspace_verdict_offset
+    wide = size(512, 201088, 2880, _abi.BF16)
+    # the narrowed rows, a magnitude per row, a factor per 256-row tile, the verdict word
+    assert wide >= 512 * 2880 * 2 + 512 * 4 + 2 * 4 + 4 and wide % 256 == 0
+    assert size(16384, 201088, 2880, _abi.BF16) > wide
+    assert 512 * 2880 * 2 <= verdict(512, 201088, 2880, _abi.BF16) <= wide - 4
+    assert verdict(512, 201088, 2880, _abi.BF16) % 4 == 0
+    for rows, outputs, inputs, dtype in ((511, 201088, 2880, _abi.BF16),   # few rows
+                                         (512, 5760, 2880, _abi.BF16),     # narrow weight
+                                         (512, 201088, 2880, _abi.F16),    # already F16
+                                         (512, 201088, 2872, _abi.BF16),   # K not in 64s
+                                         (0, 201088, 2880, _abi.BF16),
+                                         (512, 201088, 2880, 77)):
+        assert size(rows, outputs, inputs, dtype) == 0
+        assert verdict(rows, outputs, inputs, dtype) == 0
+
+
 def test_operators_refuse_cpu_tensors():
     import torch
     from nml_b200 import ops
