@@ -40,3 +40,27 @@ def test_decode_step_shape_and_bound():
     slowest = 1.0 / (shape.rope_factor * shape.rope_theta ** (31 / 32))
     assert math.isclose(frequencies[-1].item(), slowest, rel_tol=1e-5)  # slowest is interpolated
     assert math.isclose(factor, 0.1 * math.log(32.0) + 1.0)
+
+
+def test_f16_narrowing_bound_of_the_wide_linear():
+    # The dense linear narrows BF16 activations to F16, a 256-row tile times one power of two
+    # that puts the tile's largest magnitude into [2^14, 2^15).  The arithmetic of that pass,
+    # restated with torch on the CPU: elements down to 2^-28 of the tile's largest survive
+    # exactly, smaller ones are off by at most 2^-39 of it, and nothing overflows.
+    generator = torch.Generator().manual_seed(5)
+    tile = torch.randn((256, 512), generator=generator)
+    tile *= torch.exp2(torch.randint(-8, 1, (256, 1), generator=generator).float())  # rows within 2^8
+    tile[:, ::7] *= 2.0 ** -30   # elements far below their row
+    tile[3] = 0.0
+    tile = tile.to(torch.bfloat16)
+    largest = tile.float().abs().max()
+    exponent = math.floor(math.log2(float(largest)))
+    down = 2.0 ** (14 - exponent)
+    narrowed = (tile.float() * down).to(torch.float16)
+    assert torch.isfinite(narrowed).all()
+    assert 2.0 ** 14 <= float(narrowed.float().abs().max()) < 2.0 ** 15
+    restored = narrowed.float() / down
+    exact = tile.float().abs() >= float(largest) * 2.0 ** -28
+    assert torch.equal(restored[exact], tile.float()[exact])
+    assert float((restored - tile.float()).abs().max()) <= float(largest) * 2.0 ** -39
+    assert (restored[3] == 0).all()
